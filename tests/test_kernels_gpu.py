@@ -1,0 +1,227 @@
+"""Each CUDA kernel alone against its plain reference, at sizes other than the
+tiny models': head sizes in steps of 16, odd head counts and groups, widths and
+vocabularies that are no power of two."""
+
+from __future__ import annotations
+
+import pytest
+import torch
+
+import plain_ops
+
+pytestmark = pytest.mark.gpu
+
+DTYPES = [torch.float32, torch.bfloat16]
+
+
+def kernels():
+    import vllm_from_scratch_b200.kernels as k
+    return k
+
+
+def close(actual, expected, dtype, scale=1.0, what=""):
+    bound = (2e-5 if dtype == torch.float32 else 1.6e-2) * scale
+    diff = float((actual.float() - expected.float()).abs().max())
+    assert diff <= bound, f"{what}: max |diff| {diff:.3e} > {bound:.3e}"
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("tokens,hidden", [(1, 64), (7, 1000), (33, 2048), (5, 5120), (3, 8192 + 24)])
+def test_add_rmsnorm(dtype, tokens, hidden):
+    k = kernels()
+    g = torch.Generator(device="cuda").manual_seed(tokens * hidden)
+    x = torch.randn(tokens, hidden, device="cuda", generator=g).to(dtype)
+    residual = torch.randn(tokens, hidden, device="cuda", generator=g) * 3
+    weight = 1 + 0.1 * torch.randn(hidden, device="cuda", generator=g)
+    for with_x in (True, False):
+        res_a, res_b = residual.clone(), residual.clone()
+        out_a = torch.empty(tokens, hidden, device="cuda", dtype=dtype)
+        out_b = torch.empty_like(out_a)
+        k.add_rmsnorm(x if with_x else None, res_a, weight, 1e-5, out_a)
+        plain_ops.add_rmsnorm(x if with_x else None, res_b, weight, 1e-5, out_b)
+        close(out_a, out_b, dtype, scale=4, what="normed")
+        assert torch.allclose(res_a, res_b, atol=1e-6), "residual sum"
+    rows = torch.tensor([tokens - 1, 0], dtype=torch.int32, device="cuda")
+    res_a = residual.clone()
+    out_a = torch.empty(2, hidden, device="cuda", dtype=dtype)
+    out_b = torch.empty_like(out_a)
+    k.add_rmsnorm(x, res_a, weight, 1e-6, out_a, rows)
+    plain_ops.add_rmsnorm(x, residual.clone(), weight, 1e-6, out_b, rows)
+    close(out_a, out_b, dtype, scale=4, what="gathered rows")
+    assert torch.equal(res_a, residual), "gathered norm must not touch the residual"
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+def test_embedding_and_bad_id(dtype):
+    k = kernels()
+    table = torch.randn(503, 96, device="cuda").to(dtype)
+    ids = torch.tensor([0, 502, 17, 17, 250], dtype=torch.int32, device="cuda")
+    out = torch.empty(5, 96, device="cuda")
+    flag = torch.zeros(1, dtype=torch.int32, device="cuda")
+    k.embedding(table, ids, out, flag)
+    assert torch.equal(out, table[ids.long()].float()) and int(flag) == 0
+    ids[3] = 503
+    k.embedding(table, ids, out, flag)
+    assert int(flag) == 4 and float(out[3].abs().max()) == 0.0
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("tokens,inter", [(1, 160), (9, 6144), (130, 1111)])
+def test_silu_mul(dtype, tokens, inter):
+    k = kernels()
+    gate_up = (torch.randn(tokens, 2 * inter, device="cuda") * 3).to(dtype)
+    out_a = torch.empty(tokens, inter, device="cuda", dtype=dtype)
+    out_b = torch.empty_like(out_a)
+    k.silu_mul(gate_up, out_a)
+    plain_ops.silu_mul(gate_up, out_b)
+    close(out_a, out_b, dtype, scale=10, what="silu_mul")
+
+
+@pytest.mark.parametrize("m,n,k_", [(1, 503, 96), (5, 64, 64), (70, 257, 130), (129, 1000, 2048), (2, 4099, 77)])
+def test_gemm_f32_is_true_float32(m, n, k_):
+    k = kernels()
+    g = torch.Generator(device="cuda").manual_seed(m + n + k_)
+    x = torch.randn(m, k_, device="cuda", generator=g)
+    w = torch.randn(n, k_, device="cuda", generator=g)
+    out = torch.empty(m, n, device="cuda")
+    k.gemm(x, w, out)
+    exact = (x.double() @ w.double().T)
+    # float32 accumulation error grows like sqrt(K) * 2^-24 * |x||w|; TF32 would be ~1e-3.
+    assert float((out.double() - exact).abs().max()) < 2e-6 * (k_ ** 0.5) * 4
+    # a row's result does not depend on the rows beside it
+    alone = torch.empty(1, n, device="cuda")
+    k.gemm(x[m - 1:m].contiguous(), w, alone)
+    assert torch.equal(alone[0], out[m - 1])
+
+
+@pytest.mark.parametrize("m,n,k_", [(1, 512, 128), (8, 503, 96), (70, 264, 136), (300, 1024, 2048)])
+@pytest.mark.parametrize("out_dtype", [torch.bfloat16, torch.float32])
+def test_gemm_bf16(m, n, k_, out_dtype):
+    k = kernels()
+    g = torch.Generator(device="cuda").manual_seed(m + n + k_)
+    x = torch.randn(m, k_, device="cuda", generator=g).bfloat16()
+    w = torch.randn(n, k_, device="cuda", generator=g).bfloat16()
+    out = torch.empty(m, n, device="cuda", dtype=out_dtype)
+    k.gemm(x, w, out)
+    exact = x.double() @ w.double().T
+    scale = float(exact.abs().max())
+    bound = scale * (2 ** -8 if out_dtype == torch.bfloat16 else 1e-5)
+    assert float((out.double() - exact).abs().max()) <= bound
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("nq,nkv,d,rot,page", [(4, 2, 16, 16, 16), (6, 2, 32, 32, 8), (5, 5, 48, 48, 16),
+                                               (16, 8, 128, 128, 16), (3, 1, 80, 32, 4), (8, 2, 256, 256, 32)])
+def test_head_norm_rope_cache(dtype, nq, nkv, d, rot, page):
+    k = kernels()
+    tokens, pages = 37, 12
+    g = torch.Generator(device="cuda").manual_seed(nq * d)
+    qkv = torch.randn(tokens, (nq + 2 * nkv) * d, device="cuda", generator=g).to(dtype)
+    positions = torch.randint(0, 5000, (tokens,), device="cuda", generator=g, dtype=torch.int32)
+    slots = torch.randperm(pages * page, device="cuda", generator=g)[:tokens].to(torch.int32)
+    slots[5] = -1
+    qw = 1 + 0.1 * torch.randn(d, device="cuda", generator=g)
+    kw = 1 + 0.1 * torch.randn(d, device="cuda", generator=g)
+    inv_freq = 1.0 / (1e4 ** (torch.arange(0, rot, 2, dtype=torch.float32) / rot)).cuda()
+    for use_norm in (True, False):
+        outs = []
+        for op in (k.head_norm_rope_cache, plain_ops.head_norm_rope_cache):
+            q_out = torch.zeros(tokens, nq * d, device="cuda", dtype=dtype)
+            kp = torch.zeros(pages, nkv, page, d, device="cuda", dtype=dtype)
+            vp = torch.zeros_like(kp)
+            op(qkv, positions, slots, qw if use_norm else None, kw if use_norm else None, inv_freq, rot,
+               1e-6, q_out, kp, vp, nq, nkv, d, page)
+            outs.append((q_out, kp, vp))
+        scale = 1.0 if use_norm else 4.0
+        close(outs[0][0], outs[1][0], dtype, scale=4 * scale, what="queries")
+        close(outs[0][1], outs[1][1], dtype, scale=4 * scale, what="key pages")
+        assert torch.equal(outs[0][2], outs[1][2]), "values are copied as they are"
+    # no cache given: only queries are produced
+    q_out = torch.zeros(tokens, nq * d, device="cuda", dtype=dtype)
+    k.head_norm_rope_cache(qkv, positions, slots, qw, kw, inv_freq, rot, 1e-6, q_out, None, None, nq, nkv, d, page)
+    assert float(q_out.abs().max()) > 0
+
+
+def _attention_case(dtype, nq, nkv, d, page, q_lens, seq_lens, window, seed=0, standout=False):
+    g = torch.Generator(device="cuda").manual_seed(seed)
+    requests = len(q_lens)
+    tokens = sum(q_lens)
+    pages_per = [-(-s // page) for s in seq_lens]
+    total_pages = sum(pages_per) + 3
+    order = torch.randperm(total_pages, device="cuda", generator=g).tolist()
+    table = torch.full((requests, max(pages_per)), -1, dtype=torch.int32, device="cuda")
+    at = 0
+    for r, n in enumerate(pages_per):
+        table[r, :n] = torch.tensor(order[at:at + n], dtype=torch.int32)
+        at += n
+    kp = torch.randn(total_pages, nkv, page, d, device="cuda", generator=g).to(dtype)
+    vp = torch.randn(total_pages, nkv, page, d, device="cuda", generator=g).to(dtype)
+    q = torch.randn(tokens, nq * d, device="cuda", generator=g).to(dtype)
+    if standout:
+        # One far key gets a large score for every query of request 0: the result
+        # must be dominated by that key's value.
+        far = 3
+        page_id, offset = int(table[0, far // page]), far % page
+        kp[page_id, :, offset, :] = 0
+        kp[page_id, :, offset, 0] = 30.0
+        q.view(tokens, nq, d)[:q_lens[0], :, 0] = 6.0
+    import itertools
+    query_start = torch.tensor([0] + list(itertools.accumulate(q_lens)), dtype=torch.int32, device="cuda")
+    seq = torch.tensor(seq_lens, dtype=torch.int32, device="cuda")
+    return q, kp, vp, query_start, seq, table
+
+
+ATTENTION_SHAPES = [
+    # nq, nkv, d, page, q_lens, seq_lens, window
+    (4, 2, 16, 16, [5, 1, 17], [5, 40, 33], None),
+    (6, 2, 32, 8, [1, 1, 1, 1], [1, 7, 64, 130], None),
+    (5, 5, 48, 16, [40, 2], [100, 77], 24),
+    (16, 8, 128, 16, [1, 64, 3], [700, 64, 290], None),
+    (8, 1, 64, 32, [33], [300], 50),
+    (3, 3, 80, 4, [20, 1], [20, 90], None),
+    (2, 1, 256, 16, [18, 1], [50, 200], None),
+]
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("shape", ATTENTION_SHAPES)
+def test_paged_attention(dtype, shape):
+    k = kernels()
+    nq, nkv, d, page, q_lens, seq_lens, window = shape
+    for standout in (False, True):
+        q, kp, vp, start, seq, table = _attention_case(dtype, nq, nkv, d, page, q_lens, seq_lens, window,
+                                                       seed=nq * d + page, standout=standout)
+        out_a = torch.zeros_like(q)
+        out_b = torch.zeros_like(q)
+        args = (start, seq, table, nq, nkv, d, page, d ** -0.5, window, max(q_lens), max(seq_lens))
+        k.paged_attention(q, kp, vp, out_a, *args)
+        plain_ops.paged_attention(q, kp, vp, out_b, *args)
+        close(out_a, out_b, dtype, scale=4, what=f"attention standout={standout}")
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+def test_attention_window_edge_and_released_pages(dtype):
+    """A key exactly at the window's edge is read, the one before it is not, and a
+    page that was given back (-1 in the table) is never touched."""
+    k = kernels()
+    nq, nkv, d, page, window = 2, 1, 32, 8, 10
+    q, kp, vp, start, seq, table = _attention_case(dtype, nq, nkv, d, page, [1], [41], window, seed=9)
+    # query at position 40 reads keys 31..40; make key 31 (edge, inside) and key 30 (outside) stand out
+    q.view(1, nq, d)[:] = 0
+    q.view(1, nq, d)[:, :, 0] = 8.0
+    for pos, value in ((31, 12.0), (30, 20.0)):
+        kp[int(table[0, pos // page]), :, pos % page, :] = 0
+        kp[int(table[0, pos // page]), :, pos % page, 0] = value
+    released = table.clone()
+    released[0, :3] = -1                       # positions 0..23 lie before every window
+    outs = []
+    for tab in (table, released):
+        out = torch.zeros_like(q)
+        k.paged_attention(q, kp, vp, out, start, seq, tab, nq, nkv, d, page, d ** -0.5, window, 1, 41)
+        outs.append(out)
+    expected = torch.zeros_like(q)
+    plain_ops.paged_attention(q, kp, vp, expected, start, seq, table, nq, nkv, d, page, d ** -0.5, window, 1, 41)
+    close(outs[0], expected, dtype, scale=4, what="window edge")
+    assert torch.equal(outs[0], outs[1]), "released pages must not matter"
+    edge_value = vp[int(table[0, 31 // page]), 0, 31 % page].float()
+    assert float((outs[0].view(nq, d)[0].float() - edge_value).abs().max()) < 0.05, "edge key must dominate"

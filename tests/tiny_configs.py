@@ -1,0 +1,34 @@
+"""Tiny Qwen3 configurations for the tests.  A and B differ in every size and
+option; C adds layers that see a window of keys only."""
+
+TINY_A = {
+    "architectures": ["Qwen3ForCausalLM"], "model_type": "qwen3",
+    "num_hidden_layers": 2, "hidden_size": 64, "num_attention_heads": 4, "num_key_value_heads": 2,
+    "head_dim": 16, "intermediate_size": 128, "vocab_size": 256, "rope_theta": 10000.0,
+    "rms_norm_eps": 1e-6, "tie_word_embeddings": True, "max_position_embeddings": 128,
+    "hidden_act": "silu", "attention_bias": False, "initializer_range": 0.02,
+}
+
+TINY_B = {
+    "architectures": ["Qwen3ForCausalLM"], "model_type": "qwen3",
+    "num_hidden_layers": 3, "hidden_size": 96, "num_attention_heads": 6, "num_key_value_heads": 2,
+    "head_dim": 32, "intermediate_size": 160, "vocab_size": 503, "rope_theta": 1000000.0,
+    "rms_norm_eps": 1e-5, "tie_word_embeddings": False, "max_position_embeddings": 256,
+    "hidden_act": "silu", "attention_bias": False, "initializer_range": 0.02,
+}
+
+# Windowed layers beside full ones: two cache groups, pages of the windowed group
+# come back while the request still runs.
+TINY_C = {
+    "architectures": ["Qwen3ForCausalLM"], "model_type": "qwen3",
+    "num_hidden_layers": 4, "hidden_size": 80, "num_attention_heads": 5, "num_key_value_heads": 5,
+    "head_dim": 48, "intermediate_size": 112, "vocab_size": 311, "rope_theta": 50000.0,
+    "rms_norm_eps": 1e-5, "tie_word_embeddings": True, "max_position_embeddings": 512,
+    "hidden_act": "silu", "attention_bias": False, "initializer_range": 0.02,
+    "use_sliding_window": True, "sliding_window": 24,
+    "layer_types": ["full_attention", "sliding_attention", "sliding_attention", "full_attention"],
+}
+
+# Larger standard deviations than a checkpoint's, so that attention scores and
+# logits are far from uniform and a wrong key or a wrong page shows in the result.
+INIT = {"std": 0.08, "norm_std": 0.1}

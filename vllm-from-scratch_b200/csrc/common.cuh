@@ -1,0 +1,74 @@
+// Shared helpers of the sm_100a kernels: element conversion, warp and block
+// reductions, launch-error reporting.  Every launcher is `extern "C"`, takes raw
+// device pointers and a stream, and returns 0 or a negative code after storing a
+// message that `b200_last_error` hands to the Python side.
+#pragma once
+
+#include <cuda_bf16.h>
+#include <cuda_runtime.h>
+#include <stdint.h>
+#include <stdio.h>
+
+#define B200_EXPORT extern "C" __attribute__((visibility("default")))
+
+namespace b200 {
+
+inline char* error_buffer() {
+    static thread_local char buffer[512];
+    return buffer;
+}
+
+inline int fail(const char* where, const char* what) {
+    snprintf(error_buffer(), 512, "%s: %s", where, what);
+    return -1;
+}
+
+inline int check_launch(const char* where) {
+    cudaError_t status = cudaGetLastError();
+    if (status != cudaSuccess) return fail(where, cudaGetErrorString(status));
+    return 0;
+}
+
+__device__ __forceinline__ float to_float(float v) { return v; }
+__device__ __forceinline__ float to_float(__nv_bfloat16 v) { return __bfloat162float(v); }
+
+template <typename T> __device__ __forceinline__ T from_float(float v);
+template <> __device__ __forceinline__ float from_float<float>(float v) { return v; }
+template <> __device__ __forceinline__ __nv_bfloat16 from_float<__nv_bfloat16>(float v) {
+    return __float2bfloat16_rn(v);
+}
+
+__device__ __forceinline__ float warp_sum(float v) {
+#pragma unroll
+    for (int offset = 16; offset > 0; offset >>= 1) v += __shfl_xor_sync(0xffffffffu, v, offset);
+    return v;
+}
+
+__device__ __forceinline__ float warp_max(float v) {
+#pragma unroll
+    for (int offset = 16; offset > 0; offset >>= 1) v = fmaxf(v, __shfl_xor_sync(0xffffffffu, v, offset));
+    return v;
+}
+
+// Sum over the whole block; every thread gets the result.  `scratch` holds 33 floats.
+__device__ __forceinline__ float block_sum(float v, float* scratch) {
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    const int warps = (blockDim.x + 31) >> 5;
+    v = warp_sum(v);
+    if (lane == 0) scratch[warp] = v;
+    __syncthreads();
+    if (warp == 0) {
+        float total = lane < warps ? scratch[lane] : 0.0f;
+        total = warp_sum(total);
+        if (lane == 0) scratch[32] = total;
+    }
+    __syncthreads();
+    float result = scratch[32];
+    __syncthreads();
+    return result;
+}
+
+}  // namespace b200
+
+// One translation unit per shared object, so this definition appears once in each.
+B200_EXPORT const char* b200_last_error() { return b200::error_buffer(); }

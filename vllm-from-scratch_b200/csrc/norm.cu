@@ -1,0 +1,130 @@
+// Embedding gather and RMSNorm with the residual sum fused in.
+//
+// The residual stream is float32 in both run modes.  One block per row:
+//   pass 1: v = residual + x (x optional), stored back unless rows are gathered,
+//           sum of squares accumulated in float32;
+//   pass 2: out = v * rsqrt(mean(v^2) + eps) * weight, rounded once to the run dtype.
+// Formula: minivllm/layers/ops/layernorm.py:196-227 (epsilon inside the root, no
+// bias, plain weight); the sum and the statistics stay in 32-bit as in
+// minivllm/layers/ops/layernorm.py:75-90.
+#include "common.cuh"
+
+namespace b200 {
+
+template <typename T>
+__global__ void add_rmsnorm_kernel(const T* __restrict__ x, float* __restrict__ residual,
+                                   const float* __restrict__ weight, T* __restrict__ out,
+                                   const int* __restrict__ rows, int hidden, float eps) {
+    __shared__ float scratch[33];
+    const int out_row = blockIdx.x;
+    const int row = rows ? rows[out_row] : out_row;
+    const size_t base = (size_t)row * hidden;
+    const bool store_sum = (rows == nullptr) && (x != nullptr);
+    float sum_sq = 0.0f;
+    for (int i = threadIdx.x; i < hidden; i += blockDim.x) {
+        float v = residual[base + i];
+        if (x) v += to_float(x[base + i]);
+        if (store_sum) residual[base + i] = v;
+        sum_sq = fmaf(v, v, sum_sq);
+    }
+    const float total = block_sum(sum_sq, scratch);
+    const float inv = rsqrtf(total / (float)hidden + eps);
+    const size_t out_base = (size_t)out_row * hidden;
+    for (int i = threadIdx.x; i < hidden; i += blockDim.x) {
+        float v = residual[base + i];
+        if (x && !store_sum) v += to_float(x[base + i]);
+        out[out_base + i] = from_float<T>(v * inv * weight[i]);
+    }
+}
+
+template <typename T>
+__global__ void embedding_kernel(const T* __restrict__ table, const int* __restrict__ ids,
+                                 float* __restrict__ residual, int hidden, int vocab,
+                                 int* __restrict__ error_flag) {
+    const int token = blockIdx.x;
+    const int id = ids[token];
+    if (id < 0 || id >= vocab) {
+        // A token id outside the table: record it and write zeros instead of reading.
+        if (threadIdx.x == 0) atomicExch(error_flag, token + 1);
+        for (int i = threadIdx.x; i < hidden; i += blockDim.x) residual[(size_t)token * hidden + i] = 0.0f;
+        return;
+    }
+    const T* src = table + (size_t)id * hidden;
+    for (int i = threadIdx.x; i < hidden; i += blockDim.x)
+        residual[(size_t)token * hidden + i] = to_float(src[i]);
+}
+
+template <typename T>
+__global__ void silu_mul_kernel(const T* __restrict__ gate_up, T* __restrict__ out, int inter, size_t total) {
+    // out[t, i] = silu(gate_up[t, i]) * gate_up[t, inter + i], all in float32.
+    for (size_t idx = (size_t)blockIdx.x * blockDim.x + threadIdx.x; idx < total;
+         idx += (size_t)gridDim.x * blockDim.x) {
+        const size_t token = idx / inter;
+        const int i = (int)(idx - token * inter);
+        const float g = to_float(gate_up[token * 2 * inter + i]);
+        const float u = to_float(gate_up[token * 2 * inter + inter + i]);
+        const float s = g / (1.0f + expf(-g));
+        out[idx] = from_float<T>(s * u);
+    }
+}
+
+inline int norm_threads(int hidden) {
+    int threads = 128;
+    while (threads < 1024 && threads * 4 < hidden) threads *= 2;
+    return threads;
+}
+
+}  // namespace b200
+
+// dtype: 0 = float32, 1 = bfloat16 (the dtype of x and out; residual and weight are float32).
+B200_EXPORT int b200_add_rmsnorm(const void* x, float* residual, const float* weight, void* out,
+                                 const int* rows, int num_rows, int hidden, float eps, int dtype,
+                                 cudaStream_t stream) {
+    using namespace b200;
+    if (num_rows == 0) return 0;
+    if (num_rows < 0 || hidden <= 0) return fail("add_rmsnorm", "negative row count or width");
+    const int threads = norm_threads(hidden);
+    if (dtype == 0)
+        add_rmsnorm_kernel<float><<<num_rows, threads, 0, stream>>>(
+            (const float*)x, residual, weight, (float*)out, rows, hidden, eps);
+    else if (dtype == 1)
+        add_rmsnorm_kernel<__nv_bfloat16><<<num_rows, threads, 0, stream>>>(
+            (const __nv_bfloat16*)x, residual, weight, (__nv_bfloat16*)out, rows, hidden, eps);
+    else
+        return fail("add_rmsnorm", "dtype must be 0 (float32) or 1 (bfloat16)");
+    return check_launch("add_rmsnorm");
+}
+
+B200_EXPORT int b200_embedding(const void* table, const int* ids, float* residual, int num_tokens,
+                               int hidden, int vocab, int* error_flag, int dtype, cudaStream_t stream) {
+    using namespace b200;
+    if (num_tokens == 0) return 0;
+    const int threads = norm_threads(hidden);
+    if (dtype == 0)
+        embedding_kernel<float><<<num_tokens, threads, 0, stream>>>(
+            (const float*)table, ids, residual, hidden, vocab, error_flag);
+    else if (dtype == 1)
+        embedding_kernel<__nv_bfloat16><<<num_tokens, threads, 0, stream>>>(
+            (const __nv_bfloat16*)table, ids, residual, hidden, vocab, error_flag);
+    else
+        return fail("embedding", "dtype must be 0 (float32) or 1 (bfloat16)");
+    return check_launch("embedding");
+}
+
+B200_EXPORT int b200_silu_mul(const void* gate_up, void* out, int num_tokens, int inter, int dtype,
+                              cudaStream_t stream) {
+    using namespace b200;
+    const size_t total = (size_t)num_tokens * inter;
+    if (total == 0) return 0;
+    const int threads = 256;
+    size_t blocks = (total + threads - 1) / threads;
+    if (blocks > 148 * 32) blocks = 148 * 32;
+    if (dtype == 0)
+        silu_mul_kernel<float><<<(int)blocks, threads, 0, stream>>>((const float*)gate_up, (float*)out, inter, total);
+    else if (dtype == 1)
+        silu_mul_kernel<__nv_bfloat16><<<(int)blocks, threads, 0, stream>>>(
+            (const __nv_bfloat16*)gate_up, (__nv_bfloat16*)out, inter, total);
+    else
+        return fail("silu_mul", "dtype must be 0 (float32) or 1 (bfloat16)");
+    return check_launch("silu_mul");
+}

@@ -1,0 +1,66 @@
+"""Everything below the scheduler in one object: the model with its weights, the
+cache's memory and books, and the step function over them.  The replay program
+and the generating engine both build this and nothing else; the reference's
+counterpart is the chain ``Worker.load_model`` -> ``GPUModelRunner`` ->
+``initialize_kv_cache`` (minivllm/worker/worker.py:76-103, minivllm/worker/
+gpu_model_runner.py:342-371, 585-660)."""
+
+from __future__ import annotations
+
+from pathlib import Path
+from typing import Mapping
+
+import torch
+
+from ..cache import CacheManager, CacheStorage
+from ..config.registry import load_model_config
+from ..parts.model import DecoderModel
+from ..parts.spec import ModelSpec
+from ..weights.loader import load_weights, load_weights_from_tensors
+from .step import StepEntry, StepFunction
+
+_TORCH_DTYPE = {"float32": torch.float32, "bfloat16": torch.bfloat16}
+
+
+def require_device(device: str | torch.device) -> torch.device:
+    device = torch.device(device)
+    if device.type == "cuda" and not torch.cuda.is_available():
+        raise RuntimeError(
+            "no CUDA device is visible: the engine runs its own sm_100a kernels and has no CPU path")
+    return device
+
+
+class ModelRunner:
+    def __init__(self, spec: ModelSpec, weights: str | Path | Mapping[str, torch.Tensor], dtype: str,
+                 page_size: int, num_pages: int, max_requests: int, device: str | torch.device = "cuda",
+                 enable_prefix_caching: bool = False, model_config=None) -> None:
+        self.device = require_device(device)
+        self.dtype = _TORCH_DTYPE[dtype]
+        self.model_config = model_config
+        if self.dtype == torch.float32:
+            # The 32-bit mode is 32-bit everywhere: nothing may route a product
+            # through a reduced-precision tensor-core mode.
+            torch.backends.cuda.matmul.allow_tf32 = False
+            torch.backends.cudnn.allow_tf32 = False
+        self.model = DecoderModel(spec, self.dtype, self.device)
+        if isinstance(weights, Mapping):
+            load_weights_from_tensors(self.model, weights)
+        else:
+            load_weights(self.model, weights)
+        cache_from = [entry.cache_from for entry in spec.schedule]
+        self.storage = CacheStorage(self.model.cache_needs(), cache_from, page_size, num_pages,
+                                    max_requests, self.dtype, self.device)
+        self.manager = CacheManager(self.storage.group_windows, page_size, num_pages, max_requests,
+                                    enable_prefix_caching, has_state=self.storage.has_state)
+        self.step_function = StepFunction(self.model, self.storage, self.manager)
+
+    @classmethod
+    def from_folder(cls, folder: str | Path, dtype: str, page_size: int, num_pages: int,
+                    max_requests: int, device: str | torch.device = "cuda",
+                    enable_prefix_caching: bool = False) -> "ModelRunner":
+        entry, config = load_model_config(folder)
+        return cls(entry.build_spec(config), folder, dtype, page_size, num_pages, max_requests, device,
+                   enable_prefix_caching, model_config=config)
+
+    def step(self, entries: list[StepEntry]) -> torch.Tensor | None:
+        return self.step_function.run(entries)

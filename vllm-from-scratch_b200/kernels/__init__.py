@@ -1,0 +1,188 @@
+"""Python face of the hand-written sm_100a kernels.
+
+Each function checks its tensors (device, dtype, contiguity, shapes), then calls
+one ``extern "C"`` launcher on torch's current CUDA stream.  Nothing here has a
+CPU or library alternative: a tensor that is not on a CUDA device, or a kernel
+library that cannot be built, raises.  (The bfloat16 matrix product may go to
+the vendor's library, as the reference's does through ``F.linear``,
+minivllm/layers/quantization/methods.py:36-37.)
+"""
+
+from __future__ import annotations
+
+import ctypes
+from typing import Sequence
+
+import torch
+
+from ..csrc.build import load_library
+
+_DTYPE_CODE = {torch.float32: 0, torch.bfloat16: 1}
+
+
+class KernelError(RuntimeError):
+    pass
+
+
+def _code(dtype: torch.dtype) -> int:
+    try:
+        return _DTYPE_CODE[dtype]
+    except KeyError:
+        raise KernelError(f"kernels are built for float32 and bfloat16, not {dtype}") from None
+
+
+def _check(name: str, tensor: torch.Tensor | None, dtype: torch.dtype | Sequence[torch.dtype] | None = None,
+           shape: Sequence[int | None] | None = None, optional: bool = False) -> int:
+    """Validate one operand and return its device address (0 for an absent optional)."""
+    if tensor is None:
+        if optional:
+            return 0
+        raise KernelError(f"{name}: tensor is required")
+    if not tensor.is_cuda:
+        raise KernelError(
+            f"{name}: tensor lives on {tensor.device}; the engine's kernels run on a CUDA device only")
+    if not tensor.is_contiguous():
+        raise KernelError(f"{name}: tensor must be contiguous, strides {tensor.stride()}")
+    if dtype is not None:
+        allowed = (dtype,) if isinstance(dtype, torch.dtype) else tuple(dtype)
+        if tensor.dtype not in allowed:
+            raise KernelError(f"{name}: dtype {tensor.dtype}, expected {allowed}")
+    if shape is not None:
+        if tensor.dim() != len(shape) or any(s is not None and s != t for s, t in zip(shape, tensor.shape)):
+            raise KernelError(f"{name}: shape {tuple(tensor.shape)}, expected {tuple(shape)}")
+    return tensor.data_ptr()
+
+
+def _stream() -> ctypes.c_void_p:
+    return ctypes.c_void_p(torch.cuda.current_stream().cuda_stream)
+
+
+def _run(library: str, symbol: str, *args) -> None:
+    lib = load_library(library)
+    status = getattr(lib, symbol)(*args)
+    if status != 0:
+        raise KernelError(lib.b200_last_error().decode())
+
+
+_P = ctypes.c_void_p
+_I = ctypes.c_int
+_F = ctypes.c_float
+
+
+# ------------------------------------------------------------------ elementwise
+def embedding(table: torch.Tensor, ids: torch.Tensor, residual: torch.Tensor,
+              error_flag: torch.Tensor) -> None:
+    """``residual[t] = float32(table[ids[t]])``; an id outside the table sets
+    ``error_flag`` to 1 + the token's row and writes zeros."""
+    vocab, hidden = table.shape
+    tokens = ids.shape[0]
+    _run("norm", "b200_embedding",
+         _P(_check("embedding table", table, (torch.float32, torch.bfloat16))),
+         _P(_check("token ids", ids, torch.int32, (tokens,))),
+         _P(_check("residual", residual, torch.float32, (tokens, hidden))),
+         _I(tokens), _I(hidden), _I(vocab),
+         _P(_check("error flag", error_flag, torch.int32)), _I(_code(table.dtype)), _stream())
+
+
+def add_rmsnorm(x: torch.Tensor | None, residual: torch.Tensor, weight: torch.Tensor, eps: float,
+                out: torch.Tensor, rows: torch.Tensor | None = None) -> None:
+    """``residual += x`` in float32 (skipped when ``x`` is None), then
+    ``out = residual * rsqrt(mean(residual^2) + eps) * weight`` in ``out``'s dtype.
+    With ``rows`` only those rows are normalised, written compactly to ``out``,
+    and ``residual`` is left as it was."""
+    tokens, hidden = residual.shape
+    out_rows = tokens if rows is None else rows.shape[0]
+    _run("norm", "b200_add_rmsnorm",
+         _P(_check("norm input", x, out.dtype, (tokens, hidden), optional=True)),
+         _P(_check("residual", residual, torch.float32)),
+         _P(_check("norm weight", weight, torch.float32, (hidden,))),
+         _P(_check("norm output", out, (torch.float32, torch.bfloat16), (out_rows, hidden))),
+         _P(_check("row index", rows, torch.int32, optional=True)),
+         _I(out_rows), _I(hidden), _F(eps), _I(_code(out.dtype)), _stream())
+
+
+def silu_mul(gate_up: torch.Tensor, out: torch.Tensor) -> None:
+    """``out = silu(gate_up[:, :I]) * gate_up[:, I:]`` computed in float32."""
+    tokens, inter = out.shape
+    _run("norm", "b200_silu_mul",
+         _P(_check("gate_up", gate_up, out.dtype, (tokens, 2 * inter))),
+         _P(_check("activation output", out, (torch.float32, torch.bfloat16))),
+         _I(tokens), _I(inter), _I(_code(out.dtype)), _stream())
+
+
+# --------------------------------------------------------------- matrix product
+def gemm(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor) -> None:
+    """``out[M, N] = x[M, K] @ w[N, K]^T``.  float32 operands: the engine's own
+    fused-multiply-add kernel (no tensor-core mode).  bfloat16 operands: float32
+    accumulation on the tensor cores; ``out`` may be bfloat16 or float32."""
+    m, k = x.shape
+    n = w.shape[0]
+    if x.dtype == torch.float32:
+        _run("gemm_f32", "b200_gemm_f32",
+             _P(_check("gemm input", x, torch.float32)), _P(_check("gemm weight", w, torch.float32, (n, k))),
+             _P(_check("gemm output", out, torch.float32, (m, n))), _I(m), _I(n), _I(k), _stream())
+        return
+    _check("gemm input", x, torch.bfloat16)
+    _check("gemm weight", w, torch.bfloat16, (n, k))
+    _check("gemm output", out, (torch.bfloat16, torch.float32), (m, n))
+    from . import gemm_bf16
+    gemm_bf16.gemm_bf16(x, w, out)
+
+
+# -------------------------------------------------------------------- attention
+def head_norm_rope_cache(qkv: torch.Tensor, positions: torch.Tensor, slots: torch.Tensor,
+                         q_weight: torch.Tensor | None, k_weight: torch.Tensor | None,
+                         inv_freq: torch.Tensor | None, rotary_dim: int, eps: float,
+                         q_out: torch.Tensor, k_pages: torch.Tensor | None,
+                         v_pages: torch.Tensor | None, num_q_heads: int, num_kv_heads: int,
+                         head_dim: int, page_size: int) -> None:
+    """From the packed projection ``[T, (nq + 2 nkv) d]``: per-head RMSNorm of
+    queries and keys, rotate-half position encoding, queries to ``q_out``, keys
+    and values to their pages at ``slots`` (negative slot: not stored; pages None:
+    nothing stored)."""
+    tokens = qkv.shape[0]
+    dtype = qkv.dtype
+    width = (num_q_heads + 2 * num_kv_heads) * head_dim
+    page_shape = (None, num_kv_heads, page_size, head_dim)
+    _run("rope_cache", "b200_head_norm_rope_cache",
+         _P(_check("qkv", qkv, (torch.float32, torch.bfloat16), (tokens, width))),
+         _P(_check("positions", positions, torch.int32, (tokens,))),
+         _P(_check("slot mapping", slots, torch.int32, (tokens,))),
+         _P(_check("q head-norm weight", q_weight, torch.float32, (head_dim,), optional=True)),
+         _P(_check("k head-norm weight", k_weight, torch.float32, (head_dim,), optional=True)),
+         _P(_check("inverse frequencies", inv_freq, torch.float32, (rotary_dim // 2,), optional=True)),
+         _P(_check("q output", q_out, dtype, (tokens, num_q_heads * head_dim))),
+         _P(_check("key pages", k_pages, dtype, page_shape, optional=True)),
+         _P(_check("value pages", v_pages, dtype, page_shape, optional=True)),
+         _I(tokens), _I(num_q_heads), _I(num_kv_heads), _I(head_dim), _I(rotary_dim), _I(page_size),
+         _F(eps), _I(_code(dtype)), _stream())
+
+
+def paged_attention(q: torch.Tensor, k_pages: torch.Tensor, v_pages: torch.Tensor, out: torch.Tensor,
+                    query_start: torch.Tensor, seq_lens: torch.Tensor, block_table: torch.Tensor,
+                    num_q_heads: int, num_kv_heads: int, head_dim: int, page_size: int, scale: float,
+                    window: int | None, max_query_len: int, max_seq_len: int) -> None:
+    """Causal attention of every request's new queries over its pages."""
+    tokens = q.shape[0]
+    requests = seq_lens.shape[0]
+    dtype = q.dtype
+    page_shape = (None, num_kv_heads, page_size, head_dim)
+    args_checked = (
+        _check("queries", q, (torch.float32, torch.bfloat16), (tokens, num_q_heads * head_dim)),
+        _check("key pages", k_pages, dtype, page_shape),
+        _check("value pages", v_pages, dtype, page_shape),
+        _check("attention output", out, dtype, (tokens, num_q_heads * head_dim)),
+        _check("query_start", query_start, torch.int32, (requests + 1,)),
+        _check("seq_lens", seq_lens, torch.int32, (requests,)),
+        _check("block table", block_table, torch.int32, (requests, None)),
+    )
+    if dtype == torch.bfloat16:
+        from . import attention_bf16
+        if attention_bf16.paged_attention_bf16(
+                q, k_pages, v_pages, out, query_start, seq_lens, block_table, num_q_heads,
+                num_kv_heads, head_dim, page_size, scale, window, max_query_len, max_seq_len):
+            return
+    _run("attention_generic", "b200_paged_attention_generic",
+         *(_P(a) for a in args_checked),
+         _I(requests), _I(tokens), _I(block_table.shape[1]), _I(num_q_heads), _I(num_kv_heads),
+         _I(head_dim), _I(page_size), _F(scale), _I(window or 0), _I(_code(dtype)), _stream())

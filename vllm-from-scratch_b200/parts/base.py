@@ -1,0 +1,212 @@
+"""Interfaces of the parts and the registries that map a kind to its class.
+
+A part is built from ``(params, env)``: ``params`` are the sizes and constants
+of its :class:`~.spec.PartSpec`, ``env`` says what it is embedded in (the width
+of the residual stream, the run dtype, the device, the prefix of its tensors).
+A part never learns which model it belongs to.
+
+Every part names the tensors it wants (:meth:`Part.expected_weights`) and takes
+them in :meth:`Part.load_weights`; the loader compares the union of these names
+with the checkpoint before any tensor is read.
+"""
+
+from __future__ import annotations
+
+from dataclasses import dataclass, field
+from typing import Any, Callable, Mapping
+
+import torch
+
+
+# --------------------------------------------------------------------- weights
+@dataclass(frozen=True)
+class WeightInfo:
+    """What a part expects of one checkpoint tensor."""
+
+    shape: tuple[int, ...]
+    # "matrix": kept in the run dtype (bfloat16 when serving).
+    # "vector": small per-channel tensor used in 32-bit arithmetic, kept in float32.
+    # "table":  integer table, kept as int32.
+    kind: str = "matrix"
+
+
+@dataclass(frozen=True)
+class PartEnv:
+    hidden_size: int
+    dtype: torch.dtype
+    device: torch.device
+    prefix: str
+
+
+# ----------------------------------------------------------------- cache needs
+@dataclass(frozen=True)
+class KVPagesNeed:
+    """Keys and values in pages.  ``window=None``: every earlier key stays
+    readable; ``window=W``: only the last W positions are ever read."""
+
+    num_kv_heads: int
+    head_dim: int
+    window: int | None = None
+
+
+@dataclass(frozen=True)
+class StateNeed:
+    """A tensor of fixed shape per request, addressed by the request's slot."""
+
+    shape: tuple[int, ...]
+    dtype: torch.dtype = torch.float32
+
+
+# ---------------------------------------------------------------- step context
+@dataclass
+class GroupContext:
+    """What the layers of one cache group need to address their pages."""
+
+    page_size: int
+    block_table: torch.Tensor       # int32 [R, max_pages]; -1 where a page was given back
+    slot_mapping: torch.Tensor      # int32 [T]; page * page_size + offset of each new token
+    max_pages: int
+
+
+@dataclass
+class StepContext:
+    """One batch as the parts see it: T tokens of R requests, flattened request
+    after request.  Built by the step function; parts only read it."""
+
+    num_tokens: int
+    num_requests: int
+    positions: torch.Tensor         # int32 [T] position of each token in its request
+    query_start: torch.Tensor       # int32 [R+1] first token row of each request
+    seq_lens: torch.Tensor          # int32 [R] tokens of each request after this step
+    state_slots: torch.Tensor       # int32 [R] resident slot of each request
+    token_request: torch.Tensor     # int32 [T] request row of each token
+    max_query_len: int
+    max_seq_len: int
+    groups: dict[int, GroupContext] = field(default_factory=dict)
+    # Host copies for parts written in plain tensor code (tests' toy parts).
+    host_query_start: list[int] = field(default_factory=list)
+    host_seq_lens: list[int] = field(default_factory=list)
+    host_state_slots: list[int] = field(default_factory=list)
+
+
+@dataclass
+class CacheView:
+    """The cache one execution of a layer works on.
+
+    ``kind`` is "pages" (``keys``/``values`` are ``[pages, kv_heads, page_size,
+    head_dim]`` views of this entry's slab and ``group`` indexes
+    ``StepContext.groups``), "state" (``state`` is ``[slots, *shape]``) or "none".
+    ``writable`` is False when the cache belongs to another schedule entry.
+    """
+
+    kind: str = "none"
+    group: int = -1
+    keys: torch.Tensor | None = None
+    values: torch.Tensor | None = None
+    state: torch.Tensor | None = None
+    writable: bool = True
+
+
+# ----------------------------------------------------------------------- parts
+class Part:
+    def __init__(self, params: Mapping[str, Any], env: PartEnv) -> None:
+        self.params = params
+        self.env = env
+
+    def expected_weights(self) -> dict[str, WeightInfo]:
+        """Checkpoint names (without the prefix) and what is expected of each."""
+        return {}
+
+    def load_weights(self, tensors: Mapping[str, torch.Tensor]) -> None:
+        """Take the tensors named by :meth:`expected_weights`, already on the
+        device and in the dtype their kind asks for."""
+
+
+class Norm(Part):
+    def forward(self, x: torch.Tensor | None, residual: torch.Tensor, out: torch.Tensor | None = None,
+                rows: torch.Tensor | None = None) -> torch.Tensor:
+        """``residual += x`` (when ``x`` is given) in 32-bit, then return the
+        normalised residual in the run dtype.  With ``rows`` (int32 row indices)
+        only those rows are normalised and returned, and ``residual`` is left
+        unchanged."""
+        raise NotImplementedError
+
+
+class PositionEncoding(Part):
+    """Rotary family: the mixer's fused kernel applies it to queries and keys."""
+
+    rotary_dim: int = 0
+
+    def inverse_frequencies(self) -> torch.Tensor | None:
+        """float32 ``[rotary_dim // 2]`` on the device, or None for no rotation."""
+        return None
+
+
+class Mixer(Part):
+    def __init__(self, params: Mapping[str, Any], env: PartEnv, position: PositionEncoding) -> None:
+        super().__init__(params, env)
+        self.position = position
+
+    def cache_need(self) -> KVPagesNeed | StateNeed | None:
+        return None
+
+    def forward(self, x: torch.Tensor, ctx: StepContext, cache: CacheView) -> torch.Tensor:
+        """``x`` is ``[T, hidden]`` in the run dtype; returns the same shape."""
+        raise NotImplementedError
+
+
+class FeedForward(Part):
+    def forward(self, x: torch.Tensor, ctx: StepContext) -> torch.Tensor:
+        raise NotImplementedError
+
+
+class Block(Part):
+    """Arrangement of two norms, a mixer and a feed-forward around the residual."""
+
+    def __init__(self, params: Mapping[str, Any], env: PartEnv, *, mixer: Mixer, mixer_norm: Norm,
+                 feed_forward: FeedForward, feed_forward_norm: Norm) -> None:
+        super().__init__(params, env)
+        self.mixer, self.mixer_norm = mixer, mixer_norm
+        self.feed_forward, self.feed_forward_norm = feed_forward, feed_forward_norm
+
+    def forward(self, x: torch.Tensor | None, residual: torch.Tensor, ctx: StepContext,
+                cache: CacheView) -> torch.Tensor:
+        """Takes the previous layer's output ``x`` (None for the first layer,
+        whose input already sits in ``residual``) and the float32 residual
+        stream, updated in place; returns this layer's not-yet-added output."""
+        raise NotImplementedError
+
+
+# ------------------------------------------------------------------ registries
+class Registry:
+    def __init__(self, what: str) -> None:
+        self.what = what
+        self._classes: dict[str, Callable[..., Any]] = {}
+
+    def register(self, kind: str) -> Callable[[Callable[..., Any]], Callable[..., Any]]:
+        def decorator(cls: Callable[..., Any]) -> Callable[..., Any]:
+            if kind in self._classes:
+                raise ValueError(f"{self.what} kind {kind!r} is already registered")
+            self._classes[kind] = cls
+            return cls
+        return decorator
+
+    def unregister(self, kind: str) -> None:
+        self._classes.pop(kind, None)
+
+    def get(self, kind: str) -> Callable[..., Any]:
+        try:
+            return self._classes[kind]
+        except KeyError:
+            raise ValueError(f"{self.what} kind {kind!r} is not registered; registered: "
+                             f"{', '.join(sorted(self._classes)) or '(none)'}") from None
+
+    def kinds(self) -> list[str]:
+        return sorted(self._classes)
+
+
+MIXERS = Registry("mixer")
+FEED_FORWARDS = Registry("feed-forward")
+NORMS = Registry("norm")
+POSITION_ENCODINGS = Registry("position encoding")
+BLOCKS = Registry("block")

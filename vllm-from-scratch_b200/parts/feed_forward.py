@@ -1,0 +1,46 @@
+"""Dense gated feed-forward: ``down(silu(gate(x)) * up(x))``, no biases
+(minivllm/models/qwen3.py:44-65).  ``gate`` and ``up`` are held as one matrix
+``[2 I, H]`` with the gate rows first (minivllm/layers/linear.py:261-359), so one
+product serves both."""
+
+from __future__ import annotations
+
+from typing import Any, Mapping
+
+import torch
+
+from .. import kernels
+from .base import FEED_FORWARDS, FeedForward, PartEnv, StepContext, WeightInfo
+
+
+@FEED_FORWARDS.register("gated_silu")
+class GatedSiluFeedForward(FeedForward):
+    """params: ``intermediate_size``."""
+
+    def __init__(self, params: Mapping[str, Any], env: PartEnv) -> None:
+        super().__init__(params, env)
+        self.intermediate_size = int(params["intermediate_size"])
+        self.gate_up: torch.Tensor | None = None
+        self.down: torch.Tensor | None = None
+
+    def expected_weights(self) -> dict[str, WeightInfo]:
+        inter, hidden = self.intermediate_size, self.env.hidden_size
+        return {
+            "gate_proj.weight": WeightInfo((inter, hidden)),
+            "up_proj.weight": WeightInfo((inter, hidden)),
+            "down_proj.weight": WeightInfo((hidden, inter)),
+        }
+
+    def load_weights(self, tensors: Mapping[str, torch.Tensor]) -> None:
+        self.gate_up = torch.cat([tensors["gate_proj.weight"], tensors["up_proj.weight"]], dim=0).contiguous()
+        self.down = tensors["down_proj.weight"].contiguous()
+
+    def forward(self, x: torch.Tensor, ctx: StepContext) -> torch.Tensor:
+        tokens = x.shape[0]
+        gate_up = torch.empty((tokens, 2 * self.intermediate_size), dtype=x.dtype, device=x.device)
+        kernels.gemm(x, self.gate_up, gate_up)
+        hidden = torch.empty((tokens, self.intermediate_size), dtype=x.dtype, device=x.device)
+        kernels.silu_mul(gate_up, hidden)
+        out = torch.empty((tokens, self.env.hidden_size), dtype=x.dtype, device=x.device)
+        kernels.gemm(hidden, self.down, out)
+        return out
