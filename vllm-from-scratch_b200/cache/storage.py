@@ -51,7 +51,8 @@ class CacheStorage:
                 owner_view[index] = CacheView("pages", group, slab[position, 0], slab[position, 1])
         for index, need in enumerate(needs):
             if isinstance(need, StateNeed):
-                state = torch.zeros((max_requests, *need.shape), dtype=need.dtype, device=device)
+                # one spare row past the last slot: padded rows of fixed-shape batches land there
+                state = torch.zeros((max_requests + 1, *need.shape), dtype=need.dtype, device=device)
                 self.states[index] = state
                 owner_view[index] = CacheView("state", state=state)
         self.views: list[CacheView] = []

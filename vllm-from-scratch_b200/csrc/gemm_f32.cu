@@ -16,7 +16,7 @@ constexpr int kTileM = 64, kTileN = 64, kTileK = 16;
 
 __global__ void __launch_bounds__(256) gemm_f32_kernel(const float* __restrict__ x,
                                                        const float* __restrict__ w,
-                                                       float* __restrict__ y, int M, int N, int K) {
+                                                       float* __restrict__ y, int M, int N, int K, int vec_ok) {
     __shared__ __align__(16) float x_s[kTileK][kTileM + 4];
     __shared__ __align__(16) float w_s[kTileK][kTileN + 4];
     const int tid = threadIdx.x;
@@ -31,7 +31,6 @@ __global__ void __launch_bounds__(256) gemm_f32_kernel(const float* __restrict__
     // Loading: 64 rows x 16 k = 1024 elements per operand, 4 per thread.
     const int load_row = tid >> 2;                      // 0..63
     const int load_k = (tid & 3) * 4;                   // 0, 4, 8, 12
-    const bool vec_ok = (K % 4) == 0;
 
     for (int k0 = 0; k0 < K; k0 += kTileK) {
         float xv[4] = {0.f, 0.f, 0.f, 0.f}, wv[4] = {0.f, 0.f, 0.f, 0.f};
@@ -93,7 +92,8 @@ B200_EXPORT int b200_gemm_f32(const float* x, const float* w, float* y, int M, i
     if (M < 0 || N < 0 || K <= 0) return fail("gemm_f32", "sizes must be positive");
     dim3 grid((N + kTileN - 1) / kTileN, (M + kTileM - 1) / kTileM);
     if (grid.y > 65535) return fail("gemm_f32", "more than 65535 * 64 rows in one product");
-    if (((uintptr_t)x | (uintptr_t)w) & 15) return fail("gemm_f32", "operands must be 16-byte aligned");
-    gemm_f32_kernel<<<grid, 256, 0, stream>>>(x, w, y, M, N, K);
+    // 128-bit loads need rows that start on 16-byte boundaries; otherwise scalar loads.
+    const int vec_ok = (K % 4 == 0) && ((((uintptr_t)x | (uintptr_t)w) & 15) == 0);
+    gemm_f32_kernel<<<grid, 256, 0, stream>>>(x, w, y, M, N, K, vec_ok);
     return check_launch("gemm_f32");
 }

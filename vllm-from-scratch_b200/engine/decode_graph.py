@@ -1,0 +1,94 @@
+"""CUDA-graph replay of decode steps.
+
+A step in which every request brings exactly one token has a shape that depends
+only on the number of requests.  For each batch size from a short list the whole
+step (every kernel of the model and the output product) is captured once into a
+CUDA graph over fixed input buffers; later steps of that size copy their packed
+inputs into the buffers and replay the graph: one launch instead of hundreds.
+Batches between two sizes are padded with requests that read and write nothing
+(slot -1, length 0), the scheme of the reference's full graphs for uniform decode
+batches (minivllm/worker/gpu_model_runner.py:1108-1165, 1215-1276, 1415-1477).
+Block tables are captured at their full width (``max_model_len`` positions) and
+kernel launch shapes are chosen for that length, so a replay is valid for any
+context length.
+"""
+
+from __future__ import annotations
+
+import torch
+
+from .runner import ModelRunner
+from .step import StepEntry
+
+CAPTURE_SIZES = (1, 2, 4, 8, 16, 32, 64, 128, 256)
+
+
+class _Captured:
+    def __init__(self, graph, packed, meta, logits) -> None:
+        self.graph, self.packed, self.meta, self.logits = graph, packed, meta, logits
+
+
+class DecodeGraphs:
+    def __init__(self, runner: ModelRunner, max_num_seqs: int, max_model_len: int) -> None:
+        self.runner = runner
+        self.step_function = runner.step_function
+        self.sizes = [size for size in CAPTURE_SIZES if size < max_num_seqs] + [max_num_seqs]
+        self.table_width = -(-max_model_len // runner.storage.page_size)
+        self.max_model_len = max_model_len
+        self._graphs: dict[int, _Captured] = {}
+        self._pool = None
+        self.replays = 0
+
+    def accepts(self, entries: list[StepEntry]) -> bool:
+        return (0 < len(entries) <= self.sizes[-1] and all(len(e.tokens) == 1 for e in entries)
+                and all(e.start + 1 <= self.max_model_len for e in entries))
+
+    def _bucket(self, count: int) -> int:
+        return next(size for size in self.sizes if size >= count)
+
+    def _capture(self, size: int, host: torch.Tensor, meta: dict) -> _Captured:
+        device = self.runner.device
+        packed = torch.empty(host.numel(), dtype=torch.int32, device=device)
+        packed.copy_(host, non_blocking=True)
+        # Launch shapes must hold for every later replay: plan for the longest context.
+        meta = {**meta, "max_seq_len": self.max_model_len}
+        ctx, token_ids, _ = self.step_function.context_from(packed, meta)
+        rows = torch.arange(size, dtype=torch.int32, device=device)
+        model, views = self.runner.model, self.runner.storage.views
+
+        def body() -> torch.Tensor:
+            x, residual = model.forward(token_ids, ctx, views)
+            return model.logits(x, residual, rows)
+
+        stream = torch.cuda.Stream(device=device)
+        stream.wait_stream(torch.cuda.current_stream(device))
+        with torch.cuda.stream(stream):
+            body()                      # warm-up: kernels compiled and loaded before the capture
+        torch.cuda.current_stream(device).wait_stream(stream)
+        torch.cuda.synchronize(device)
+        graph = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(graph, pool=self._pool):
+            logits = body()
+        if self._pool is None:
+            self._pool = graph.pool()
+        return _Captured(graph, packed, meta, logits)
+
+    def run(self, entries: list[StepEntry]) -> torch.Tensor | None:
+        """The same result as ``StepFunction.run`` for a batch of single tokens."""
+        size = self._bucket(len(entries))
+        self.runner.storage.zero_slots(self.runner.manager.take_fresh_slots())
+        # Every row's logits are computed; only the wanted ones are handed back.
+        wanted = [row for row, entry in enumerate(entries) if entry.want]
+        plain = [StepEntry(e.request_id, e.tokens, e.start, []) for e in entries]
+        host, meta = self.step_function.pack_host(plain, pad_requests=size, table_width=self.table_width)
+        captured = self._graphs.get(size)
+        if captured is None:
+            captured = self._graphs[size] = self._capture(size, host, meta)
+        captured.packed.copy_(host, non_blocking=True)
+        captured.graph.replay()
+        self.replays += 1
+        if not wanted:
+            return None
+        if len(wanted) == len(entries):
+            return captured.logits[:len(entries)]
+        return captured.logits[torch.tensor(wanted, device=captured.logits.device)]

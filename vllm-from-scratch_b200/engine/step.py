@@ -46,20 +46,28 @@ class StepFunction:
         self.last_context: StepContext | None = None     # kept for the packed-inputs trace
 
     # ------------------------------------------------------------------ packing
-    def pack(self, entries: list[StepEntry]) -> tuple[StepContext, torch.Tensor, torch.Tensor, int]:
-        """Build the device-side description of the batch.  Returns the context,
-        the token ids, the wanted rows and their number."""
+    def pack_host(self, entries: list[StepEntry], pad_requests: int | None = None,
+                  table_width: int | None = None) -> tuple[torch.Tensor, dict]:
+        """Describe the batch in one pinned int32 buffer.  ``pad_requests`` adds
+        requests of one token that read and write nothing (for shapes fixed in
+        advance); ``table_width`` fixes the width of the block tables."""
         page_size = self.page_size
-        num_requests = len(entries)
-        lengths = [len(entry.tokens) for entry in entries]
+        real = len(entries)
+        num_requests = max(real, pad_requests or 0)
+        padding = num_requests - real
+        lengths = [len(entry.tokens) for entry in entries] + [1] * padding
         num_tokens = sum(lengths)
         query_start = np.zeros(num_requests + 1, dtype=np.int32)
         np.cumsum(lengths, out=query_start[1:])
-        seq_lens = np.array([entry.start + n for entry, n in zip(entries, lengths)], dtype=np.int32)
-        slots = np.array([self.manager.slot(entry.request_id) for entry in entries], dtype=np.int32)
-        token_ids = np.concatenate([np.asarray(entry.tokens, dtype=np.int32) for entry in entries])
-        positions = np.concatenate([np.arange(entry.start, entry.start + n, dtype=np.int32)
-                                    for entry, n in zip(entries, lengths)])
+        seq_lens = np.array([entry.start + len(entry.tokens) for entry in entries] + [0] * padding,
+                            dtype=np.int32)
+        # Padded requests use the spare state slot past the last real one.
+        slots = np.array([self.manager.slot(entry.request_id) for entry in entries]
+                         + [self.storage.max_requests] * padding, dtype=np.int32)
+        zeros = np.zeros(padding, dtype=np.int32)
+        token_ids = np.concatenate([np.asarray(entry.tokens, dtype=np.int32) for entry in entries] + [zeros])
+        positions = np.concatenate([np.arange(entry.start, entry.start + len(entry.tokens), dtype=np.int32)
+                                    for entry in entries] + [zeros])
         token_request = np.repeat(np.arange(num_requests, dtype=np.int32), lengths)
         want_rows: list[int] = []
         for row, entry in enumerate(entries):
@@ -71,43 +79,58 @@ class StepFunction:
         want = np.asarray(want_rows, dtype=np.int32)
 
         pieces = [token_ids, positions, token_request, query_start, seq_lens, slots, want]
-        group_shapes = []
+        widths = []
+        real_tokens = int(query_start[real])
         for group in range(len(self.storage.groups)):
             tables = [self.manager.block_table(entry.request_id, group) for entry in entries]
-            needed = [-(-int(total) // page_size) for total in seq_lens]
+            needed = [-(-int(total) // page_size) for total in seq_lens[:real]]
             for entry, table, pages in zip(entries, tables, needed):
                 if len(table) < pages:
                     raise ValueError(
                         f"request {entry.request_id!r} holds {len(table)} pages in group {group} but "
                         f"this step reaches position {pages * page_size - 1}: allocate before the step")
-            width = max(needed)
+            width = max(needed) if table_width is None else table_width
+            if width < max(needed):
+                raise ValueError(f"block table width {width} is too small for {max(needed)} pages")
             block_table = np.full((num_requests, width), RELEASED, dtype=np.int32)
             for row, (table, pages) in enumerate(zip(tables, needed)):
                 block_table[row, :pages] = table[:pages]
-            page_of_token = block_table[token_request, positions // page_size]
-            if num_tokens and int(page_of_token.min()) < 0:
+            slot_mapping = np.full(num_tokens, -1, dtype=np.int32)
+            page_of_token = block_table[token_request[:real_tokens], positions[:real_tokens] // page_size]
+            if real_tokens and int(page_of_token.min()) < 0:
                 bad = int(np.argmin(page_of_token))
                 raise ValueError(f"token row {bad} would be written to a page that was given back")
-            slot_mapping = (page_of_token * page_size + positions % page_size).astype(np.int32)
+            slot_mapping[:real_tokens] = page_of_token * page_size + positions[:real_tokens] % page_size
             pieces += [slot_mapping, block_table.reshape(-1)]
-            group_shapes.append(width)
+            widths.append(width)
 
         sizes = [piece.size for piece in pieces]
         host = torch.empty(sum(sizes), dtype=torch.int32, pin_memory=self.device.type == "cuda")
         np.concatenate(pieces, out=host.numpy())
-        packed = host.to(self.device, non_blocking=True)
-        parts = list(torch.split(packed, sizes))
+        meta = {
+            "sizes": sizes, "widths": widths, "num_tokens": num_tokens, "num_requests": num_requests,
+            "num_wanted": len(want_rows), "max_query_len": max(lengths),
+            "max_seq_len": int(seq_lens.max()), "query_start": query_start.tolist(),
+            "seq_lens": seq_lens.tolist(), "slots": slots.tolist(),
+        }
+        return host, meta
+
+    def context_from(self, packed: torch.Tensor, meta: dict
+                     ) -> tuple[StepContext, torch.Tensor, torch.Tensor]:
+        """Views into the device copy of a packed buffer: context, token ids, wanted rows."""
+        parts = list(torch.split(packed, meta["sizes"]))
         ids_d, pos_d, req_d, start_d, lens_d, slots_d, want_d = parts[:7]
         ctx = StepContext(
-            num_tokens=num_tokens, num_requests=num_requests, positions=pos_d, query_start=start_d,
-            seq_lens=lens_d, state_slots=slots_d, token_request=req_d,
-            max_query_len=max(lengths), max_seq_len=int(seq_lens.max()),
-            host_query_start=query_start.tolist(), host_seq_lens=seq_lens.tolist(),
-            host_state_slots=slots.tolist())
-        for group, width in enumerate(group_shapes):
+            num_tokens=meta["num_tokens"], num_requests=meta["num_requests"], positions=pos_d,
+            query_start=start_d, seq_lens=lens_d, state_slots=slots_d, token_request=req_d,
+            max_query_len=meta["max_query_len"], max_seq_len=meta["max_seq_len"],
+            host_query_start=meta["query_start"], host_seq_lens=meta["seq_lens"],
+            host_state_slots=meta["slots"])
+        for group, width in enumerate(meta["widths"]):
             slot_d, table_d = parts[7 + 2 * group], parts[8 + 2 * group]
-            ctx.groups[group] = GroupContext(page_size, table_d.view(num_requests, width), slot_d, width)
-        return ctx, ids_d, want_d, len(want_rows)
+            ctx.groups[group] = GroupContext(self.page_size, table_d.view(meta["num_requests"], width),
+                                             slot_d, width)
+        return ctx, ids_d, want_d
 
     # ---------------------------------------------------------------------- run
     def run(self, entries: list[StepEntry]) -> torch.Tensor | None:
@@ -120,9 +143,10 @@ class StepFunction:
             if entry.start < 0:
                 raise ValueError(f"request {entry.request_id!r}: negative start position")
         self.storage.zero_slots(self.manager.take_fresh_slots())
-        ctx, token_ids, want_rows, num_wanted = self.pack(entries)
+        host, meta = self.pack_host(entries)
+        ctx, token_ids, want_rows = self.context_from(host.to(self.device, non_blocking=True), meta)
         self.last_context = ctx
         x, residual = self.model.forward(token_ids, ctx, self.storage.views)
-        if num_wanted == 0:
+        if meta["num_wanted"] == 0:
             return None
         return self.model.logits(x, residual, want_rows)

@@ -186,3 +186,50 @@ def paged_attention(q: torch.Tensor, k_pages: torch.Tensor, v_pages: torch.Tenso
          *(_P(a) for a in args_checked),
          _I(requests), _I(tokens), _I(block_table.shape[1]), _I(num_q_heads), _I(num_kv_heads),
          _I(head_dim), _I(page_size), _F(scale), _I(window or 0), _I(_code(dtype)), _stream())
+
+
+# --------------------------------------------------------------------- sampling
+_U64 = ctypes.c_uint64
+
+
+def sample(logits: torch.Tensor, temperature: torch.Tensor, top_k: torch.Tensor, top_p: torch.Tensor,
+           min_p: torch.Tensor, seeds: torch.Tensor, draw_index: torch.Tensor, tokens: torch.Tensor,
+           greedy_eps: float) -> None:
+    """One token per row of float32 ``logits``: argmax where ``temperature`` is
+    below ``greedy_eps``, otherwise temperature, min-p, top-k, top-p and a seeded
+    draw keyed by ``(seeds[r], draw_index[r], token id)``."""
+    rows, vocab = logits.shape
+    _run("sampling", "b200_sample",
+         _P(_check("logits", logits, torch.float32)), _I(rows), _I(vocab),
+         _P(_check("temperature", temperature, torch.float32, (rows,))),
+         _P(_check("top_k", top_k, torch.int32, (rows,))),
+         _P(_check("top_p", top_p, torch.float32, (rows,))),
+         _P(_check("min_p", min_p, torch.float32, (rows,))),
+         _P(_check("seeds", seeds, torch.int64, (rows,))),
+         _P(_check("draw index", draw_index, torch.int64, (rows,))),
+         _P(_check("sampled tokens", tokens, torch.int32, (rows,))), _F(greedy_eps), _stream())
+
+
+def apply_penalties(logits: torch.Tensor, offsets: torch.Tensor, seen_tokens: torch.Tensor,
+                    output_counts: torch.Tensor, repetition: torch.Tensor, frequency: torch.Tensor,
+                    presence: torch.Tensor) -> None:
+    """In place: for row r and each distinct seen token ``seen_tokens[offsets[r]:
+    offsets[r + 1]]`` apply the repetition, frequency and presence penalties."""
+    rows, vocab = logits.shape
+    _run("sampling", "b200_penalties",
+         _P(_check("logits", logits, torch.float32)), _I(rows), _I(vocab),
+         _P(_check("offsets", offsets, torch.int32, (rows + 1,))),
+         _P(_check("seen tokens", seen_tokens, torch.int32)),
+         _P(_check("output counts", output_counts, torch.int32, tuple(seen_tokens.shape))),
+         _P(_check("repetition", repetition, torch.float32, (rows,))),
+         _P(_check("frequency", frequency, torch.float32, (rows,))),
+         _P(_check("presence", presence, torch.float32, (rows,))), _stream())
+
+
+def mask_tokens(logits: torch.Tensor, rows: torch.Tensor, tokens: torch.Tensor) -> None:
+    """In place: ``logits[rows[i], tokens[i]] = -inf``."""
+    count = rows.shape[0]
+    _run("sampling", "b200_mask_tokens",
+         _P(_check("logits", logits, torch.float32)), _I(logits.shape[1]),
+         _P(_check("rows", rows, torch.int32, (count,))), _P(_check("tokens", tokens, torch.int32, (count,))),
+         _I(count), _stream())

@@ -8,6 +8,10 @@ from __future__ import annotations
 
 import torch
 
+# Partial sums of a product split along K stay in float32: the library must not
+# add them up in bfloat16.
+torch.backends.cuda.matmul.allow_bf16_reduced_precision_reduction = False
+
 
 def gemm_bf16(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor) -> None:
     if out.dtype == torch.bfloat16:

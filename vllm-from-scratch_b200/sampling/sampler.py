@@ -1,0 +1,87 @@
+"""From a step's logits to one token per request.
+
+Order of operations as in the reference's sampler (minivllm/sample/sampler.py:
+73-120, 243-288): float32 logits -> penalties -> stop tokens masked while a
+request is below ``min_tokens`` -> greedy rows take the argmax (never divided by
+the temperature), the other rows are scaled by their temperature, filtered by
+min-p, top-k and top-p and drawn.  The draw is keyed by the request's seed and by
+how many tokens it has generated, so a request's tokens do not depend on what
+else is in the batch or on the order of calls (the scheme of minivllm/worker/gpu/
+sample/gumbel.py:94-131).
+"""
+
+from __future__ import annotations
+
+from collections import Counter
+from typing import Sequence
+
+import numpy as np
+import torch
+
+from .. import kernels
+from .params import GREEDY_EPS, SamplingParams
+
+
+class Sampler:
+    def __init__(self, vocab_size: int, device: torch.device | str) -> None:
+        self.vocab_size = vocab_size
+        self.device = torch.device(device)
+
+    def _to_device(self, array: np.ndarray) -> torch.Tensor:
+        return torch.from_numpy(array).to(self.device, non_blocking=True)
+
+    def sample(self, logits: torch.Tensor, params: Sequence[SamplingParams], seeds: Sequence[int],
+               prompts: Sequence[Sequence[int]], outputs: Sequence[Sequence[int]]) -> list[int]:
+        """``logits`` is ``[rows, vocab]`` float32 on the device (changed in place by
+        penalties and masks); the other arguments have one entry per row."""
+        tokens = self.sample_device(logits, params, seeds, prompts, outputs)
+        return tokens.tolist()
+
+    def sample_device(self, logits, params, seeds, prompts, outputs) -> torch.Tensor:
+        rows = logits.shape[0]
+        if rows != len(params):
+            raise ValueError(f"{rows} rows of logits for {len(params)} requests")
+        self._penalties(logits, params, prompts, outputs)
+        self._min_tokens(logits, params, outputs)
+        temperature = np.array([p.temperature for p in params], dtype=np.float32)
+        top_k = np.array([p.top_k if p.top_k > 0 else 0 for p in params], dtype=np.int32)
+        top_p = np.array([p.top_p for p in params], dtype=np.float32)
+        min_p = np.array([p.min_p for p in params], dtype=np.float32)
+        seed = np.array([s & 0x7FFFFFFFFFFFFFFF for s in seeds], dtype=np.int64)
+        draw = np.array([len(o) for o in outputs], dtype=np.int64)
+        tokens = torch.empty(rows, dtype=torch.int32, device=logits.device)
+        kernels.sample(logits, self._to_device(temperature), self._to_device(top_k),
+                       self._to_device(top_p), self._to_device(min_p), self._to_device(seed),
+                       self._to_device(draw), tokens, GREEDY_EPS)
+        return tokens
+
+    def _penalties(self, logits, params, prompts, outputs) -> None:
+        if not any(p.has_penalties for p in params):
+            return
+        offsets, seen, counts = [0], [], []
+        for p, prompt, output in zip(params, prompts, outputs):
+            if p.has_penalties:
+                in_output = Counter(output)
+                for token in sorted(set(prompt) | set(in_output)):
+                    seen.append(token)
+                    counts.append(in_output.get(token, 0))
+            offsets.append(len(seen))
+        if not seen:
+            return
+        kernels.apply_penalties(
+            logits, self._to_device(np.array(offsets, dtype=np.int32)),
+            self._to_device(np.array(seen, dtype=np.int32)), self._to_device(np.array(counts, dtype=np.int32)),
+            self._to_device(np.array([p.repetition_penalty for p in params], dtype=np.float32)),
+            self._to_device(np.array([p.frequency_penalty for p in params], dtype=np.float32)),
+            self._to_device(np.array([p.presence_penalty for p in params], dtype=np.float32)))
+
+    def _min_tokens(self, logits, params, outputs) -> None:
+        rows, tokens = [], []
+        for row, (p, output) in enumerate(zip(params, outputs)):
+            if len(output) < p.min_tokens:
+                for token in sorted(p.all_stop_token_ids):
+                    rows.append(row)
+                    tokens.append(token)
+        if rows:
+            kernels.mask_tokens(logits, self._to_device(np.array(rows, dtype=np.int32)),
+                                self._to_device(np.array(tokens, dtype=np.int32)))
