@@ -1,0 +1,135 @@
+"""The sampling kernels against the reference's formulas written in plain tensor
+code (minivllm/sample/ops/topk_topp_sampler.py:48-90, minivllm/sample/sampler.py:
+290-303, minivllm/sample/ops/penalties.py:51-72)."""
+
+from __future__ import annotations
+
+import pytest
+import torch
+
+pytestmark = pytest.mark.gpu
+
+
+def plain_keep_mask(logits, temperature, top_k, top_p, min_p):
+    """Which tokens survive temperature -> min_p -> top-k -> top-p, one row."""
+    x = logits.double() / temperature
+    keep = torch.ones_like(x, dtype=torch.bool)
+    if min_p > 0:
+        probs = torch.softmax(x, dim=-1)
+        keep &= probs >= probs.max() * min_p
+        x = x.masked_fill(~keep, float("-inf"))
+    if top_k > 0 and top_k < x.numel():
+        kth = torch.topk(x, top_k).values[-1]
+        keep &= x >= kth
+        x = x.masked_fill(~keep, float("-inf"))
+    if top_p < 1.0:
+        order = torch.argsort(x)                       # ascending
+        probs = torch.softmax(x, dim=-1)[order]
+        drop = torch.cumsum(probs, dim=-1) <= 1 - top_p
+        drop[-1] = False
+        keep[order[drop]] = False
+    return keep
+
+
+def draw(logits_row, n, temperature, top_k=0, top_p=1.0, min_p=0.0, seed0=0):
+    import vllm_from_scratch_b200.kernels as k
+    vocab = logits_row.numel()
+    logits = logits_row.float().cuda().unsqueeze(0).repeat(n, 1).contiguous()
+    f = lambda v, dt: torch.full((n,), v, dtype=dt, device="cuda")
+    seeds = torch.arange(seed0, seed0 + n, dtype=torch.int64, device="cuda")
+    index = torch.arange(n, dtype=torch.int64, device="cuda") % 7
+    out = torch.empty(n, dtype=torch.int32, device="cuda")
+    k.sample(logits, f(temperature, torch.float32), f(top_k, torch.int32), f(top_p, torch.float32),
+             f(min_p, torch.float32), seeds, index, out, 1e-5)
+    return out.cpu().long()
+
+
+@pytest.mark.parametrize("vocab", [256, 503, 151936])
+def test_greedy_is_first_argmax(vocab):
+    g = torch.Generator().manual_seed(vocab)
+    row = torch.randn(vocab, generator=g)
+    row[vocab // 3] = row[vocab // 2] = row.max() + 1.0       # a tie: the first index wins
+    tokens = draw(row, 3, temperature=0.0)
+    assert tokens.tolist() == [vocab // 3] * 3
+
+
+@pytest.mark.parametrize("temperature,top_k,top_p,min_p", [
+    (1.0, 5, 1.0, 0.0), (0.7, 0, 0.9, 0.0), (1.3, 0, 1.0, 0.05), (0.8, 20, 0.8, 0.01), (1.0, 1, 1.0, 0.0),
+    (1.0, 0, 0.3, 0.0),
+])
+def test_filters_keep_the_reference_set(temperature, top_k, top_p, min_p):
+    g = torch.Generator().manual_seed(7)
+    row = torch.randn(503, generator=g) * 2.0
+    keep = plain_keep_mask(row, temperature, top_k, top_p, min_p)
+    tokens = draw(row, 4096, temperature, top_k, top_p, min_p)
+    assert bool(keep[tokens].all()), "a token outside the reference's candidate set was drawn"
+    kept = int(keep.sum())
+    if kept <= 8:
+        assert set(tokens.tolist()) == set(keep.nonzero().flatten().tolist())
+
+
+def test_distribution_follows_softmax():
+    g = torch.Generator().manual_seed(3)
+    row = torch.randn(311, generator=g) * 1.5
+    n = 1 << 16
+    tokens = draw(row, n, temperature=0.9)
+    expected = torch.softmax(row.double() / 0.9, dim=-1)
+    counts = torch.bincount(tokens, minlength=311).double()
+    sigma = torch.sqrt(expected * (1 - expected) * n)
+    z = (counts - expected * n).abs() / sigma.clamp(min=1.0)
+    assert float(z.max()) < 5.0, f"worst deviation {float(z.max()):.2f} sigma"
+
+
+def test_same_key_same_token_and_large_vocabulary():
+    g = torch.Generator().manual_seed(1)
+    row = torch.randn(151936, generator=g) * 3
+    a = draw(row, 64, temperature=1.0, top_k=50, top_p=0.95)
+    b = draw(row, 64, temperature=1.0, top_k=50, top_p=0.95)
+    assert torch.equal(a, b)
+    assert len(set(a.tolist())) > 3
+    keep = plain_keep_mask(row, 1.0, 50, 0.95, 0.0)
+    assert bool(keep[a].all())
+
+
+def test_penalties_and_masks_follow_the_formula():
+    import vllm_from_scratch_b200.kernels as k
+    vocab = 503
+    g = torch.Generator().manual_seed(5)
+    logits = torch.randn(3, vocab, generator=g)
+    prompts = [[1, 2, 2, 400], [5], [7, 8]]
+    outputs = [[2, 9, 9, 9], [], [8, 8, 502]]
+    rep, freq, pres = [1.3, 1.0, 0.7], [0.2, 0.0, 0.5], [0.1, 0.0, 0.4]
+    expected = logits.clone()
+    for r in range(3):
+        seen = set(prompts[r]) | set(outputs[r])
+        for t in seen:
+            v = expected[r, t]
+            expected[r, t] = v / rep[r] if v > 0 else v * rep[r]
+        for t in set(outputs[r]):
+            expected[r, t] -= freq[r] * outputs[r].count(t) + pres[r]
+    offsets, seen_tokens, counts = [0], [], []
+    for r in range(3):
+        for t in sorted(set(prompts[r]) | set(outputs[r])):
+            seen_tokens.append(t)
+            counts.append(outputs[r].count(t))
+        offsets.append(len(seen_tokens))
+    device = logits.cuda()
+    i32 = lambda v: torch.tensor(v, dtype=torch.int32, device="cuda")
+    f32 = lambda v: torch.tensor(v, dtype=torch.float32, device="cuda")
+    k.apply_penalties(device, i32(offsets), i32(seen_tokens), i32(counts), f32(rep), f32(freq), f32(pres))
+    assert torch.allclose(device.cpu(), expected, atol=1e-6)
+    k.mask_tokens(device, i32([0, 2]), i32([17, 502]))
+    assert device[0, 17] == float("-inf") and device[2, 502] == float("-inf")
+    assert torch.isfinite(device[1]).all()
+
+
+def test_min_tokens_masks_stop_ids_even_for_greedy_rows():
+    import vllm_from_scratch_b200 as engine
+    sampler = engine.Sampler(64, "cuda")
+    logits = torch.zeros(2, 64, device="cuda")
+    logits[:, 10] = 5.0
+    logits[:, 11] = 4.0
+    params = [engine.SamplingParams(temperature=0.0, min_tokens=3, max_tokens=8, eos_token_id=10),
+              engine.SamplingParams(temperature=0.0, min_tokens=0, max_tokens=8, eos_token_id=10)]
+    tokens = sampler.sample(logits, params, [1, 2], [[1], [1]], [[], []])
+    assert tokens == [11, 10]

@@ -24,8 +24,11 @@ CAPTURE_SIZES = (1, 2, 4, 8, 16, 32, 64, 128, 256)
 
 
 class _Captured:
-    def __init__(self, graph, packed, meta, logits) -> None:
+    def __init__(self, graph, packed, meta, logits, keep_alive) -> None:
         self.graph, self.packed, self.meta, self.logits = graph, packed, meta, logits
+        # The graph holds raw addresses only: every tensor its kernels read must
+        # outlive it.
+        self.keep_alive = keep_alive
 
 
 class DecodeGraphs:
@@ -38,6 +41,7 @@ class DecodeGraphs:
         self._graphs: dict[int, _Captured] = {}
         self._pool = None
         self.replays = 0
+        self.last_h2d_bytes = 0
 
     def accepts(self, entries: list[StepEntry]) -> bool:
         return (0 < len(entries) <= self.sizes[-1] and all(len(e.tokens) == 1 for e in entries)
@@ -71,7 +75,7 @@ class DecodeGraphs:
             logits = body()
         if self._pool is None:
             self._pool = graph.pool()
-        return _Captured(graph, packed, meta, logits)
+        return _Captured(graph, packed, meta, logits, (rows, ctx, token_ids))
 
     def run(self, entries: list[StepEntry]) -> torch.Tensor | None:
         """The same result as ``StepFunction.run`` for a batch of single tokens."""
@@ -85,6 +89,7 @@ class DecodeGraphs:
         if captured is None:
             captured = self._graphs[size] = self._capture(size, host, meta)
         captured.packed.copy_(host, non_blocking=True)
+        self.last_h2d_bytes = host.numel() * host.element_size()
         captured.graph.replay()
         self.replays += 1
         if not wanted:

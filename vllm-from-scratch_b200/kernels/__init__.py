@@ -57,7 +57,12 @@ def _stream() -> ctypes.c_void_p:
     return ctypes.c_void_p(torch.cuda.current_stream().cuda_stream)
 
 
+launch_count = 0        # kernel launchers called so far (the benchmark reports the difference)
+
+
 def _run(library: str, symbol: str, *args) -> None:
+    global launch_count
+    launch_count += 1
     lib = load_library(library)
     status = getattr(lib, symbol)(*args)
     if status != 0:

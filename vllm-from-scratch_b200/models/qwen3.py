@@ -48,21 +48,26 @@ def build_spec(config: Qwen3Config) -> ModelSpec:
 
 
 def random_weights(config: Qwen3Config, seed: int, *, std: float | None = None, norm_std: float = 0.1,
-                   dtype: torch.dtype = torch.bfloat16) -> dict[str, torch.Tensor]:
+                   dtype: torch.dtype = torch.bfloat16, device: str | torch.device = "cpu"
+                   ) -> dict[str, torch.Tensor]:
     """Seeded random tensors under the checkpoint's names: matrices and the
     embedding ``N(0, std)`` (``std`` defaults to the configuration's
     ``initializer_range``), norm weights ``1 + N(0, norm_std)``.  The reference's
     generator draws the matrices the same way and sets norm weights to one
     (minivllm/testing/tiny_models.py:811-850); weights of exactly one would hide a
-    misplaced norm weight, hence the spread."""
+    misplaced norm weight, hence the spread.  ``device`` says where the tensors are
+    drawn (a CUDA device draws a large model in seconds; the values then differ from
+    the CPU's for the same seed)."""
     std = config.initializer_range if std is None else std
-    generator = torch.Generator().manual_seed(seed)
+    generator = torch.Generator(device=device).manual_seed(seed)
 
     def matrix(*shape: int) -> torch.Tensor:
-        return torch.empty(*shape, dtype=torch.float32).normal_(0.0, std, generator=generator).to(dtype)
+        return torch.empty(*shape, dtype=torch.float32, device=device).normal_(
+            0.0, std, generator=generator).to(dtype)
 
     def norm(size: int) -> torch.Tensor:
-        return (1.0 + torch.empty(size, dtype=torch.float32).normal_(0.0, norm_std, generator=generator)).to(dtype)
+        return (1.0 + torch.empty(size, dtype=torch.float32, device=device).normal_(
+            0.0, norm_std, generator=generator)).to(dtype)
 
     hidden, inter, d = config.hidden_size, config.intermediate_size, config.head_dim
     weights = {"model.embed_tokens.weight": matrix(config.vocab_size, hidden)}
