@@ -225,3 +225,51 @@ def test_attention_window_edge_and_released_pages(dtype):
     assert torch.equal(outs[0], outs[1]), "released pages must not matter"
     edge_value = vp[int(table[0, 31 // page]), 0, 31 % page].float()
     assert float((outs[0].view(nq, d)[0].float() - edge_value).abs().max()) < 0.05, "edge key must dominate"
+
+
+TENSOR_CORE_SHAPES = [
+    # nq, nkv, d, page, q_lens, seq_lens, window      (decode: every q_len is 1)
+    (16, 8, 128, 16, [1, 1, 1], [700, 64, 2900], None),
+    (16, 8, 128, 16, [1], [5000], None),
+    (32, 8, 128, 16, [1, 1], [1, 333], None),
+    (64, 8, 128, 32, [1, 1, 1, 1, 1], [17, 300, 1000, 64, 65], None),
+    (4, 4, 64, 8, [1, 1], [100, 3000], 700),
+    (4, 1, 256, 16, [1, 1], [50, 600], None),
+    (16, 8, 128, 16, [200, 1, 64, 3], [200, 500, 300, 131], None),
+    (8, 2, 64, 16, [130, 70], [130, 1000], None),
+    (6, 3, 128, 16, [300], [1500], 256),
+    (2, 1, 256, 8, [65, 1], [65, 90], None),
+]
+
+
+@pytest.mark.parametrize("shape", TENSOR_CORE_SHAPES)
+def test_tensor_core_attention(shape):
+    """The bfloat16 tensor-core kernels (decode with split keys, and the general one)
+    against the plain reference, with and without a key that must dominate."""
+    k = kernels()
+    from vllm_from_scratch_b200.kernels import attention_bf16
+    nq, nkv, d, page, q_lens, seq_lens, window = shape
+    for standout in (False, True):
+        q, kp, vp, start, seq, table = _attention_case(torch.bfloat16, nq, nkv, d, page, q_lens, seq_lens,
+                                                       window, seed=nq + d + page, standout=standout)
+        out_a = torch.zeros_like(q)
+        out_b = torch.zeros_like(q)
+        args = (start, seq, table, nq, nkv, d, page, d ** -0.5, window, max(q_lens), max(seq_lens))
+        assert attention_bf16.paged_attention_bf16(q, kp, vp, out_a, *args), "shape must take the fast path"
+        plain_ops.paged_attention(q, kp, vp, out_b, *args)
+        close(out_a, out_b, torch.bfloat16, scale=2, what=f"tensor-core attention standout={standout}")
+
+
+def test_decode_attention_same_for_any_split():
+    """The number of splits is a launch detail: planning for a longer context
+    (more splits) must give the same result beyond rounding."""
+    from vllm_from_scratch_b200.kernels import attention_bf16
+    nq, nkv, d, page = 16, 8, 128, 16
+    q, kp, vp, start, seq, table = _attention_case(torch.bfloat16, nq, nkv, d, page, [1, 1], [900, 77], None, seed=4)
+    outs = []
+    for planned in (900, 40000):
+        out = torch.zeros_like(q)
+        assert attention_bf16.paged_attention_bf16(q, kp, vp, out, start, seq, table, nq, nkv, d, page,
+                                                   d ** -0.5, None, 1, planned)
+        outs.append(out.float())
+    assert float((outs[0] - outs[1]).abs().max()) < 8e-3

@@ -60,9 +60,13 @@ def _stream() -> ctypes.c_void_p:
 launch_count = 0        # kernel launchers called so far (the benchmark reports the difference)
 
 
-def _run(library: str, symbol: str, *args) -> None:
+def count_launch(count: int = 1) -> None:
     global launch_count
-    launch_count += 1
+    launch_count += count
+
+
+def _run(library: str, symbol: str, *args) -> None:
+    count_launch()
     lib = load_library(library)
     status = getattr(lib, symbol)(*args)
     if status != 0:

@@ -1,16 +1,61 @@
 """Tensor-core attention kernels of the bfloat16 run mode.
 
 ``paged_attention_bf16`` returns True when it ran a kernel and False when the
-shape is one these kernels refuse; the caller then uses the float32-arithmetic
-kernel, which takes every shape.
+shape is one these kernels refuse (head sizes other than 64, 128, 256, or more
+than 16 query heads per key/value head); the caller then uses the
+float32-arithmetic kernel, which takes every shape.
 """
 
 from __future__ import annotations
 
+import ctypes
+
 import torch
+
+from ..csrc.build import load_library
+
+NUM_SMS = 148
+_P, _I, _F = ctypes.c_void_p, ctypes.c_int, ctypes.c_float
+
+
+def decode_splits(num_requests: int, num_kv_heads: int, max_seq_len: int) -> int:
+    """Over how many blocks the keys of one (request, key/value head) are split:
+    enough blocks to fill the GPU a few times over, each with at least 256 keys."""
+    pairs = max(1, num_requests * num_kv_heads)
+    wanted = -(-4 * NUM_SMS // pairs)
+    by_length = max(1, max_seq_len // 256)
+    return max(1, min(wanted, by_length, 64))
 
 
 def paged_attention_bf16(q, k_pages, v_pages, out, query_start, seq_lens, block_table, num_q_heads,
                          num_kv_heads, head_dim, page_size, scale, window, max_query_len,
                          max_seq_len) -> bool:
-    return False
+    lib = load_library("attention_bf16")
+    if not lib.b200_attention_bf16_supports(num_q_heads, num_kv_heads, head_dim):
+        return False
+    from . import KernelError, _stream
+    requests = seq_lens.shape[0]
+    tokens = q.shape[0]
+    if max_query_len == 1 and tokens == requests:
+        splits = decode_splits(requests, num_kv_heads, max_seq_len)
+        partial_o = partial_ml = None
+        if splits > 1:
+            partial_o = torch.empty((tokens * num_q_heads * splits, head_dim), dtype=torch.float32, device=q.device)
+            partial_ml = torch.empty((tokens * num_q_heads * splits, 2), dtype=torch.float32, device=q.device)
+        status = lib.b200_decode_attention_bf16(
+            _P(q.data_ptr()), _P(k_pages.data_ptr()), _P(v_pages.data_ptr()), _P(out.data_ptr()),
+            _P(partial_o.data_ptr() if splits > 1 else 0), _P(partial_ml.data_ptr() if splits > 1 else 0),
+            _P(seq_lens.data_ptr()), _P(block_table.data_ptr()), _I(requests), _I(block_table.shape[1]),
+            _I(num_q_heads), _I(num_kv_heads), _I(head_dim), _I(page_size), _F(scale), _I(window or 0),
+            _I(splits), _stream())
+    else:
+        status = lib.b200_prefill_attention_bf16(
+            _P(q.data_ptr()), _P(k_pages.data_ptr()), _P(v_pages.data_ptr()), _P(out.data_ptr()),
+            _P(query_start.data_ptr()), _P(seq_lens.data_ptr()), _P(block_table.data_ptr()), _I(requests),
+            _I(tokens), _I(block_table.shape[1]), _I(num_q_heads), _I(num_kv_heads), _I(head_dim),
+            _I(page_size), _F(scale), _I(window or 0), _stream())
+    if status != 0:
+        raise KernelError(lib.b200_last_error().decode())
+    from . import count_launch
+    count_launch()
+    return True
