@@ -32,7 +32,7 @@ EXTRA_FLAGS: dict[str, list[str]] = {
     "gemm_bf16": ["-lcuda"],
 }
 LIBRARIES = ("norm", "rope_cache", "attention_generic", "gemm_f32", "attention_bf16", "gemm_bf16",
-             "sampling")
+             "sampling", "decode_attention_static")
 
 _loaded: dict[str, ctypes.CDLL] = {}
 _lock = threading.Lock()
@@ -78,7 +78,7 @@ def _build_dir() -> Path:
 def _digest(name: str) -> str:
     h = hashlib.sha256()
     h.update((SOURCE_DIR / f"{name}.cu").read_bytes())
-    for header in sorted(SOURCE_DIR.glob("*.cuh")):
+    for header in sorted([*SOURCE_DIR.glob("*.cuh"), *SOURCE_DIR.glob("*.h")]):
         h.update(header.read_bytes())
     h.update(" ".join(_flags(name)).encode())
     return h.hexdigest()[:16]
