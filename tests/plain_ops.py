@@ -111,3 +111,17 @@ def patch(monkeypatch) -> None:
     import vllm_from_scratch_b200.kernels as kernels
     for name in ALL:
         monkeypatch.setattr(kernels, name, globals()[name])
+
+
+def sample(logits, temperature, top_k, top_p, min_p, seeds, draw_index, tokens, greedy_eps):
+    """Greedy rows only: enough to drive the engine on the CPU."""
+    if bool((temperature >= greedy_eps).any()):
+        raise NotImplementedError("the plain stand-in samples greedily only")
+    tokens.copy_(logits.argmax(dim=-1).to(tokens.dtype))
+
+
+def mask_tokens(logits, rows, tokens):
+    logits[rows.long(), tokens.long()] = float("-inf")
+
+
+ALL = ALL + ("sample", "mask_tokens")

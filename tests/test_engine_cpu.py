@@ -1,0 +1,104 @@
+"""The engine's host-side logic on a machine without a GPU: the kernels are
+replaced by their plain stand-ins (tests/plain_ops.py), everything else is the
+engine's own code: packing, cache, scheduler, engine loop."""
+
+from __future__ import annotations
+
+import pytest
+import torch
+
+import helpers
+import plain_ops
+import tiny_configs
+import vllm_from_scratch_b200 as engine
+
+
+@pytest.fixture(autouse=True)
+def plain_kernels(monkeypatch):
+    plain_ops.patch(monkeypatch)
+
+
+@pytest.fixture(scope="module")
+def folders(tmp_path_factory):
+    base = tmp_path_factory.mktemp("cpu_models")
+    return {"A": helpers.make_model_folder(base, tiny_configs.TINY_A, seed=31),
+            "B": helpers.make_model_folder(base, tiny_configs.TINY_B, seed=32),
+            "C": helpers.make_model_folder(base, tiny_configs.TINY_C, seed=33)}
+
+
+@pytest.mark.parametrize("name,page", [("A", 16), ("B", 8), ("C", 16)])
+def test_every_cut_gives_the_plain_logits(folders, name, page):
+    raw = getattr(tiny_configs, f"TINY_{name}")
+    lengths = {"a": 45, "b": 70, "c": 33, "d": 3, "e": 90}
+    sequences = {rid: helpers.random_tokens(raw["vocab_size"], n, seed=n) for rid, n in lengths.items()}
+    expected = {rid: helpers.plain_logits(folders[name], toks) for rid, toks in sequences.items()}
+    cuts = {
+        "whole": helpers.cut_whole(lengths), "tail": helpers.cut_tail_one_by_one(lengths, 32),
+        "portions": helpers.cut_changing_portions(lengths), "mixed": helpers.cut_mixed(lengths, seed=2),
+    }
+    for label, steps in cuts.items():
+        pages = sum(sorted((-(-n // page) for n in lengths.values()), reverse=True)[:4])
+        runner = engine.ModelRunner.from_folder(folders[name], "float32", page, pages, 4, device="cpu")
+        results = helpers.run_schedule(runner, sequences, steps)
+        for rid in sequences:
+            diff = float((results[rid] - expected[rid]).abs().max())
+            assert diff < 2e-5, (name, label, rid, diff)
+
+
+def greedy(folder, prompts, **options):
+    llm = engine.LLM(folder, dtype="float32", device="cpu", enforce_eager=True, **options)
+    outs = llm.generate(prompts, engine.SamplingParams(temperature=0.0, max_tokens=10))
+    llm.engine.runner.manager.check_invariants()
+    assert llm.engine.runner.manager.stats()["requests"] == 0
+    return [o.token_ids for o in outs], llm
+
+
+def test_generation_is_the_same_under_every_engine_setting(folders):
+    raw = tiny_configs.TINY_B
+    prompts = [helpers.random_tokens(raw["vocab_size"], n, seed=7 * n) for n in (1, 7, 40, 64, 3, 100)]
+    prompts.append(prompts[3][:48] + [5, 6, 7])             # shares three pages with prompts[3]
+    base, _ = greedy(folders["B"], prompts, max_model_len=128, block_size=8, max_num_seqs=4,
+                     max_num_batched_tokens=32)
+    for prompt, tokens in zip(prompts[:3], base[:3]):
+        sequence = list(prompt)
+        for token in tokens:
+            logits = helpers.plain_logits(folders["B"], sequence)[-1]
+            assert token == int(logits.argmax())
+            sequence.append(token)
+    shared, llm = greedy(folders["B"], prompts, max_model_len=128, block_size=8, max_num_seqs=4,
+                         max_num_batched_tokens=32, enable_prefix_caching=True)
+    assert shared == base
+    assert llm.engine.runner.manager.pools[0].num_published > 0
+    small, llm = greedy(folders["B"], prompts, max_model_len=128, block_size=8, max_num_seqs=4,
+                        max_num_batched_tokens=64, num_gpu_blocks=20)
+    assert small == base and llm.engine.scheduler.num_preemptions > 0
+    one_by_one, _ = greedy(folders["B"], prompts, max_model_len=128, block_size=8, max_num_seqs=1,
+                           max_num_batched_tokens=7)
+    assert one_by_one == base
+
+
+def test_first_step_inputs_are_recorded(folders):
+    llm = engine.LLM(folders["A"], dtype="float32", device="cpu", enforce_eager=True, max_model_len=64,
+                     block_size=16, max_num_seqs=2, max_num_batched_tokens=8)
+    llm.generate([[1, 2, 3, 4, 5], [9, 8, 7, 6, 5, 4]], engine.SamplingParams(temperature=0.0, max_tokens=2))
+    first = llm.engine.first_step_inputs
+    assert first["num_scheduled_tokens"] == {"gen-0": 5, "gen-1": 3}
+    assert first["positions"] == [0, 1, 2, 3, 4, 0, 1, 2]
+    assert first["query_start"] == [0, 5, 8] and first["seq_lens"] == [5, 3]
+    table = first["block_table"][0]
+    assert first["slot_mapping"][0] == [table[0][0] * 16 + i for i in range(5)] + [table[1][0] * 16 + i for i in range(3)]
+
+
+def test_stop_token_and_min_tokens(folders):
+    raw = tiny_configs.TINY_A
+    prompt = helpers.random_tokens(raw["vocab_size"], 9, seed=3)
+    llm = engine.LLM(folders["A"], dtype="float32", device="cpu", enforce_eager=True, max_model_len=64)
+    free = llm.generate([prompt], engine.SamplingParams(temperature=0.0, max_tokens=6))[0].token_ids
+    stopper = free[2]
+    stopped = llm.generate([prompt], engine.SamplingParams(temperature=0.0, max_tokens=6,
+                                                           stop_token_ids=[stopper]))[0]
+    assert stopped.token_ids == free[:free.index(stopper) + 1] and stopped.finish_reason.name == "STOP"
+    assert stopped.stop_reason == stopper
+    held = llm.generate([prompt], engine.SamplingParams(temperature=0.0, max_tokens=6, min_tokens=6,
+                                                        stop_token_ids=[stopper]))[0]
+    assert stopper not in held.token_ids[:5] and len(held.token_ids) == 6

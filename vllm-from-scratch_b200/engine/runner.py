@@ -58,6 +58,7 @@ class ModelRunner:
     def from_folder(cls, folder: str | Path, dtype: str, page_size: int, num_pages: int,
                     max_requests: int, device: str | torch.device = "cuda",
                     enable_prefix_caching: bool = False) -> "ModelRunner":
+        require_device(device)
         entry, config = load_model_config(folder)
         return cls(entry.build_spec(config), folder, dtype, page_size, num_pages, max_requests, device,
                    enable_prefix_caching, model_config=config)

@@ -231,11 +231,11 @@ class Scheduler:
                     raise RuntimeError(f"no token was sampled for request {request.request_id!r}")
                 request.output_token_ids.append(int(sampled[request.request_id]))
                 finished = check_stop(request, self.max_model_len)
+            # Publish full pages first: they stay hittable after the request is gone.
+            self.cache.commit(request.request_id, request.num_computed_tokens, request.all_token_ids)
             if finished:
                 self.running.remove(request)
                 self._free(request)
-            else:
-                self.cache.commit(request.request_id, request.num_computed_tokens, request.all_token_ids)
             if item.samples:
                 results.append(RequestOutput(
                     request.request_id, request.prompt_token_ids, list(request.output_token_ids), finished,
