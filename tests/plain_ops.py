@@ -38,6 +38,13 @@ def gemm(x, w, out):
     out.copy_((x.float() @ w.float().T).to(out.dtype))
 
 
+def gated_silu_gemm(x, w_gate_up, out):
+    inter = out.shape[1]
+    gate_up = x.float() @ w_gate_up.float().T
+    gate, up = gate_up[:, :inter], gate_up[:, inter:]
+    out.copy_((gate * torch.sigmoid(gate) * up).to(out.dtype))
+
+
 def head_norm_rope_cache(qkv, positions, slots, q_weight, k_weight, inv_freq, rotary_dim, eps, q_out,
                          k_pages, v_pages, num_q_heads, num_kv_heads, head_dim, page_size):
     tokens = qkv.shape[0]
@@ -103,7 +110,7 @@ def paged_attention(q, k_pages, v_pages, out, query_start, seq_lens, block_table
         out[begin:end] = result.to(out.dtype)
 
 
-ALL = ("embedding", "add_rmsnorm", "silu_mul", "gemm", "head_norm_rope_cache", "paged_attention")
+ALL = ("embedding", "add_rmsnorm", "silu_mul", "gemm", "gated_silu_gemm", "head_norm_rope_cache", "paged_attention")
 
 
 def patch(monkeypatch) -> None:

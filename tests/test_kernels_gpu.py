@@ -273,3 +273,39 @@ def test_decode_attention_same_for_any_split():
                                                    d ** -0.5, None, 1, planned)
         outs.append(out.float())
     assert float((outs[0] - outs[1]).abs().max()) < 8e-3
+
+
+@pytest.mark.parametrize("m,n,k_", [(1, 512, 128), (8, 4096, 2048), (3, 2048, 6144), (16, 503, 96), (9, 264, 160),
+                                    (16, 12288, 2048), (5, 151936, 256)])
+@pytest.mark.parametrize("out_dtype", [torch.bfloat16, torch.float32])
+def test_few_rows_gemm(m, n, k_, out_dtype):
+    """The weight-streaming kernel (M <= 16): exact float64 reference, and a token's
+    result must not depend on the other tokens of the launch."""
+    k = kernels()
+    g = torch.Generator(device="cuda").manual_seed(m + n + k_)
+    x = torch.randn(m, k_, device="cuda", generator=g).bfloat16()
+    w = torch.randn(n, k_, device="cuda", generator=g).bfloat16()
+    out = torch.full((m, n), 7.0, device="cuda", dtype=out_dtype)
+    k.gemm(x, w, out)
+    exact = x.double() @ w.double().T
+    scale = float(exact.abs().max())
+    bound = scale * (2 ** -8 if out_dtype == torch.bfloat16 else 1e-5)
+    assert float((out.double() - exact).abs().max()) <= bound
+    alone = torch.empty(1, n, device="cuda", dtype=out_dtype)
+    k.gemm(x[m - 1:m].clone(), w, alone)
+    assert torch.equal(alone[0], out[m - 1])
+
+
+@pytest.mark.parametrize("m,inter,k_", [(1, 160, 96), (8, 6144, 2048), (16, 1111, 64), (40, 256, 128)])
+@pytest.mark.parametrize("dtype", DTYPES)
+def test_gated_silu_gemm(m, inter, k_, dtype):
+    k = kernels()
+    g = torch.Generator(device="cuda").manual_seed(m + inter)
+    x = torch.randn(m, k_, device="cuda", generator=g).to(dtype)
+    w = (torch.randn(2 * inter, k_, device="cuda", generator=g) * 0.1).to(dtype)
+    out_a = torch.empty(m, inter, device="cuda", dtype=dtype)
+    out_b = torch.empty_like(out_a)
+    k.gated_silu_gemm(x, w, out_a)
+    plain_ops.gated_silu_gemm(x, w, out_b)
+    bound = float(out_b.float().abs().max()) * (2 ** -7 if dtype == torch.bfloat16 else 1e-5)
+    assert float((out_a.float() - out_b.float()).abs().max()) <= bound

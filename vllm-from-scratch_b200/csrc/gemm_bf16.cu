@@ -1,0 +1,216 @@
+// bfloat16 matrix products for few rows: y[M, N] = x[M, K] . w[N, K]^T with
+// M <= 16, float32 accumulation, output bfloat16 or float32.
+//
+// With so few rows the product is a stream of the weight matrix through the SMs:
+// every weight is used once, so the kernel is built to keep many 16-byte loads in
+// flight and nothing else.  One block of four warps owns 8 (or 2 x 8) weight rows;
+// the warps split K in interleaved blocks of 32, so that together they read 256
+// contiguous bytes of each row per round.  The products run on the tensor cores
+// (m16n8k16, rows of the fragment = the tokens, columns = the 8 weight rows) with
+// the k index permuted the same way in both operands: a thread's 16-byte load of
+// a weight row and of a token row are the fragments of two k-steps as they are, no
+// shuffles.  The four partial sums are added in a fixed order, so a token's result
+// does not depend on how many other tokens share the launch.
+//
+// The gated variant computes silu(x w_gate^T) * (x w_up^T) for the two row blocks
+// [0, I) and [I, 2I) of one matrix (minivllm/models/qwen3.py:44-65 as one kernel).
+#include <stdlib.h>
+
+#include "common.cuh"
+
+namespace b200 {
+
+using bf16 = __nv_bfloat16;
+
+__device__ __forceinline__ void mma_m16n8k16(float (&c)[4], unsigned a0, unsigned a1, unsigned a2,
+                                             unsigned a3, unsigned b0, unsigned b1) {
+    asm volatile(
+        "mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, "
+        "{%0,%1,%2,%3};\n"
+        : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
+        : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
+}
+
+__device__ __forceinline__ uint4 load_stream(const bf16* p) {
+    // weights are read once: do not keep them in L1
+    uint4 v;
+    asm volatile("ld.global.nc.L1::no_allocate.v4.u32 {%0,%1,%2,%3}, [%4];\n"
+                 : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w)
+                 : "l"(p));
+    return v;
+}
+
+template <typename T> __device__ __forceinline__ void store_pair(T* p, float a, float b);
+template <> __device__ __forceinline__ void store_pair<bf16>(bf16* p, float a, float b) {
+    *reinterpret_cast<__nv_bfloat162*>(p) = __floats2bfloat162_rn(a, b);
+}
+template <> __device__ __forceinline__ void store_pair<float>(float* p, float a, float b) {
+    *reinterpret_cast<float2*>(p) = make_float2(a, b);
+}
+template <typename T> __device__ __forceinline__ void store_one(T* p, float a) { *p = from_float<T>(a); }
+
+constexpr int kSkinnyMaxWarps = 16;
+
+// TILES: weight-row blocks of 8 per CTA.  GATED: TILES must be 2; block 0 = gate rows, block 1 = up rows.
+// The block's warps (blockDim.x / 32, at most 16) split K; each keeps UNROLL blocks of 32 in flight.
+template <int TILES, bool GATED, typename OutT, int UNROLL>
+__global__ void __launch_bounds__(kSkinnyMaxWarps * 32) skinny_gemm_kernel(
+    const bf16* __restrict__ x, const bf16* __restrict__ w, OutT* __restrict__ y, int M, int N, int K,
+    int up_offset) {
+    __shared__ float partial[kSkinnyMaxWarps][TILES][32][4];
+    const int kSkinnyWarps = blockDim.x >> 5;
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    const int g = lane >> 2, t = lane & 3;
+    const int n0 = blockIdx.x * (GATED ? 8 : 8 * TILES);
+
+    const bf16* w_row[TILES];
+    bool w_ok[TILES];
+#pragma unroll
+    for (int i = 0; i < TILES; ++i) {
+        const int n = GATED ? (n0 + g + i * up_offset) : (n0 + i * 8 + g);
+        w_ok[i] = GATED ? (n0 + g < N) : (n < N);
+        w_row[i] = w + (size_t)(w_ok[i] ? n : 0) * K + 8 * t;
+    }
+    const bool x_lo = g < M, x_hi = g + 8 < M;
+    const bf16* x_row_lo = x + (size_t)(x_lo ? g : 0) * K + 8 * t;
+    const bf16* x_row_hi = x + (size_t)(x_hi ? g + 8 : 0) * K + 8 * t;
+
+    float acc[TILES][4];
+#pragma unroll
+    for (int i = 0; i < TILES; ++i) acc[i][0] = acc[i][1] = acc[i][2] = acc[i][3] = 0.0f;
+
+    const int blocks = K >> 5;                          // K is a multiple of 32
+    constexpr int kUnroll = UNROLL;
+    const uint4 zero = make_uint4(0, 0, 0, 0);
+    int j = warp;
+    for (; j + (kUnroll - 1) * kSkinnyWarps < blocks; j += kUnroll * kSkinnyWarps) {
+        uint4 wv[kUnroll][TILES], xl[kUnroll], xh[kUnroll];
+#pragma unroll
+        for (int u = 0; u < kUnroll; ++u) {
+            const int off = (j + u * kSkinnyWarps) << 5;
+#pragma unroll
+            for (int i = 0; i < TILES; ++i) wv[u][i] = w_ok[i] ? load_stream(w_row[i] + off) : zero;
+            xl[u] = x_lo ? *reinterpret_cast<const uint4*>(x_row_lo + off) : zero;
+            xh[u] = x_hi ? *reinterpret_cast<const uint4*>(x_row_hi + off) : zero;
+        }
+#pragma unroll
+        for (int u = 0; u < kUnroll; ++u)
+#pragma unroll
+            for (int i = 0; i < TILES; ++i) {
+                mma_m16n8k16(acc[i], xl[u].x, xh[u].x, xl[u].y, xh[u].y, wv[u][i].x, wv[u][i].y);
+                mma_m16n8k16(acc[i], xl[u].z, xh[u].z, xl[u].w, xh[u].w, wv[u][i].z, wv[u][i].w);
+            }
+    }
+    for (; j < blocks; j += kSkinnyWarps) {
+        const int off = j << 5;
+        const uint4 xl = x_lo ? *reinterpret_cast<const uint4*>(x_row_lo + off) : zero;
+        const uint4 xh = x_hi ? *reinterpret_cast<const uint4*>(x_row_hi + off) : zero;
+#pragma unroll
+        for (int i = 0; i < TILES; ++i) {
+            const uint4 wv = w_ok[i] ? load_stream(w_row[i] + off) : zero;
+            mma_m16n8k16(acc[i], xl.x, xh.x, xl.y, xh.y, wv.x, wv.y);
+            mma_m16n8k16(acc[i], xl.z, xh.z, xl.w, xh.w, wv.z, wv.w);
+        }
+    }
+
+#pragma unroll
+    for (int i = 0; i < TILES; ++i)
+#pragma unroll
+        for (int e = 0; e < 4; ++e) partial[warp][i][lane][e] = acc[i][e];
+    __syncthreads();
+    if (warp != 0) return;
+    float total[TILES][4];
+#pragma unroll
+    for (int i = 0; i < TILES; ++i)
+#pragma unroll
+        for (int e = 0; e < 4; ++e) {
+            float s = partial[0][i][lane][e];
+            for (int wi = 1; wi < kSkinnyWarps; ++wi) s += partial[wi][i][lane][e];
+            total[i][e] = s;
+        }
+    // accumulator layout: c0, c1 = (token g, weight rows 2t, 2t+1), c2, c3 = (token g + 8, same rows)
+    if (GATED) {
+        const int n = n0 + 2 * t;
+#pragma unroll
+        for (int half = 0; half < 2; ++half) {
+            const int token = g + half * 8;
+            if (token >= M) continue;
+            const float g0 = total[0][half * 2], g1 = total[0][half * 2 + 1];
+            const float u0 = total[1][half * 2], u1 = total[1][half * 2 + 1];
+            const float r0 = g0 / (1.0f + expf(-g0)) * u0, r1 = g1 / (1.0f + expf(-g1)) * u1;
+            OutT* dst = y + (size_t)token * N + n;
+            if (n + 1 < N && (N & 1) == 0) store_pair<OutT>(dst, r0, r1);
+            else {
+                if (n < N) store_one<OutT>(dst, r0);
+                if (n + 1 < N) store_one<OutT>(dst + 1, r1);
+            }
+        }
+    } else {
+#pragma unroll
+        for (int i = 0; i < TILES; ++i) {
+            const int n = n0 + i * 8 + 2 * t;
+#pragma unroll
+            for (int half = 0; half < 2; ++half) {
+                const int token = g + half * 8;
+                if (token >= M) continue;
+                OutT* dst = y + (size_t)token * N + n;
+                if (n + 1 < N && (N & 1) == 0) store_pair<OutT>(dst, total[i][half * 2], total[i][half * 2 + 1]);
+                else {
+                    if (n < N) store_one<OutT>(dst, total[i][half * 2]);
+                    if (n + 1 < N) store_one<OutT>(dst + 1, total[i][half * 2 + 1]);
+                }
+            }
+        }
+    }
+}
+
+template <typename OutT>
+int launch_skinny(const bf16* x, const bf16* w, OutT* y, int M, int N, int K, int gated_inter,
+                  cudaStream_t stream) {
+    // The GPU should hold a few thousand warps, each with all of its loads in flight:
+    // the fewer blocks a product has, the more warps split K inside each block.
+    const int k_blocks = K >> 5;
+    const bool two_tiles = gated_inter > 0 || N >= 148 * 4 * 16;
+    const int ctas = gated_inter > 0 ? (gated_inter + 7) / 8 : two_tiles ? (N + 15) / 16 : (N + 7) / 8;
+    const int wanted = 6144 / (ctas * (two_tiles ? 2 : 1));
+    int warps = 4;
+    while (warps * 2 <= wanted && warps < kSkinnyMaxWarps) warps *= 2;
+    while (warps > 1 && warps > k_blocks) warps /= 2;
+    if (const char* forced = getenv("B200_SKINNY_WARPS")) warps = atoi(forced);
+    const int threads = warps * 32;
+    if (gated_inter > 0) {
+        skinny_gemm_kernel<2, true, OutT, 4><<<ctas, threads, 0, stream>>>(x, w, y, M, gated_inter, K, gated_inter);
+    } else if (two_tiles) {
+        skinny_gemm_kernel<2, false, OutT, 4><<<ctas, threads, 0, stream>>>(x, w, y, M, N, K, 0);
+    } else {
+        skinny_gemm_kernel<1, false, OutT, 8><<<ctas, threads, 0, stream>>>(x, w, y, M, N, K, 0);
+    }
+    return check_launch("skinny_gemm");
+}
+
+}  // namespace b200
+
+// Largest M and the divisibility of K the few-rows kernel takes.
+B200_EXPORT int b200_skinny_gemm_supports(int M, int N, int K) {
+    return (M >= 1 && M <= 16 && K >= 32 && K % 32 == 0 && N >= 1) ? 1 : 0;
+}
+
+// out_dtype: 0 = float32, 1 = bfloat16.  gated_inter > 0: w is [2 * gated_inter, K] and
+// y is [M, gated_inter] = silu(x w[:I]^T) * (x w[I:]^T).
+B200_EXPORT int b200_skinny_gemm_bf16(const void* x, const void* w, void* y, int M, int N, int K,
+                                      int gated_inter, int out_dtype, cudaStream_t stream) {
+    using namespace b200;
+    if (M == 0 || N == 0) return 0;
+    if (!b200_skinny_gemm_supports(M, N, K)) return fail("skinny_gemm", "needs 1 <= M <= 16 and K a multiple of 32");
+    if (((uintptr_t)x | (uintptr_t)w) & 15) return fail("skinny_gemm", "operands must be 16-byte aligned");
+    if (gated_inter > 0 && N != 2 * gated_inter) return fail("skinny_gemm", "gated product needs N = 2 * inter");
+    if (out_dtype == 1) {
+        if ((uintptr_t)y & 3) return fail("skinny_gemm", "output must be 4-byte aligned");
+        return launch_skinny<bf16>((const bf16*)x, (const bf16*)w, (bf16*)y, M, N, K, gated_inter, stream);
+    }
+    if (out_dtype == 0) {
+        if ((uintptr_t)y & 7) return fail("skinny_gemm", "output must be 8-byte aligned");
+        return launch_skinny<float>((const bf16*)x, (const bf16*)w, (float*)y, M, N, K, gated_inter, stream);
+    }
+    return fail("skinny_gemm", "out_dtype must be 0 (float32) or 1 (bfloat16)");
+}

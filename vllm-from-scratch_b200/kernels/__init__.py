@@ -138,6 +138,24 @@ def gemm(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor) -> None:
     gemm_bf16.gemm_bf16(x, w, out)
 
 
+def gated_silu_gemm(x: torch.Tensor, w_gate_up: torch.Tensor, out: torch.Tensor) -> None:
+    """``out[M, I] = silu(x @ w[:I]^T) * (x @ w[I:]^T)`` for ``w_gate_up`` of shape
+    ``[2 I, K]`` (gate rows first).  One fused kernel where the shape allows it,
+    otherwise the product followed by the activation kernel."""
+    m, k = x.shape
+    inter = out.shape[1]
+    _check("gated input", x, (torch.float32, torch.bfloat16))
+    _check("gate_up weight", w_gate_up, x.dtype, (2 * inter, k))
+    _check("gated output", out, x.dtype, (m, inter))
+    if x.dtype == torch.bfloat16:
+        from . import gemm_bf16
+        if gemm_bf16.gated_silu_gemm_bf16(x, w_gate_up, out):
+            return
+    gate_up = torch.empty((m, 2 * inter), dtype=x.dtype, device=x.device)
+    gemm(x, w_gate_up, gate_up)
+    silu_mul(gate_up, out)
+
+
 # -------------------------------------------------------------------- attention
 def head_norm_rope_cache(qkv: torch.Tensor, positions: torch.Tensor, slots: torch.Tensor,
                          q_weight: torch.Tensor | None, k_weight: torch.Tensor | None,

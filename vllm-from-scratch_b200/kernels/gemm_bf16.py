@@ -1,21 +1,56 @@
-"""bfloat16 matrix product with float32 accumulation.
+"""bfloat16 matrix products with float32 accumulation.
 
-The product goes to the vendor's library through ``torch.mm``, as the
-reference's ``F.linear`` does (minivllm/layers/quantization/methods.py:36-37).
+Up to 16 rows (decode steps of small batches): the engine's own weight-streaming
+kernel, optionally with the gated SiLU fused in.  More rows: the vendor's library
+through ``torch.mm``, as the reference's ``F.linear`` does
+(minivllm/layers/quantization/methods.py:36-37).
 """
 
 from __future__ import annotations
 
+import ctypes
+
 import torch
+
+from ..csrc.build import load_library
 
 # Partial sums of a product split along K stay in float32: the library must not
 # add them up in bfloat16.
 torch.backends.cuda.matmul.allow_bf16_reduced_precision_reduction = False
 
+SKINNY_MAX_ROWS = 16
+_P, _I = ctypes.c_void_p, ctypes.c_int
+
+
+def _skinny_ok(m: int, k: int, *tensors: torch.Tensor) -> bool:
+    return 1 <= m <= SKINNY_MAX_ROWS and k >= 32 and k % 32 == 0 and all(t.data_ptr() % 16 == 0 for t in tensors)
+
+
+def _skinny(x, w, out, gated_inter: int) -> None:
+    from . import KernelError, _stream, count_launch
+    lib = load_library("gemm_bf16")
+    status = lib.b200_skinny_gemm_bf16(
+        _P(x.data_ptr()), _P(w.data_ptr()), _P(out.data_ptr()), _I(x.shape[0]), _I(w.shape[0]), _I(x.shape[1]),
+        _I(gated_inter), _I(1 if out.dtype == torch.bfloat16 else 0), _stream())
+    if status != 0:
+        raise KernelError(lib.b200_last_error().decode())
+    count_launch()
+
 
 def gemm_bf16(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor) -> None:
-    if out.dtype == torch.bfloat16:
+    if _skinny_ok(x.shape[0], x.shape[1], x, w, out):
+        _skinny(x, w, out, 0)
+    elif out.dtype == torch.bfloat16:
         torch.mm(x, w.t(), out=out)
     else:
         # float32 result straight from the float32 accumulator (no bfloat16 rounding).
         out.copy_(torch.mm(x, w.t(), out_dtype=torch.float32))
+
+
+def gated_silu_gemm_bf16(x: torch.Tensor, w_gate_up: torch.Tensor, out: torch.Tensor) -> bool:
+    """``out = silu(x w[:I]^T) * (x w[I:]^T)`` in one kernel; False if the shape is
+    not one the fused kernel takes (the caller then does it in two steps)."""
+    if not _skinny_ok(x.shape[0], x.shape[1], x, w_gate_up, out):
+        return False
+    _skinny(x, w_gate_up, out, out.shape[1])
+    return True

@@ -1,0 +1,168 @@
+"""Time one kernel on synthetic inputs of a given shape.
+
+    python -m vllm_from_scratch_b200.kernels.microbench decode_attention --batch 64 --context 2048
+    python -m vllm_from_scratch_b200.kernels.microbench prefill_attention --tokens 2048
+    python -m vllm_from_scratch_b200.kernels.microbench gemm --m 8 --n 12288 --k 2048
+    python -m vllm_from_scratch_b200.kernels.microbench norm | silu_mul | rope --tokens 2048
+
+CUDA events around ``--iters`` launches after ``--warmup``; between launches a
+buffer larger than L2 is written unless ``--keep-l2`` is given.  Prints one JSON
+line with the time per launch and the achieved bytes/s or flop/s for the
+algorithmic minimum of traffic or work.
+"""
+
+from __future__ import annotations
+
+import argparse
+import itertools
+import json
+
+import torch
+
+from .. import kernels
+
+
+def _time(fn, warmup: int, iters: int, flush: bool) -> float:
+    """Median milliseconds of ``fn``.  ``fn`` is captured into a CUDA graph first, so
+    that the time is the GPU's and not that of the Python calls that launch it."""
+    scrub = torch.empty(192 * 1024 * 1024, dtype=torch.uint8, device="cuda") if flush else None
+    fn()
+    torch.cuda.synchronize()
+    graph = torch.cuda.CUDAGraph()
+    with torch.cuda.graph(graph):
+        fn()
+    fn = graph.replay
+    for _ in range(warmup):
+        fn()
+    times = []
+    for _ in range(iters):
+        if scrub is not None:
+            scrub.fill_(1)
+        begin, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        begin.record()
+        fn()
+        end.record()
+        torch.cuda.synchronize()
+        times.append(begin.elapsed_time(end))
+    times.sort()
+    return times[len(times) // 2]
+
+
+def _paged_case(batch, q_len, context, nq, nkv, d, page, dtype):
+    pages_per = -(-context // page)
+    total = batch * pages_per
+    g = torch.Generator(device="cuda").manual_seed(0)
+    table = torch.randperm(total, device="cuda", generator=g).to(torch.int32).view(batch, pages_per)
+    kp = torch.randn(total, nkv, page, d, device="cuda", generator=g).to(dtype)
+    vp = torch.randn(total, nkv, page, d, device="cuda", generator=g).to(dtype)
+    q = torch.randn(batch * q_len, nq * d, device="cuda", generator=g).to(dtype)
+    start = torch.tensor([0] + list(itertools.accumulate([q_len] * batch)), dtype=torch.int32, device="cuda")
+    seq = torch.full((batch,), context, dtype=torch.int32, device="cuda")
+    return q, kp, vp, start, seq, table
+
+
+def main(argv=None) -> int:
+    parser = argparse.ArgumentParser(description=__doc__, formatter_class=argparse.RawTextHelpFormatter)
+    parser.add_argument("op", choices=("decode_attention", "prefill_attention", "gemm", "norm", "silu_mul", "rope"))
+    parser.add_argument("--batch", type=int, default=8)
+    parser.add_argument("--context", type=int, default=2048)
+    parser.add_argument("--tokens", type=int, default=2048)
+    parser.add_argument("--heads", type=int, default=16)
+    parser.add_argument("--kv-heads", type=int, default=8)
+    parser.add_argument("--head-dim", type=int, default=128)
+    parser.add_argument("--page", type=int, default=16)
+    parser.add_argument("--hidden", type=int, default=2048)
+    parser.add_argument("--inter", type=int, default=6144)
+    parser.add_argument("--m", type=int, default=8)
+    parser.add_argument("--n", type=int, default=4096)
+    parser.add_argument("--k", type=int, default=2048)
+    parser.add_argument("--dtype", default="bfloat16", choices=("bfloat16", "float32"))
+    parser.add_argument("--planned-context", type=int, default=None,
+                        help="context length the decode launch is planned for (default: --context)")
+    parser.add_argument("--warmup", type=int, default=3)
+    parser.add_argument("--iters", type=int, default=10)
+    parser.add_argument("--keep-l2", action="store_true")
+    parser.add_argument("--gated", action="store_true", help="gemm: fused silu(gate) * up, N = 2 * inter")
+    args = parser.parse_args(argv)
+    dtype = torch.bfloat16 if args.dtype == "bfloat16" else torch.float32
+    size = 2 if dtype == torch.bfloat16 else 4
+    nq, nkv, d = args.heads, args.kv_heads, args.head_dim
+    record: dict = {"op": args.op, "dtype": args.dtype}
+
+    if args.op in ("decode_attention", "prefill_attention"):
+        decode = args.op == "decode_attention"
+        batch = args.batch if decode else 1
+        q_len = 1 if decode else args.tokens
+        context = args.context if decode else args.tokens
+        q, kp, vp, start, seq, table = _paged_case(batch, q_len, context, nq, nkv, d, args.page, dtype)
+        out = torch.empty_like(q)
+        planned = args.planned_context or context
+        fn = lambda: kernels.paged_attention(q, kp, vp, out, start, seq, table, nq, nkv, d, args.page,
+                                             d ** -0.5, None, q_len, planned)
+        ms = _time(fn, args.warmup, args.iters, not args.keep_l2)
+        record.update(batch=batch, context=context, heads=nq, kv_heads=nkv, head_dim=d, page=args.page)
+        if decode:
+            moved = batch * context * nkv * d * 2 * size
+            record.update(bytes=moved, gb_s=round(moved / ms / 1e6, 1))
+        else:
+            flops = 2 * 2 * nq * d * context * context / 2
+            record.update(flops=flops, tflop_s=round(flops / ms / 1e9, 1))
+    elif args.op == "gemm":
+        x = torch.randn(args.m, args.k, device="cuda").to(dtype)
+        # Enough copies of the weight to exceed L2 several times over: launched back to
+        # back, each launch reads cold weights and the launch gaps are amortised.
+        copies = max(1, min(64, (512 * 1024 * 1024) // (args.n * args.k * size)))
+        ws = [torch.randn(args.n, args.k, device="cuda").to(dtype) for _ in range(copies)]
+        if args.gated:
+            out = torch.empty(args.m, args.n // 2, device="cuda", dtype=dtype)
+            one = lambda w: kernels.gated_silu_gemm(x, w, out)
+        else:
+            out = torch.empty(args.m, args.n, device="cuda", dtype=dtype)
+            one = lambda w: kernels.gemm(x, w, out)
+
+        def sweep():
+            for w in ws:
+                one(w)
+        ms = _time(sweep, args.warmup, args.iters, False) / copies
+        moved = (args.n * args.k + args.m * args.k + args.m * args.n) * size
+        flops = 2 * args.m * args.n * args.k
+        record.update(m=args.m, n=args.n, k=args.k, gb_s=round(moved / ms / 1e6, 1),
+                      tflop_s=round(flops / ms / 1e9, 2))
+    elif args.op == "norm":
+        x = torch.randn(args.tokens, args.hidden, device="cuda").to(dtype)
+        residual = torch.randn(args.tokens, args.hidden, device="cuda")
+        weight = torch.ones(args.hidden, device="cuda")
+        out = torch.empty_like(x)
+        ms = _time(lambda: kernels.add_rmsnorm(x, residual, weight, 1e-6, out), args.warmup, args.iters,
+                   not args.keep_l2)
+        moved = args.tokens * args.hidden * (2 * size + 8)
+        record.update(tokens=args.tokens, hidden=args.hidden, gb_s=round(moved / ms / 1e6, 1))
+    elif args.op == "silu_mul":
+        gate_up = torch.randn(args.tokens, 2 * args.inter, device="cuda").to(dtype)
+        out = torch.empty(args.tokens, args.inter, device="cuda", dtype=dtype)
+        ms = _time(lambda: kernels.silu_mul(gate_up, out), args.warmup, args.iters, not args.keep_l2)
+        moved = args.tokens * args.inter * 3 * size
+        record.update(tokens=args.tokens, inter=args.inter, gb_s=round(moved / ms / 1e6, 1))
+    else:
+        tokens = args.tokens
+        qkv = torch.randn(tokens, (nq + 2 * nkv) * d, device="cuda").to(dtype)
+        positions = torch.arange(tokens, dtype=torch.int32, device="cuda")
+        slots = torch.arange(tokens, dtype=torch.int32, device="cuda")
+        pages = -(-tokens // args.page)
+        kp = torch.zeros(pages, nkv, args.page, d, device="cuda", dtype=dtype)
+        vp = torch.zeros_like(kp)
+        q_out = torch.empty(tokens, nq * d, device="cuda", dtype=dtype)
+        weight = torch.ones(d, device="cuda")
+        inv_freq = (1.0 / (1e6 ** (torch.arange(0, d, 2, dtype=torch.float32) / d))).cuda()
+        ms = _time(lambda: kernels.head_norm_rope_cache(qkv, positions, slots, weight, weight, inv_freq, d,
+                                                        1e-6, q_out, kp, vp, nq, nkv, d, args.page),
+                   args.warmup, args.iters, not args.keep_l2)
+        moved = tokens * (nq + 2 * nkv) * d * 2 * size
+        record.update(tokens=tokens, gb_s=round(moved / ms / 1e6, 1))
+    record["us"] = round(ms * 1000, 2)
+    print(json.dumps(record))
+    return 0
+
+
+if __name__ == "__main__":
+    raise SystemExit(main())

@@ -37,10 +37,8 @@ class GatedSiluFeedForward(FeedForward):
 
     def forward(self, x: torch.Tensor, ctx: StepContext) -> torch.Tensor:
         tokens = x.shape[0]
-        gate_up = torch.empty((tokens, 2 * self.intermediate_size), dtype=x.dtype, device=x.device)
-        kernels.gemm(x, self.gate_up, gate_up)
         hidden = torch.empty((tokens, self.intermediate_size), dtype=x.dtype, device=x.device)
-        kernels.silu_mul(gate_up, hidden)
+        kernels.gated_silu_gemm(x, self.gate_up, hidden)
         out = torch.empty((tokens, self.env.hidden_size), dtype=x.dtype, device=x.device)
         kernels.gemm(hidden, self.down, out)
         return out
