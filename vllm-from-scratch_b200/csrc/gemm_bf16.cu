@@ -3,13 +3,13 @@
 //
 // With so few rows the product is a stream of the weight matrix through the SMs:
 // every weight is used once, so the kernel is built to keep many 16-byte loads in
-// flight and nothing else.  One block of four warps owns 8 (or 2 x 8) weight rows;
-// the warps split K in interleaved blocks of 32, so that together they read 256
-// contiguous bytes of each row per round.  The products run on the tensor cores
+// flight and nothing else.  One block owns 8 (or 2 x 8) weight rows; its warps (4 to
+// 16, more the fewer blocks the product has) split K in interleaved blocks of 32, so
+// that together they read long contiguous pieces of each row per round.  The products run on the tensor cores
 // (m16n8k16, rows of the fragment = the tokens, columns = the 8 weight rows) with
 // the k index permuted the same way in both operands: a thread's 16-byte load of
 // a weight row and of a token row are the fragments of two k-steps as they are, no
-// shuffles.  The four partial sums are added in a fixed order, so a token's result
+// shuffles.  The warps' partial sums are added in a fixed order, so a token's result
 // does not depend on how many other tokens share the launch.
 //
 // The gated variant computes silu(x w_gate^T) * (x w_up^T) for the two row blocks
@@ -17,6 +17,7 @@
 #include <stdlib.h>
 
 #include "common.cuh"
+#include "stream_gemm.cuh"
 
 namespace b200 {
 
@@ -188,7 +189,72 @@ int launch_skinny(const bf16* x, const bf16* w, OutT* y, int M, int N, int K, in
     return check_launch("skinny_gemm");
 }
 
+// Set by a kernel whose bounded wait ran out (0 = never).  Read and cleared by
+// b200_stream_gemm_error().
+__device__ int g_stream_error;
+
+// Returns 1 when the shape was launched, 0 when its token rows do not fit in shared
+// memory beside at least three weight stages (the caller then uses the other kernel).
+template <int TILES, bool GATED, typename OutT>
+int launch_stream_one(const bf16* x, const bf16* w, OutT* y, int M, int N, int K, int up_offset,
+                      int* error_flag, cudaStream_t stream) {
+    auto kernel = stream_gemm_kernel<TILES, GATED, OutT>;
+    const int x_rows = M <= 8 ? 8 : 16;
+    const int limit = 227 * 1024;
+    const int half = limit / 2 - 1024;                       // two blocks per SM when they fit
+    int stages = 8;
+    while (stages > 3 && stream_gemm_smem(TILES, stages, x_rows, K) > half) --stages;
+    if (stream_gemm_smem(TILES, stages, x_rows, K) > half) {
+        stages = 8;                                          // one block per SM, as many stages as fit
+        while (stages > 3 && stream_gemm_smem(TILES, stages, x_rows, K) > limit) --stages;
+    }
+    const int smem = stream_gemm_smem(TILES, stages, x_rows, K);
+    if (smem > limit) return 0;
+    cudaError_t status = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
+    if (status != cudaSuccess) return fail("stream_gemm", cudaGetErrorString(status));
+    const int rows_per_tile = GATED ? 8 : 8 * TILES;
+    const int num_tiles = (N + rows_per_tile - 1) / rows_per_tile;
+    const int resident = 148 * (limit / (smem + 1024));
+    const int grid = num_tiles < resident ? num_tiles : resident;
+    kernel<<<grid, (kStreamConsumers + 1) * 32, smem, stream>>>(x, w, y, M, N, K, up_offset, num_tiles, stages,
+                                                                x_rows, error_flag);
+    if (check_launch("stream_gemm")) return -1;
+    return 1;
+}
+
+template <typename OutT>
+int launch_stream(const bf16* x, const bf16* w, OutT* y, int M, int N, int K, int gated_inter,
+                  cudaStream_t stream) {
+    static int* error_flag[64] = {};
+    int device = 0;
+    if (cudaGetDevice(&device) != cudaSuccess || device < 0 || device >= 64) return fail("stream_gemm", "no device");
+    if (error_flag[device] == nullptr) {
+        void* found = nullptr;
+        cudaError_t status = cudaGetSymbolAddress(&found, g_stream_error);
+        if (status != cudaSuccess) return fail("stream_gemm", cudaGetErrorString(status));
+        error_flag[device] = static_cast<int*>(found);
+    }
+    if (gated_inter > 0)
+        return launch_stream_one<2, true, OutT>(x, w, y, M, gated_inter, K, gated_inter, error_flag[device], stream);
+    if (N >= 148 * 3 * 16)
+        return launch_stream_one<2, false, OutT>(x, w, y, M, N, K, 0, error_flag[device], stream);
+    return launch_stream_one<1, false, OutT>(x, w, y, M, N, K, 0, error_flag[device], stream);
+}
+
 }  // namespace b200
+
+// 0, or the code a kernel left when one of its bounded waits ran out (1: the producer
+// waited for a free stage, 2: for its own copies, 3: a consumer waited for data).
+// Synchronises with the device and clears the code.
+B200_EXPORT int b200_stream_gemm_error() {
+    int code = 0;
+    if (cudaMemcpyFromSymbol(&code, b200::g_stream_error, sizeof(int)) != cudaSuccess) return -1;
+    if (code != 0) {
+        const int zero = 0;
+        cudaMemcpyToSymbol(b200::g_stream_error, &zero, sizeof(int));
+    }
+    return code;
+}
 
 // Largest M and the divisibility of K the few-rows kernel takes.
 B200_EXPORT int b200_skinny_gemm_supports(int M, int N, int K) {
@@ -204,6 +270,13 @@ B200_EXPORT int b200_skinny_gemm_bf16(const void* x, const void* w, void* y, int
     if (!b200_skinny_gemm_supports(M, N, K)) return fail("skinny_gemm", "needs 1 <= M <= 16 and K a multiple of 32");
     if (((uintptr_t)x | (uintptr_t)w) & 15) return fail("skinny_gemm", "operands must be 16-byte aligned");
     if (gated_inter > 0 && N != 2 * gated_inter) return fail("skinny_gemm", "gated product needs N = 2 * inter");
+    const bool streamed = K >= 512 && getenv("B200_STREAM_GEMM") != nullptr;
+    if (streamed && (out_dtype == 0 || out_dtype == 1)) {
+        const int rc = out_dtype == 1
+            ? launch_stream<bf16>((const bf16*)x, (const bf16*)w, (bf16*)y, M, N, K, gated_inter, stream)
+            : launch_stream<float>((const bf16*)x, (const bf16*)w, (float*)y, M, N, K, gated_inter, stream);
+        if (rc != 0) return rc < 0 ? rc : 0;       // launched (1) or failed (< 0); 0 = shape too large for it
+    }
     if (out_dtype == 1) {
         if ((uintptr_t)y & 3) return fail("skinny_gemm", "output must be 4-byte aligned");
         return launch_skinny<bf16>((const bf16*)x, (const bf16*)w, (bf16*)y, M, N, K, gated_inter, stream);
