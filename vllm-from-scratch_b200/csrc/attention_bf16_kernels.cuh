@@ -68,20 +68,31 @@ __device__ __forceinline__ float quad_sum(float v) {
 
 // Keys k0 .. k0+63 of one request and key/value head into a stage of shared memory.
 // Positions at or beyond k_end, and pages that were given back, are filled with zeros.
+// A thread always copies the same 16-byte chunk of its rows, so the only per-row work
+// is the look-up of the row's page (a shift when the page size is a power of two).
 template <int D>
 __device__ __forceinline__ void load_kv_tile(bf16* k_s, bf16* v_s, const bf16* __restrict__ k_pages,
                                              const bf16* __restrict__ v_pages,
                                              const int* __restrict__ table, int k0, int k_end,
-                                             int kv_head, int nkv, int page_size) {
+                                             int kv_head, int nkv, int page_size, int page_shift) {
     constexpr int kChunks = D / 8;
-    for (int idx = threadIdx.x; idx < kKeys * kChunks; idx += kThreads) {
-        const int row = idx / kChunks, chunk = idx - row * kChunks;
+    constexpr int kRowsPerPass = kThreads / kChunks;
+    const int chunk = threadIdx.x % kChunks, first_row = threadIdx.x / kChunks;
+    const size_t in_page = (size_t)kv_head * page_size * D + chunk * 8;
+    const size_t page_stride = (size_t)nkv * page_size * D;
+#pragma unroll
+    for (int i = 0; i < kKeys / kRowsPerPass; ++i) {
+        const int row = first_row + i * kRowsPerPass;
         const int kp = k0 + row;
         const int at_s = row * D + ((chunk ^ (row & 7)) << 3);
-        int page = -1;
-        if (kp < k_end) page = table[kp / page_size];
+        int page = -1, offset = 0;
+        if (kp < k_end) {
+            const int index = page_shift >= 0 ? kp >> page_shift : kp / page_size;
+            offset = page_shift >= 0 ? kp & (page_size - 1) : kp - index * page_size;
+            page = table[index];
+        }
         if (page >= 0) {
-            const size_t at = (((size_t)page * nkv + kv_head) * page_size + (kp % page_size)) * D + chunk * 8;
+            const size_t at = (size_t)page * page_stride + in_page + (size_t)offset * D;
             cp_async16(k_s + at_s, k_pages + at);
             cp_async16(v_s + at_s, v_pages + at);
         } else {
@@ -130,6 +141,7 @@ __global__ void __launch_bounds__(kThreads) decode_attention_kernel(
     const int my_end = min(seq_len, my_begin + chunk);
     const int tiles = my_end > my_begin ? (my_end - my_begin + kKeys - 1) / kKeys : 0;
     const int* table = block_table + (size_t)request * max_pages;
+    const int page_shift = (page_size & (page_size - 1)) == 0 ? 31 - __clz(page_size) : -1;
 
     const int row_a = lane >> 2, row_b = row_a + 8;
     const bf16* q_base = q + ((size_t)request * nq + (size_t)kv_head * group) * D;
@@ -146,14 +158,14 @@ __global__ void __launch_bounds__(kThreads) decode_attention_kernel(
     auto v_stage = [&](int s) { return stage_base + (size_t)s * 2 * kKeys * D + kKeys * D; };
 
     if (tiles > 0) {
-        load_kv_tile<D>(k_stage(0), v_stage(0), k_pages, v_pages, table, my_begin, my_end, kv_head, nkv, page_size);
+        load_kv_tile<D>(k_stage(0), v_stage(0), k_pages, v_pages, table, my_begin, my_end, kv_head, nkv, page_size, page_shift);
         cp_async_commit();
     }
     for (int t = 0; t < tiles; ++t) {
         const int k0 = my_begin + t * kKeys;
         if (t + 1 < tiles) {
             load_kv_tile<D>(k_stage((t + 1) & 1), v_stage((t + 1) & 1), k_pages, v_pages, table,
-                            k0 + kKeys, my_end, kv_head, nkv, page_size);
+                            k0 + kKeys, my_end, kv_head, nkv, page_size, page_shift);
             cp_async_commit();
             cp_async_wait<1>();
         } else {
@@ -290,7 +302,7 @@ __global__ void merge_splits_kernel(const float* __restrict__ partial_o, const f
 // request, 16 per warp; the request of a tile is found from the tile index as in
 // attention_generic.cu (request r owns tiles [start[r] / 64 + r, start[r+1] / 64 + r + 1)).
 template <int D>
-__global__ void __launch_bounds__(kThreads) prefill_attention_kernel(
+__global__ void __launch_bounds__(kThreads, 3) prefill_attention_kernel(
     const bf16* __restrict__ q, const bf16* __restrict__ k_pages, const bf16* __restrict__ v_pages,
     bf16* __restrict__ out, const int* __restrict__ query_start, const int* __restrict__ seq_lens,
     const int* __restrict__ block_table, int num_requests, int max_pages, int nq, int nkv,
@@ -298,7 +310,9 @@ __global__ void __launch_bounds__(kThreads) prefill_attention_kernel(
     extern __shared__ __align__(128) unsigned char smem_raw[];
     bf16* stage_base = reinterpret_cast<bf16*>(smem_raw);
     constexpr int kRows = 64;
-    const int block = blockIdx.x;
+    // Late tiles of a long request have the most keys to visit: hand them out first, so
+    // that the short ones fill the end of the launch.
+    const int block = gridDim.x - 1 - blockIdx.x;
     int lo = 0, hi = num_requests - 1;
     while (lo < hi) {
         const int mid = (lo + hi + 1) >> 1;
@@ -315,6 +329,7 @@ __global__ void __launch_bounds__(kThreads) prefill_attention_kernel(
     const int head = blockIdx.y;
     const int kv_head = head / (nq / nkv);
     const int* table = block_table + (size_t)request * max_pages;
+    const int page_shift = (page_size & (page_size - 1)) == 0 ? 31 - __clz(page_size) : -1;
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
 
     const int row_a = warp * 16 + (lane >> 2), row_b = row_a + 8;
@@ -340,13 +355,13 @@ __global__ void __launch_bounds__(kThreads) prefill_attention_kernel(
     auto k_stage = [&](int s) { return stage_base + (size_t)s * 2 * kKeys * D; };
     auto v_stage = [&](int s) { return stage_base + (size_t)s * 2 * kKeys * D + kKeys * D; };
 
-    load_kv_tile<D>(k_stage(0), v_stage(0), k_pages, v_pages, table, k_first, k_end, kv_head, nkv, page_size);
+    load_kv_tile<D>(k_stage(0), v_stage(0), k_pages, v_pages, table, k_first, k_end, kv_head, nkv, page_size, page_shift);
     cp_async_commit();
     for (int t = 0; t < tiles; ++t) {
         const int k0 = k_first + t * kKeys;
         if (t + 1 < tiles) {
             load_kv_tile<D>(k_stage((t + 1) & 1), v_stage((t + 1) & 1), k_pages, v_pages, table,
-                            k0 + kKeys, k_end, kv_head, nkv, page_size);
+                            k0 + kKeys, k_end, kv_head, nkv, page_size, page_shift);
             cp_async_commit();
             cp_async_wait<1>();
         } else {
@@ -376,18 +391,32 @@ __global__ void __launch_bounds__(kThreads) prefill_attention_kernel(
                 }
             }
             float max_a = -INFINITY, max_b = -INFINITY;
+            // A tile wholly before the warp's first query (and inside every window) needs no mask.
+            const bool all_visible = k0 + kKeys - 1 <= warp_first_pos &&
+                                     (window <= 0 || k0 > warp_last_pos - window);
+            if (all_visible) {
 #pragma unroll
-            for (int nt = 0; nt < 8; ++nt)
+                for (int nt = 0; nt < 8; ++nt)
 #pragma unroll
-                for (int e = 0; e < 4; ++e) {
-                    const int kp = k0 + nt * 8 + (lane & 3) * 2 + (e & 1);
-                    const int q_pos = e < 2 ? pos_a : pos_b;
-                    bool visible = kp <= q_pos;
-                    if (window > 0) visible = visible && (kp > q_pos - window);
-                    const float v = visible ? s[nt][e] * scale_log2 : -INFINITY;
-                    s[nt][e] = v;
-                    if (e < 2) max_a = fmaxf(max_a, v); else max_b = fmaxf(max_b, v);
-                }
+                    for (int e = 0; e < 4; ++e) {
+                        const float v = s[nt][e] * scale_log2;
+                        s[nt][e] = v;
+                        if (e < 2) max_a = fmaxf(max_a, v); else max_b = fmaxf(max_b, v);
+                    }
+            } else {
+#pragma unroll
+                for (int nt = 0; nt < 8; ++nt)
+#pragma unroll
+                    for (int e = 0; e < 4; ++e) {
+                        const int kp = k0 + nt * 8 + (lane & 3) * 2 + (e & 1);
+                        const int q_pos = e < 2 ? pos_a : pos_b;
+                        bool visible = kp <= q_pos;
+                        if (window > 0) visible = visible && (kp > q_pos - window);
+                        const float v = visible ? s[nt][e] * scale_log2 : -INFINITY;
+                        s[nt][e] = v;
+                        if (e < 2) max_a = fmaxf(max_a, v); else max_b = fmaxf(max_b, v);
+                    }
+            }
             max_a = quad_max(max_a);
             max_b = quad_max(max_b);
             const float new_a = fmaxf(m_a, max_a), new_b = fmaxf(m_b, max_b);

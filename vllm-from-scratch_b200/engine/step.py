@@ -21,6 +21,7 @@ from dataclasses import dataclass, field
 import numpy as np
 import torch
 
+from .. import kernels
 from ..cache import RELEASED, CacheManager, CacheStorage
 from ..parts.base import GroupContext, StepContext
 from ..parts.model import DecoderModel
@@ -44,6 +45,7 @@ class StepFunction:
         self.device = model.device
         self.page_size = storage.page_size
         self.last_context: StepContext | None = None     # kept for the packed-inputs trace
+        self._validated_shapes: set[tuple[int, int, int]] = set()
 
     # ------------------------------------------------------------------ packing
     def pack_host(self, entries: list[StepEntry], pad_requests: int | None = None,
@@ -146,7 +148,12 @@ class StepFunction:
         host, meta = self.pack_host(entries)
         ctx, token_ids, want_rows = self.context_from(host.to(self.device, non_blocking=True), meta)
         self.last_context = ctx
-        x, residual = self.model.forward(token_ids, ctx, self.storage.views)
-        if meta["num_wanted"] == 0:
-            return None
-        return self.model.logits(x, residual, want_rows)
+        # Operand checks run the first time a batch shape is seen; later steps of that
+        # shape go through the same code with the same sizes.
+        shape = (meta["num_tokens"], meta["num_requests"], meta["num_wanted"])
+        first_time = shape not in self._validated_shapes
+        with kernels.validation(first_time):
+            x, residual = self.model.forward(token_ids, ctx, self.storage.views)
+            logits = None if meta["num_wanted"] == 0 else self.model.logits(x, residual, want_rows)
+        self._validated_shapes.add(shape)
+        return logits

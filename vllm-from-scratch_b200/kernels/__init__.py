@@ -11,6 +11,7 @@ minivllm/layers/quantization/methods.py:36-37.)
 from __future__ import annotations
 
 import ctypes
+import os
 from typing import Sequence
 
 import torch
@@ -31,6 +32,29 @@ def _code(dtype: torch.dtype) -> int:
         raise KernelError(f"kernels are built for float32 and bfloat16, not {dtype}") from None
 
 
+# Full validation of every operand costs a few microseconds per launch.  The engine's
+# own step function switches it off (``validation(False)``) once a batch shape has run
+# with it on; everything else (tests, parts written by users, direct calls) keeps it.
+# The environment variable B200_VALIDATE=1 keeps it on everywhere.
+_validate = True
+
+
+class validation:
+    """Context manager: ``with validation(False): ...`` skips operand checks inside."""
+
+    def __init__(self, enabled: bool) -> None:
+        self.enabled = enabled or os.environ.get("B200_VALIDATE") == "1"
+
+    def __enter__(self):
+        global _validate
+        self.previous, _validate = _validate, self.enabled
+        return self
+
+    def __exit__(self, *exc):
+        global _validate
+        _validate = self.previous
+
+
 def _check(name: str, tensor: torch.Tensor | None, dtype: torch.dtype | Sequence[torch.dtype] | None = None,
            shape: Sequence[int | None] | None = None, optional: bool = False) -> int:
     """Validate one operand and return its device address (0 for an absent optional)."""
@@ -38,6 +62,8 @@ def _check(name: str, tensor: torch.Tensor | None, dtype: torch.dtype | Sequence
         if optional:
             return 0
         raise KernelError(f"{name}: tensor is required")
+    if not _validate:
+        return tensor.data_ptr()
     if not tensor.is_cuda:
         raise KernelError(
             f"{name}: tensor lives on {tensor.device}; the engine's kernels run on a CUDA device only")
@@ -54,7 +80,7 @@ def _check(name: str, tensor: torch.Tensor | None, dtype: torch.dtype | Sequence
 
 
 def _stream() -> ctypes.c_void_p:
-    return ctypes.c_void_p(torch.cuda.current_stream().cuda_stream)
+    return ctypes.c_void_p(torch._C._cuda_getCurrentRawStream(torch.cuda.current_device()))
 
 
 launch_count = 0        # kernel launchers called so far (the benchmark reports the difference)

@@ -19,12 +19,19 @@ _P, _I, _F = ctypes.c_void_p, ctypes.c_int, ctypes.c_float
 
 
 def decode_splits(num_requests: int, num_kv_heads: int, max_seq_len: int) -> int:
-    """Over how many blocks the keys of one (request, key/value head) are split:
-    enough blocks to fill the GPU a few times over, each with at least 256 keys."""
+    """Over how many blocks the keys of one (request, key/value head) are split.
+    Three blocks fit on an SM at a time; the split is chosen so that the blocks fill
+    whole rounds of the GPU (a last round with few blocks would leave it idle), with
+    at least 512 keys per block at the planned length."""
     pairs = max(1, num_requests * num_kv_heads)
-    wanted = -(-4 * NUM_SMS // pairs)
-    by_length = max(1, max_seq_len // 256)
-    return max(1, min(wanted, by_length, 64))
+    slots = 3 * NUM_SMS
+    best, best_fill = 1, 0.0
+    for splits in range(1, max(1, min(16, max_seq_len // 512)) + 1):
+        blocks = pairs * splits
+        fill = blocks / (-(-blocks // slots) * slots) - 0.002 * splits     # a split more costs a little
+        if fill > best_fill:
+            best, best_fill = splits, fill
+    return best
 
 
 def paged_attention_bf16(q, k_pages, v_pages, out, query_start, seq_lens, block_table, num_q_heads,
