@@ -309,3 +309,37 @@ def test_gated_silu_gemm(m, inter, k_, dtype):
     plain_ops.gated_silu_gemm(x, w, out_b)
     bound = float(out_b.float().abs().max()) * (2 ** -7 if dtype == torch.bfloat16 else 1e-5)
     assert float((out_a.float() - out_b.float()).abs().max()) <= bound
+
+
+@pytest.mark.parametrize("m,n,k_", [(1, 256, 128), (8, 4096, 2048), (16, 2048, 6144), (17, 1000, 264), (64, 12288, 2048),
+                                    (100, 503, 96), (256, 384, 512), (5, 151936, 256)])
+@pytest.mark.parametrize("out_dtype", [torch.bfloat16, torch.float32])
+def test_tensor_memory_gemm(m, n, k_, out_dtype):
+    """The tcgen05 / TMA kernel against a float64 product; no bounded wait may run out."""
+    from vllm_from_scratch_b200.kernels import gemm_bf16
+    g = torch.Generator(device="cuda").manual_seed(m + n + k_)
+    x = torch.randn(m, k_, device="cuda", generator=g).bfloat16()
+    w = torch.randn(n, k_, device="cuda", generator=g).bfloat16()
+    out = torch.full((m, n), 7.0, device="cuda", dtype=out_dtype)
+    for _ in range(2):                               # twice: the tile counters must reset themselves
+        gemm_bf16.tc_gemm_bf16(x, w, out)
+    assert gemm_bf16.device_error_code() == 0
+    exact = x.double() @ w.double().T
+    scale = float(exact.abs().max())
+    bound = scale * (2 ** -8 if out_dtype == torch.bfloat16 else 1e-5)
+    assert float((out.double() - exact).abs().max()) <= bound
+
+
+@pytest.mark.parametrize("m,inter,k_", [(1, 256, 128), (8, 6144, 2048), (33, 1000, 320), (64, 1536, 1024)])
+def test_tensor_memory_gated_gemm(m, inter, k_):
+    from vllm_from_scratch_b200.kernels import gemm_bf16
+    g = torch.Generator(device="cuda").manual_seed(m + inter)
+    x = torch.randn(m, k_, device="cuda", generator=g).bfloat16()
+    w = (torch.randn(2 * inter, k_, device="cuda", generator=g) * 0.1).bfloat16()
+    out = torch.empty(m, inter, device="cuda", dtype=torch.bfloat16)
+    expected = torch.empty_like(out)
+    gemm_bf16.tc_gemm_bf16(x, w, out, gated=True)
+    assert gemm_bf16.device_error_code() == 0
+    plain_ops.gated_silu_gemm(x, w, expected)
+    bound = float(expected.float().abs().max()) * 2 ** -7
+    assert float((out.float() - expected.float()).abs().max()) <= bound

@@ -18,6 +18,11 @@
 
 #include "common.cuh"
 #include "stream_gemm.cuh"
+#include "tc_gemm.cuh"
+
+#include <map>
+#include <mutex>
+#include <tuple>
 
 namespace b200 {
 
@@ -254,6 +259,136 @@ B200_EXPORT int b200_stream_gemm_error() {
         cudaMemcpyToSymbol(b200::g_stream_error, &zero, sizeof(int));
     }
     return code;
+}
+
+namespace b200 {
+
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                                  const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
+                                  CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+// The driver's tensor-map encoder, found through the runtime (no link against libcuda).
+inline EncodeTiledFn encode_tiled() {
+    static EncodeTiledFn fn = nullptr;
+    if (fn == nullptr) {
+        void* found = nullptr;
+        cudaDriverEntryPointQueryResult result;
+        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &found, cudaEnableDefault, &result) == cudaSuccess &&
+            result == cudaDriverEntryPointSuccess)
+            fn = reinterpret_cast<EncodeTiledFn>(found);
+    }
+    return fn;
+}
+
+// Tensor map of a row-major bfloat16 matrix [rows, K] with boxes of 64 columns (128 bytes,
+// swizzled) x box_rows rows; rows outside the matrix read as zeros.  Maps are cached by
+// (address, rows, K, box_rows): weights keep theirs for the life of the process.
+inline const CUtensorMap* tensor_map_for(const void* base, int rows, int K, int box_rows) {
+    static std::map<std::tuple<const void*, int, int, int>, CUtensorMap> cache;
+    static std::mutex guard;
+    std::lock_guard<std::mutex> lock(guard);
+    const auto key = std::make_tuple(base, rows, K, box_rows);
+    auto it = cache.find(key);
+    if (it != cache.end()) return &it->second;
+    EncodeTiledFn encode = encode_tiled();
+    if (encode == nullptr) return nullptr;
+    if (cache.size() > 4096) cache.clear();
+    CUtensorMap map;
+    const cuuint64_t dims[2] = {(cuuint64_t)K, (cuuint64_t)rows};
+    const cuuint64_t strides[1] = {(cuuint64_t)K * 2};
+    const cuuint32_t box[2] = {(cuuint32_t)kTcK, (cuuint32_t)box_rows};
+    const cuuint32_t element_strides[2] = {1, 1};
+    const CUresult status = encode(&map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(base), dims, strides,
+                                   box, element_strides, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
+                                   CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    if (status != CUDA_SUCCESS) return nullptr;
+    return &cache.emplace(key, map).first->second;
+}
+
+struct TcPlan {
+    int ntok, stages, splits, steps_per_split, row_tiles, smem;
+};
+
+inline TcPlan tc_plan(int M, int N, int K, bool gated) {
+    TcPlan plan;
+    plan.ntok = ((M + 15) / 16) * 16;
+    const int stage = kTcATile + plan.ntok * kTcK * 2;
+    plan.stages = 8;
+    while (plan.stages > 2 && TcLayout(plan.stages, plan.ntok).total(gated) > 112 * 1024) --plan.stages;
+    plan.smem = TcLayout(plan.stages, plan.ntok).total(gated);
+    const int rows_per_tile = gated ? 64 : kTcRows;
+    plan.row_tiles = (N + rows_per_tile - 1) / rows_per_tile;
+    const int total_steps = (K + kTcK - 1) / kTcK;
+    // Enough blocks for two per SM; the split depends on the matrix only, never on the
+    // number of tokens, so a token's sums are formed the same way in every batch.
+    int splits = (2 * 148 + plan.row_tiles - 1) / plan.row_tiles;
+    if (splits > 16) splits = 16;
+    if (splits > total_steps / 2) splits = total_steps / 2;
+    if (splits < 1) splits = 1;
+    plan.steps_per_split = (total_steps + splits - 1) / splits;
+    plan.splits = (total_steps + plan.steps_per_split - 1) / plan.steps_per_split;
+    (void)stage;
+    return plan;
+}
+
+template <bool GATED, typename OutT>
+int launch_tc(const bf16* x, const bf16* w, OutT* y, float* scratch, int* counters, int M, int N, int K,
+              int w_rows, int* error_flag, cudaStream_t stream) {
+    const TcPlan plan = tc_plan(M, N, K, GATED);
+    const CUtensorMap* map_w = tensor_map_for(w, w_rows, K, GATED ? 64 : kTcRows);
+    const CUtensorMap* map_x = tensor_map_for(x, M, K, plan.ntok);
+    if (map_w == nullptr || map_x == nullptr) return fail("tc_gemm", "could not encode a tensor map");
+    auto kernel = tc_gemm_kernel<GATED, OutT>;
+    cudaError_t status = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, plan.smem);
+    if (status != cudaSuccess) return fail("tc_gemm", cudaGetErrorString(status));
+    dim3 grid(plan.row_tiles, plan.splits);
+    kernel<<<grid, 128, plan.smem, stream>>>(*map_w, *map_x, scratch, counters, y, M, N, K, plan.ntok, plan.stages,
+                                             plan.steps_per_split, GATED ? N : 0, error_flag);
+    return check_launch("tc_gemm");
+}
+
+}  // namespace b200
+
+// What the tcgen05 product needs of its caller for a shape: number of K splits (scratch
+// must hold splits * M * width floats when splits > 1, width = N, or 2 N for the gated
+// product) and of row tiles (one zeroed int counter each).  Returns 0 if the shape is not
+// one this kernel takes.
+B200_EXPORT int b200_tc_gemm_plan(int M, int N, int K, int gated, int* splits, int* row_tiles) {
+    if (M < 1 || M > 256 || K < 64 || K % 8 != 0 || N < 1) return 0;
+    const b200::TcPlan plan = b200::tc_plan(M, N, K, gated != 0);
+    *splits = plan.splits;
+    *row_tiles = plan.row_tiles;
+    return 1;
+}
+
+// y[M, N] = x[M, K] . w[N, K]^T (gated_inter = 0), or y[M, I] = silu(x w[:I]^T) * (x w[I:]^T)
+// with w of 2 I rows (gated_inter = I, N = 2 I).  out_dtype: 0 float32, 1 bfloat16.
+B200_EXPORT int b200_tc_gemm_bf16(const void* x, const void* w, void* y, float* scratch, int* counters, int M,
+                                  int N, int K, int gated_inter, int out_dtype, cudaStream_t stream) {
+    using namespace b200;
+    if (M == 0 || N == 0) return 0;
+    if (M < 1 || M > 256 || K < 64 || K % 8 != 0) return fail("tc_gemm", "needs 1 <= M <= 256 and K >= 64, a multiple of 8");
+    if (((uintptr_t)x | (uintptr_t)w) & 15) return fail("tc_gemm", "operands must be 16-byte aligned");
+    if (gated_inter > 0 && N != 2 * gated_inter) return fail("tc_gemm", "gated product needs N = 2 * inter");
+    if (out_dtype != 0 && out_dtype != 1) return fail("tc_gemm", "out_dtype must be 0 (float32) or 1 (bfloat16)");
+    static int* error_flag[64] = {};
+    int device = 0;
+    if (cudaGetDevice(&device) != cudaSuccess || device < 0 || device >= 64) return fail("tc_gemm", "no device");
+    if (error_flag[device] == nullptr) {
+        void* found = nullptr;
+        if (cudaGetSymbolAddress(&found, g_stream_error) != cudaSuccess) return fail("tc_gemm", "no error flag");
+        error_flag[device] = static_cast<int*>(found);
+    }
+    const bf16* xb = (const bf16*)x;
+    const bf16* wb = (const bf16*)w;
+    if (gated_inter > 0) {
+        if (out_dtype == 1)
+            return launch_tc<true, bf16>(xb, wb, (bf16*)y, scratch, counters, M, gated_inter, K, N, error_flag[device], stream);
+        return launch_tc<true, float>(xb, wb, (float*)y, scratch, counters, M, gated_inter, K, N, error_flag[device], stream);
+    }
+    if (out_dtype == 1)
+        return launch_tc<false, bf16>(xb, wb, (bf16*)y, scratch, counters, M, N, K, N, error_flag[device], stream);
+    return launch_tc<false, float>(xb, wb, (float*)y, scratch, counters, M, N, K, N, error_flag[device], stream);
 }
 
 // Largest M and the divisibility of K the few-rows kernel takes.

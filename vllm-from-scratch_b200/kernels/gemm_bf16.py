@@ -54,3 +54,45 @@ def gated_silu_gemm_bf16(x: torch.Tensor, w_gate_up: torch.Tensor, out: torch.Te
         return False
     _skinny(x, w_gate_up, out, out.shape[1])
     return True
+
+
+# ------------------------------------------------------------ tcgen05 product
+_counters: dict[int, torch.Tensor] = {}
+
+
+def tc_gemm_supported(m: int, n: int, k: int) -> bool:
+    return 1 <= m <= 256 and k >= 64 and k % 8 == 0 and n >= 1
+
+
+def tc_gemm_bf16(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, gated: bool = False) -> None:
+    """The tensor-memory kernel (tc_gemm.cuh): ``out = x @ w^T``, or with ``gated``
+    ``out = silu(x @ w[:I]^T) * (x @ w[I:]^T)``.  Allocates the float32 scratch of a
+    split K product itself; the per-tile counters live for the life of the process."""
+    from . import KernelError, _stream, count_launch
+    lib = load_library("gemm_bf16")
+    m, k = x.shape
+    n = w.shape[0]
+    splits, tiles = ctypes.c_int(0), ctypes.c_int(0)
+    if not lib.b200_tc_gemm_plan(_I(m), _I(n // 2 if gated else n), _I(k), _I(1 if gated else 0),
+                                 ctypes.byref(splits), ctypes.byref(tiles)):
+        raise KernelError(f"tc_gemm: shape M={m}, N={n}, K={k} is not taken")
+    device = x.device.index or 0
+    counters = _counters.get(device)
+    if counters is None or counters.numel() < tiles.value:
+        counters = _counters[device] = torch.zeros(max(8192, tiles.value), dtype=torch.int32, device=x.device)
+    scratch = None
+    if splits.value > 1:
+        scratch = torch.empty(splits.value * m * n, dtype=torch.float32, device=x.device)
+    status = lib.b200_tc_gemm_bf16(
+        _P(x.data_ptr()), _P(w.data_ptr()), _P(out.data_ptr()), _P(scratch.data_ptr() if scratch is not None else 0),
+        _P(counters.data_ptr()), _I(m), _I(n), _I(k), _I(n // 2 if gated else 0),
+        _I(1 if out.dtype == torch.bfloat16 else 0), _stream())
+    if status != 0:
+        raise KernelError(lib.b200_last_error().decode())
+    count_launch()
+
+
+def device_error_code() -> int:
+    """0, or the code left by a kernel whose bounded wait ran out (synchronises)."""
+    lib = load_library("gemm_bf16")
+    return int(lib.b200_stream_gemm_error())

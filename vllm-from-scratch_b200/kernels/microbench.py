@@ -83,6 +83,8 @@ def main(argv=None) -> int:
     parser.add_argument("--iters", type=int, default=10)
     parser.add_argument("--keep-l2", action="store_true")
     parser.add_argument("--gated", action="store_true", help="gemm: fused silu(gate) * up, N = 2 * inter")
+    parser.add_argument("--kernel", default="default", choices=("default", "tc", "library"),
+                        help="gemm: the engine's choice, the tcgen05 kernel, or the vendor library")
     args = parser.parse_args(argv)
     dtype = torch.bfloat16 if args.dtype == "bfloat16" else torch.float32
     size = 2 if dtype == torch.bfloat16 else 4
@@ -113,11 +115,15 @@ def main(argv=None) -> int:
         # back, each launch reads cold weights and the launch gaps are amortised.
         copies = max(1, min(64, (512 * 1024 * 1024) // (args.n * args.k * size)))
         ws = [torch.randn(args.n, args.k, device="cuda").to(dtype) for _ in range(copies)]
-        if args.gated:
-            out = torch.empty(args.m, args.n // 2, device="cuda", dtype=dtype)
+        out = torch.empty(args.m, args.n // 2 if args.gated else args.n, device="cuda", dtype=dtype)
+        if args.kernel == "tc":
+            from . import gemm_bf16
+            one = lambda w: gemm_bf16.tc_gemm_bf16(x, w, out, gated=args.gated)
+        elif args.kernel == "library":
+            one = lambda w: torch.mm(x, w.t(), out=out)
+        elif args.gated:
             one = lambda w: kernels.gated_silu_gemm(x, w, out)
         else:
-            out = torch.empty(args.m, args.n, device="cuda", dtype=dtype)
             one = lambda w: kernels.gemm(x, w, out)
 
         def sweep():
