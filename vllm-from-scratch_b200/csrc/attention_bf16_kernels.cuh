@@ -129,6 +129,8 @@ __global__ void __launch_bounds__(kThreads) decode_attention_kernel(
     int nkv, int page_size, float scale_log2, int window, int splits) {
     extern __shared__ __align__(128) unsigned char smem_raw[];
     bf16* stage_base = reinterpret_cast<bf16*>(smem_raw);
+    overlap_trigger();
+    overlap_wait();
     const int split = blockIdx.x, kv_head = blockIdx.y, request = blockIdx.z;
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
     const int group = nq / nkv;
@@ -281,6 +283,8 @@ __global__ void __launch_bounds__(kThreads) decode_attention_kernel(
 template <int D>
 __global__ void merge_splits_kernel(const float* __restrict__ partial_o, const float* __restrict__ partial_ml,
                                     bf16* __restrict__ out, int splits) {
+    overlap_trigger();
+    overlap_wait();
     const size_t head = blockIdx.x;
     float m_star = -INFINITY;
     for (int s = 0; s < splits; ++s) m_star = fmaxf(m_star, partial_ml[(head * splits + s) * 2]);
@@ -483,13 +487,13 @@ int launch_decode(const void* q, const void* k_pages, const void* v_pages, void*
     cudaError_t status = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
     if (status != cudaSuccess) return fail("decode_attention", cudaGetErrorString(status));
     dim3 grid(splits, nkv, num_requests);
-    kernel<<<grid, kThreads, smem, stream>>>(
+    launch_overlapped(kernel, grid, kThreads, smem, stream,
         (const bf16*)q, (const bf16*)k_pages, (const bf16*)v_pages, (bf16*)out, partial_o, partial_ml,
         seq_lens, block_table, max_pages, nq, nkv, page_size, scale * kLog2e, window, splits);
     if (int rc = check_launch("decode_attention")) return rc;
     if (splits > 1) {
-        merge_splits_kernel<D><<<num_requests * nq, D < 128 ? D : 128, 0, stream>>>(
-            partial_o, partial_ml, (bf16*)out, splits);
+        launch_overlapped(merge_splits_kernel<D>, num_requests * nq, D < 128 ? D : 128, 0, stream,
+                          (const float*)partial_o, (const float*)partial_ml, (bf16*)out, splits);
         return check_launch("merge_splits");
     }
     return 0;

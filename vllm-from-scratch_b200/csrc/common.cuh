@@ -8,6 +8,7 @@
 #include <cuda_runtime.h>
 #include <stdint.h>
 #include <stdio.h>
+#include <stdlib.h>
 
 #define B200_EXPORT extern "C" __attribute__((visibility("default")))
 
@@ -66,6 +67,40 @@ __device__ __forceinline__ float block_sum(float v, float* scratch) {
     float result = scratch[32];
     __syncthreads();
     return result;
+}
+
+// ---------------------------------------------------------------- overlapped launches
+// A decode step is a chain of some hundred short kernels.  Launched "overlapped"
+// (programmatic dependent launch), a kernel may be scheduled while its predecessor on
+// the stream is still draining: it runs up to `overlap_wait()` (which returns when the
+// predecessor has completed and its writes are visible), so everything before that
+// call (index arithmetic, barrier and tensor-memory set-up, loads of weights, which
+// no kernel writes) overlaps the predecessor's tail.  `overlap_trigger()` tells the
+// scheduler that the kernels after this one may start being scheduled.
+// A kernel launched this way must not read anything a predecessor writes, nor write
+// anything at all, before `overlap_wait()`.
+__device__ __forceinline__ void overlap_wait() { asm volatile("griddepcontrol.wait;\n" ::: "memory"); }
+__device__ __forceinline__ void overlap_trigger() { asm volatile("griddepcontrol.launch_dependents;\n" ::: "memory"); }
+
+inline bool overlap_enabled() {
+    static const bool enabled = getenv("B200_NO_OVERLAP") == nullptr;
+    return enabled;
+}
+
+template <typename... Params, typename... Args>
+inline void launch_overlapped(void (*kernel)(Params...), dim3 grid, dim3 block, size_t smem, cudaStream_t stream,
+                              Args... args) {
+    cudaLaunchConfig_t config = {};
+    config.gridDim = grid;
+    config.blockDim = block;
+    config.dynamicSmemBytes = smem;
+    config.stream = stream;
+    cudaLaunchAttribute attribute[1];
+    attribute[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attribute[0].val.programmaticStreamSerializationAllowed = overlap_enabled() ? 1 : 0;
+    config.attrs = attribute;
+    config.numAttrs = 1;
+    cudaLaunchKernelEx(&config, kernel, static_cast<Params>(args)...);
 }
 
 }  // namespace b200

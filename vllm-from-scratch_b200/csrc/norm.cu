@@ -66,6 +66,8 @@ __global__ void add_rmsnorm_vec_kernel(const T* __restrict__ x, float* __restric
                                        const int* __restrict__ rows, int hidden, float eps) {
     __shared__ float scratch[33];
     constexpr int kSteps = 4;
+    overlap_trigger();
+    overlap_wait();
     const int out_row = blockIdx.x;
     const int row = rows ? rows[out_row] : out_row;
     const size_t base = (size_t)row * hidden;
@@ -175,11 +177,11 @@ B200_EXPORT int b200_add_rmsnorm(const void* x, float* residual, const float* we
         while (threads < 1024 && threads * 16 < hidden) threads *= 2;      // at most four steps a thread
         while (threads < 256 && threads * 4 < hidden) threads *= 2;        // short rows: one step a thread
         if (dtype == 0)
-            add_rmsnorm_vec_kernel<float><<<num_rows, threads, 0, stream>>>(
-                (const float*)x, residual, weight, (float*)out, rows, hidden, eps);
+            launch_overlapped(add_rmsnorm_vec_kernel<float>, num_rows, threads, 0, stream,
+                              (const float*)x, residual, weight, (float*)out, rows, hidden, eps);
         else
-            add_rmsnorm_vec_kernel<__nv_bfloat16><<<num_rows, threads, 0, stream>>>(
-                (const __nv_bfloat16*)x, residual, weight, (__nv_bfloat16*)out, rows, hidden, eps);
+            launch_overlapped(add_rmsnorm_vec_kernel<__nv_bfloat16>, num_rows, threads, 0, stream,
+                              (const __nv_bfloat16*)x, residual, weight, (__nv_bfloat16*)out, rows, hidden, eps);
         return check_launch("add_rmsnorm");
     }
     const int threads = norm_threads(hidden);

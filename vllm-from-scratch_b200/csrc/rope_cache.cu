@@ -22,6 +22,8 @@ __global__ void head_norm_rope_cache_kernel(
     const float* __restrict__ q_weight, const float* __restrict__ k_weight,
     const float* __restrict__ inv_freq, T* __restrict__ q_out, T* __restrict__ k_pages,
     T* __restrict__ v_pages, int nq, int nkv, int d, int rotary_dim, int page_size, float eps) {
+    overlap_trigger();
+    overlap_wait();
     const int token = blockIdx.x;
     const int warps = blockDim.x >> 5;
     const int head_slot = blockIdx.y * warps + (threadIdx.x >> 5);
@@ -101,11 +103,11 @@ B200_EXPORT int b200_head_norm_rope_cache(
     dim3 grid(num_tokens, (total_heads + warps - 1) / warps);
     if (grid.y > 65535) return fail("head_norm_rope_cache", "too many heads");
     if (dtype == 0)
-        head_norm_rope_cache_kernel<float><<<grid, warps * 32, 0, stream>>>(
+        launch_overlapped(head_norm_rope_cache_kernel<float>, grid, warps * 32, 0, stream,
             (const float*)qkv, positions, slots, q_weight, k_weight, inv_freq, (float*)q_out,
             (float*)k_pages, (float*)v_pages, nq, nkv, d, rotary_dim, page_size, eps);
     else if (dtype == 1)
-        head_norm_rope_cache_kernel<__nv_bfloat16><<<grid, warps * 32, 0, stream>>>(
+        launch_overlapped(head_norm_rope_cache_kernel<__nv_bfloat16>, grid, warps * 32, 0, stream,
             (const __nv_bfloat16*)qkv, positions, slots, q_weight, k_weight, inv_freq,
             (__nv_bfloat16*)q_out, (__nv_bfloat16*)k_pages, (__nv_bfloat16*)v_pages, nq, nkv, d,
             rotary_dim, page_size, eps);
