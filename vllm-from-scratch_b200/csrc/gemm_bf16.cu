@@ -64,6 +64,7 @@ __global__ void __launch_bounds__(kSkinnyMaxWarps * 32) skinny_gemm_kernel(
     const bf16* __restrict__ x, const bf16* __restrict__ w, OutT* __restrict__ y, int M, int N, int K,
     int up_offset) {
     __shared__ float partial[kSkinnyMaxWarps][TILES][32][4];
+    overlap_trigger();
     const int kSkinnyWarps = blockDim.x >> 5;
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
     const int g = lane >> 2, t = lane & 3;
@@ -87,6 +88,7 @@ __global__ void __launch_bounds__(kSkinnyMaxWarps * 32) skinny_gemm_kernel(
 
     const int blocks = K >> 5;                          // K is a multiple of 32
     constexpr int kUnroll = UNROLL;
+    overlap_wait();                                     // the token rows come from the kernel before this one
     const uint4 zero = make_uint4(0, 0, 0, 0);
     int j = warp;
     for (; j + (kUnroll - 1) * kSkinnyWarps < blocks; j += kUnroll * kSkinnyWarps) {
@@ -185,11 +187,11 @@ int launch_skinny(const bf16* x, const bf16* w, OutT* y, int M, int N, int K, in
     if (const char* forced = getenv("B200_SKINNY_WARPS")) warps = atoi(forced);
     const int threads = warps * 32;
     if (gated_inter > 0) {
-        skinny_gemm_kernel<2, true, OutT, 4><<<ctas, threads, 0, stream>>>(x, w, y, M, gated_inter, K, gated_inter);
+        launch_overlapped(skinny_gemm_kernel<2, true, OutT, 4>, ctas, threads, 0, stream, x, w, y, M, gated_inter, K, gated_inter);
     } else if (two_tiles) {
-        skinny_gemm_kernel<2, false, OutT, 4><<<ctas, threads, 0, stream>>>(x, w, y, M, N, K, 0);
+        launch_overlapped(skinny_gemm_kernel<2, false, OutT, 4>, ctas, threads, 0, stream, x, w, y, M, N, K, 0);
     } else {
-        skinny_gemm_kernel<1, false, OutT, 8><<<ctas, threads, 0, stream>>>(x, w, y, M, N, K, 0);
+        launch_overlapped(skinny_gemm_kernel<1, false, OutT, 8>, ctas, threads, 0, stream, x, w, y, M, N, K, 0);
     }
     return check_launch("skinny_gemm");
 }
