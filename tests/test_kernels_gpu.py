@@ -281,18 +281,18 @@ def test_decode_attention_same_for_any_split():
 def test_few_rows_gemm(m, n, k_, out_dtype):
     """The weight-streaming kernel (M <= 16): exact float64 reference, and a token's
     result must not depend on the other tokens of the launch."""
-    k = kernels()
+    from vllm_from_scratch_b200.kernels import gemm_bf16
     g = torch.Generator(device="cuda").manual_seed(m + n + k_)
     x = torch.randn(m, k_, device="cuda", generator=g).bfloat16()
     w = torch.randn(n, k_, device="cuda", generator=g).bfloat16()
     out = torch.full((m, n), 7.0, device="cuda", dtype=out_dtype)
-    k.gemm(x, w, out)
+    gemm_bf16._skinny(x, w, out, 0)
     exact = x.double() @ w.double().T
     scale = float(exact.abs().max())
     bound = scale * (2 ** -8 if out_dtype == torch.bfloat16 else 1e-5)
     assert float((out.double() - exact).abs().max()) <= bound
     alone = torch.empty(1, n, device="cuda", dtype=out_dtype)
-    k.gemm(x[m - 1:m].clone(), w, alone)
+    gemm_bf16._skinny(x[m - 1:m].clone(), w, alone, 0)
     assert torch.equal(alone[0], out[m - 1])
 
 
@@ -309,6 +309,12 @@ def test_gated_silu_gemm(m, inter, k_, dtype):
     plain_ops.gated_silu_gemm(x, w, out_b)
     bound = float(out_b.float().abs().max()) * (2 ** -7 if dtype == torch.bfloat16 else 1e-5)
     assert float((out_a.float() - out_b.float()).abs().max()) <= bound
+    if dtype == torch.bfloat16 and m <= 16 and k_ % 32 == 0:
+        # the fused few-rows kernel itself, whatever the dispatch above chose
+        from vllm_from_scratch_b200.kernels import gemm_bf16
+        fused = torch.empty_like(out_a)
+        gemm_bf16._skinny(x, w, fused, inter)
+        assert float((fused.float() - out_b.float()).abs().max()) <= bound
 
 
 @pytest.mark.parametrize("m,n,k_", [(1, 256, 128), (8, 4096, 2048), (16, 2048, 6144), (17, 1000, 264), (64, 12288, 2048),

@@ -29,6 +29,17 @@ TINY_C = {
     "layer_types": ["full_attention", "sliding_attention", "sliding_attention", "full_attention"],
 }
 
+# Head size 64 and widths that are multiples of 32: in bfloat16 this one runs on the
+# tensor-core attention kernels and the few-rows product, which the smaller head sizes
+# above do not reach.
+TINY_D = {
+    "architectures": ["Qwen3ForCausalLM"], "model_type": "qwen3",
+    "num_hidden_layers": 2, "hidden_size": 256, "num_attention_heads": 8, "num_key_value_heads": 2,
+    "head_dim": 64, "intermediate_size": 416, "vocab_size": 777, "rope_theta": 1000000.0,
+    "rms_norm_eps": 1e-6, "tie_word_embeddings": True, "max_position_embeddings": 1024,
+    "hidden_act": "silu", "attention_bias": False, "initializer_range": 0.02,
+}
+
 # Larger standard deviations than a checkpoint's, so that attention scores and
 # logits are far from uniform and a wrong key or a wrong page shows in the result.
 INIT = {"std": 0.08, "norm_std": 0.1}

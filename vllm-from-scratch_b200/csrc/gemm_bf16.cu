@@ -178,7 +178,7 @@ int launch_skinny(const bf16* x, const bf16* w, OutT* y, int M, int N, int K, in
     // The GPU should hold a few thousand warps, each with all of its loads in flight:
     // the fewer blocks a product has, the more warps split K inside each block.
     const int k_blocks = K >> 5;
-    const bool two_tiles = gated_inter > 0 || N >= 148 * 4 * 16;
+    const bool two_tiles = gated_inter > 0 || (N >= 148 * 4 * 16 && getenv("B200_SKINNY_ONE_TILE") == nullptr);
     const int ctas = gated_inter > 0 ? (gated_inter + 7) / 8 : two_tiles ? (N + 15) / 16 : (N + 7) / 8;
     const int wanted = 6144 / (ctas * (two_tiles ? 2 : 1));
     int warps = 4;
@@ -325,6 +325,7 @@ inline TcPlan tc_plan(int M, int N, int K, bool gated) {
     // number of tokens, so a token's sums are formed the same way in every batch.
     int splits = (2 * 148 + plan.row_tiles - 1) / plan.row_tiles;
     if (splits > 16) splits = 16;
+    if (const char* forced = getenv("B200_TC_SPLITS")) splits = atoi(forced);
     if (splits > total_steps / 2) splits = total_steps / 2;
     if (splits < 1) splits = 1;
     plan.steps_per_split = (total_steps + splits - 1) / splits;

@@ -1,9 +1,11 @@
 """bfloat16 matrix products with float32 accumulation.
 
-Up to 16 rows (decode steps of small batches): the engine's own weight-streaming
-kernel, optionally with the gated SiLU fused in.  More rows: the vendor's library
-through ``torch.mm``, as the reference's ``F.linear`` does
-(minivllm/layers/quantization/methods.py:36-37).
+Few rows and a matrix of moderate height (decode steps of small batches): the
+engine's own weight-streaming kernel, optionally with the gated SiLU fused in.
+Otherwise the vendor's library through ``torch.mm``, as the reference's ``F.linear``
+does (minivllm/layers/quantization/methods.py:36-37).  A tcgen05 / tensor-memory
+kernel for up to 256 rows is built and tested (``tc_gemm_bf16``) but is not chosen
+by default: its 128-row tiles leave too few blocks for matrices of this size.
 """
 
 from __future__ import annotations
@@ -18,12 +20,19 @@ from ..csrc.build import load_library
 # add them up in bfloat16.
 torch.backends.cuda.matmul.allow_bf16_reduced_precision_reduction = False
 
-SKINNY_MAX_ROWS = 16
+# Where the engine's own few-rows kernel is the faster one (CUDA-graph timings on B200,
+# cold weights): up to 8 rows and up to 8192 weight rows it takes 7.3 / 11.1 / 6.1 us on
+# 4096 x 2048, 2048 x 6144 and 2048 x 2048 against the library's 7.3 / 15.0 / 6.6 us; on
+# wider matrices (12288 x 2048: 15.5 us against 10.1 us) and from 9 rows on the library's
+# kernels are ahead and are used.
+SKINNY_MAX_ROWS = 8
+SKINNY_MAX_WEIGHT_ROWS = 8192
 _P, _I = ctypes.c_void_p, ctypes.c_int
 
 
-def _skinny_ok(m: int, k: int, *tensors: torch.Tensor) -> bool:
-    return 1 <= m <= SKINNY_MAX_ROWS and k >= 32 and k % 32 == 0 and all(t.data_ptr() % 16 == 0 for t in tensors)
+def _skinny_ok(m: int, n: int, k: int, *tensors: torch.Tensor) -> bool:
+    return (1 <= m <= SKINNY_MAX_ROWS and n <= SKINNY_MAX_WEIGHT_ROWS and k >= 32 and k % 32 == 0
+            and all(t.data_ptr() % 16 == 0 for t in tensors))
 
 
 def _skinny(x, w, out, gated_inter: int) -> None:
@@ -38,7 +47,7 @@ def _skinny(x, w, out, gated_inter: int) -> None:
 
 
 def gemm_bf16(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor) -> None:
-    if _skinny_ok(x.shape[0], x.shape[1], x, w, out):
+    if _skinny_ok(x.shape[0], w.shape[0], x.shape[1], x, w, out):
         _skinny(x, w, out, 0)
     elif out.dtype == torch.bfloat16:
         torch.mm(x, w.t(), out=out)
@@ -50,7 +59,7 @@ def gemm_bf16(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor) -> None:
 def gated_silu_gemm_bf16(x: torch.Tensor, w_gate_up: torch.Tensor, out: torch.Tensor) -> bool:
     """``out = silu(x w[:I]^T) * (x w[I:]^T)`` in one kernel; False if the shape is
     not one the fused kernel takes (the caller then does it in two steps)."""
-    if not _skinny_ok(x.shape[0], x.shape[1], x, w_gate_up, out):
+    if not _skinny_ok(x.shape[0], w_gate_up.shape[0], x.shape[1], x, w_gate_up, out):
         return False
     _skinny(x, w_gate_up, out, out.shape[1])
     return True
