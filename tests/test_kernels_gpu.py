@@ -349,3 +349,31 @@ def test_tensor_memory_gated_gemm(m, inter, k_):
     plain_ops.gated_silu_gemm(x, w, expected)
     bound = float(expected.float().abs().max()) * 2 ** -7
     assert float((out.float() - expected.float()).abs().max()) <= bound
+
+
+TENSOR_MEMORY_ATTENTION_SHAPES = [
+    # nq, nkv, d, page, q_lens, seq_lens, window
+    (2, 1, 128, 16, [128], [128], None),
+    (16, 8, 128, 16, [300], [300], None),
+    (4, 2, 128, 16, [200, 1, 64, 3], [200, 500, 300, 131], None),
+    (8, 2, 128, 32, [130, 70], [130, 1000], None),
+    (6, 3, 128, 8, [333], [1500], 256),
+    (4, 4, 128, 128, [257, 64], [257, 640], None),
+]
+
+
+@pytest.mark.parametrize("shape", TENSOR_MEMORY_ATTENTION_SHAPES)
+def test_tensor_memory_attention(shape):
+    """The tcgen05 kernel for portions of prompts against the plain reference."""
+    from vllm_from_scratch_b200.kernels import attention_bf16
+    nq, nkv, d, page, q_lens, seq_lens, window = shape
+    for standout in (False, True):
+        q, kp, vp, start, seq, table = _attention_case(torch.bfloat16, nq, nkv, d, page, q_lens, seq_lens,
+                                                       window, seed=nq + page, standout=standout)
+        out_a = torch.zeros_like(q)
+        out_b = torch.zeros_like(q)
+        args = (start, seq, table, nq, nkv, d, page, d ** -0.5, window, max(q_lens), max(seq_lens))
+        assert attention_bf16.paged_attention_bf16(q, kp, vp, out_a, *args)
+        assert attention_bf16.attention_error_code() == 0
+        plain_ops.paged_attention(q, kp, vp, out_b, *args)
+        close(out_a, out_b, torch.bfloat16, scale=2, what=f"tensor-memory attention standout={standout}")

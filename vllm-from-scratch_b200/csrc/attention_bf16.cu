@@ -1,6 +1,8 @@
 // Exported launchers of the bfloat16 tensor-core attention kernels; the kernels
 // themselves are in attention_bf16_kernels.cuh.
 #include "attention_bf16_kernels.cuh"
+#include "attention_tc.cuh"
+#include "tensor_map.cuh"
 
 // Returns 1 if head_dim / head counts are ones these kernels are built for.
 B200_EXPORT int b200_attention_bf16_supports(int nq, int nkv, int d) {
@@ -44,4 +46,56 @@ B200_EXPORT int b200_prefill_attention_bf16(
     B200_CASE(64) B200_CASE(128) B200_CASE(256)
 #undef B200_CASE
     return fail("prefill_attention", "head_dim not built");
+}
+
+namespace b200 {
+// Set by a kernel whose bounded wait ran out (0 = never); read and cleared by b200_attention_error().
+__device__ int g_attention_error;
+}  // namespace b200
+
+B200_EXPORT int b200_attention_error() {
+    int code = 0;
+    if (cudaMemcpyFromSymbol(&code, b200::g_attention_error, sizeof(int)) != cudaSuccess) return -1;
+    if (code != 0) {
+        const int zero = 0;
+        cudaMemcpyToSymbol(b200::g_attention_error, &zero, sizeof(int));
+    }
+    return code;
+}
+
+// 1 if the tcgen05 kernel takes this shape: head size 128, pages of 8, 16, 32, 64 or 128 keys.
+B200_EXPORT int b200_prefill_attention_tc_supports(int nq, int nkv, int d, int page_size) {
+    return d == 128 && nkv > 0 && nq % nkv == 0 && nq <= 65535 && page_size >= 8 && page_size <= 128 &&
+                   (page_size & (page_size - 1)) == 0
+               ? 1 : 0;
+}
+
+// The tensor-memory kernel for portions of prompts.  num_pages: pages in k_pages / v_pages.
+B200_EXPORT int b200_prefill_attention_tc_bf16(
+    const void* q, const void* k_pages, const void* v_pages, void* out, const int* query_start,
+    const int* seq_lens, const int* block_table, int num_requests, int num_tokens, int max_pages, int nq,
+    int nkv, int d, int page_size, int num_pages, float scale, int window, cudaStream_t stream) {
+    using namespace b200;
+    if (num_requests == 0 || num_tokens == 0) return 0;
+    if (!b200_prefill_attention_tc_supports(nq, nkv, d, page_size)) return fail("prefill_attention_tc", "shape not built");
+    static int* error_flag[64] = {};
+    int device = 0;
+    if (cudaGetDevice(&device) != cudaSuccess || device < 0 || device >= 64) return fail("prefill_attention_tc", "no device");
+    if (error_flag[device] == nullptr) {
+        void* found = nullptr;
+        if (cudaGetSymbolAddress(&found, g_attention_error) != cudaSuccess) return fail("prefill_attention_tc", "no error flag");
+        error_flag[device] = static_cast<int*>(found);
+    }
+    const CUtensorMap* map_q = tensor_map_for(q, num_tokens, nq * d, kAtRows);
+    const CUtensorMap* map_k = tensor_map_for(k_pages, num_pages * nkv * page_size, d, page_size);
+    const CUtensorMap* map_v = tensor_map_for(v_pages, num_pages * nkv * page_size, d, page_size);
+    if (map_q == nullptr || map_k == nullptr || map_v == nullptr)
+        return fail("prefill_attention_tc", "could not encode a tensor map");
+    cudaError_t status = cudaFuncSetAttribute(prefill_attention_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kAtSmem);
+    if (status != cudaSuccess) return fail("prefill_attention_tc", cudaGetErrorString(status));
+    dim3 grid(num_tokens / kAtRows + num_requests, nq);
+    prefill_attention_tc_kernel<<<grid, kAtThreads, kAtSmem, stream>>>(
+        *map_q, *map_k, *map_v, (__nv_bfloat16*)out, query_start, seq_lens, block_table, num_requests, max_pages,
+        nq, nkv, page_size, scale * kLog2e, window, error_flag[device]);
+    return check_launch("prefill_attention_tc");
 }

@@ -9,12 +9,14 @@ float32-arithmetic kernel, which takes every shape.
 from __future__ import annotations
 
 import ctypes
+import os
 
 import torch
 
 from ..csrc.build import load_library
 
 NUM_SMS = 148
+TC_MIN_QUERY_LEN = 64      # shorter portions go to the 64-row mma.sync kernel
 _P, _I, _F = ctypes.c_void_p, ctypes.c_int, ctypes.c_float
 
 
@@ -55,6 +57,14 @@ def paged_attention_bf16(q, k_pages, v_pages, out, query_start, seq_lens, block_
             _P(seq_lens.data_ptr()), _P(block_table.data_ptr()), _I(requests), _I(block_table.shape[1]),
             _I(num_q_heads), _I(num_kv_heads), _I(head_dim), _I(page_size), _F(scale), _I(window or 0),
             _I(splits), _stream())
+    elif (max_query_len >= TC_MIN_QUERY_LEN and os.environ.get("B200_NO_TC_ATTENTION") is None
+          and lib.b200_prefill_attention_tc_supports(num_q_heads, num_kv_heads, head_dim, page_size)):
+        # long portions of prompts: the tcgen05 / tensor-memory kernel
+        status = lib.b200_prefill_attention_tc_bf16(
+            _P(q.data_ptr()), _P(k_pages.data_ptr()), _P(v_pages.data_ptr()), _P(out.data_ptr()),
+            _P(query_start.data_ptr()), _P(seq_lens.data_ptr()), _P(block_table.data_ptr()), _I(requests),
+            _I(tokens), _I(block_table.shape[1]), _I(num_q_heads), _I(num_kv_heads), _I(head_dim),
+            _I(page_size), _I(k_pages.shape[0]), _F(scale), _I(window or 0), _stream())
     else:
         status = lib.b200_prefill_attention_bf16(
             _P(q.data_ptr()), _P(k_pages.data_ptr()), _P(v_pages.data_ptr()), _P(out.data_ptr()),
@@ -66,3 +76,8 @@ def paged_attention_bf16(q, k_pages, v_pages, out, query_start, seq_lens, block_
     from . import count_launch
     count_launch()
     return True
+
+
+def attention_error_code() -> int:
+    """0, or the code left by an attention kernel whose bounded wait ran out (synchronises)."""
+    return int(load_library("attention_bf16").b200_attention_error())
