@@ -86,14 +86,14 @@ B200_EXPORT int b200_prefill_attention_tc_bf16(
         if (cudaGetSymbolAddress(&found, g_attention_error) != cudaSuccess) return fail("prefill_attention_tc", "no error flag");
         error_flag[device] = static_cast<int*>(found);
     }
-    const CUtensorMap* map_q = tensor_map_for(q, num_tokens, nq * d, kAtRows);
+    const CUtensorMap* map_q = tensor_map_for(q, num_tokens, nq * d, kAtRows);   // one group of rows per copy
     const CUtensorMap* map_k = tensor_map_for(k_pages, num_pages * nkv * page_size, d, page_size);
     const CUtensorMap* map_v = tensor_map_for(v_pages, num_pages * nkv * page_size, d, page_size);
     if (map_q == nullptr || map_k == nullptr || map_v == nullptr)
         return fail("prefill_attention_tc", "could not encode a tensor map");
     cudaError_t status = cudaFuncSetAttribute(prefill_attention_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kAtSmem);
     if (status != cudaSuccess) return fail("prefill_attention_tc", cudaGetErrorString(status));
-    dim3 grid(num_tokens / kAtRows + num_requests, nq);
+    dim3 grid(num_tokens / kAtBlockRows + num_requests, nq);
     prefill_attention_tc_kernel<<<grid, kAtThreads, kAtSmem, stream>>>(
         *map_q, *map_k, *map_v, (__nv_bfloat16*)out, query_start, seq_lens, block_table, num_requests, max_pages,
         nq, nkv, page_size, scale * kLog2e, window, error_flag[device]);

@@ -1,9 +1,11 @@
 // Paged causal attention for portions of prompts on the 5th-generation tensor cores
 // (tcgen05, accumulators in tensor memory), head size 128, bfloat16.
 //
-// One block = 128 consecutive query tokens of one request x one query head; thread i
-// owns query row i, which is lane i of tensor memory, so the softmax needs no
-// exchange between threads.  Per tile of 128 keys:
+// One block = 256 consecutive query tokens of one request x one query head, as two
+// groups of 128 rows.  Each group has four softmax warps; a thread owns one query row,
+// which is one lane of tensor memory, so the softmax needs no exchange between threads,
+// and the two groups share every tile of keys and values.  A ninth warp requests the
+// copies and issues the MMAs.  Per tile of 128 keys and per group:
 //   S = Q K^T       8 x tcgen05.mma (M 128, N 128, K 16), Q and K from shared memory
 //                   (K-major, 128-byte swizzle, brought in by tensor copies page by page);
 //   softmax         each thread reads its row of S from tensor memory twice (maximum,
@@ -12,11 +14,11 @@
 //                   rescales its row of O in tensor memory when the maximum moved;
 //   O += P V        8 x tcgen05.mma with V read straight from its pages' layout
 //                   ([key][channel], i.e. the "MN-major" operand form).
-// tcgen05.commit after each batch of MMAs arrives on an mbarrier (one for the S batches,
-// one for the O batches); because the tensor pipe runs batches in order, "S of tile t is
-// ready" also means "P V of tile t - 1 is done", which frees the P buffer, the V stage
-// and O for rescaling.
-// Keys and values of tile t + 2 / t + 1 are requested while tile t is processed.
+// tcgen05.commit after each batch of MMAs arrives on an mbarrier (per group one for the S
+// batches, one for the O batches); because the tensor pipe runs batches in order, "S of
+// tile t is ready" also means "P V of tile t - 1 is done", which frees the P buffer, the
+// V stage and O for rescaling.  Keys of tile t + 2 and values of tile t are requested when
+// S of tile t is ready.
 // Masking and arguments are those of attention_generic.cu.  Waits are bounded.
 #pragma once
 
@@ -73,12 +75,13 @@ __device__ __forceinline__ void tmem_st32(unsigned taddr, const float (&v)[32]) 
         : "memory");
 }
 
-// Shared memory (offsets from a 1024-byte aligned base): Q 32 KB, P 32 KB, two stages of
-// K (32 KB each) and of V (32 KB each), barriers.
-constexpr int kAtQ = 0, kAtP = 2 * kAtHalf, kAtK = 4 * kAtHalf, kAtV = 8 * kAtHalf, kAtBars = 12 * kAtHalf;
+// Shared memory (offsets from a 1024-byte aligned base): Q 2 x 32 KB, P 2 x 32 KB, two
+// stages of K (32 KB each), one of V (32 KB), barriers.
+constexpr int kAtQ = 0, kAtP = 4 * kAtHalf, kAtK = 8 * kAtHalf, kAtV = 12 * kAtHalf, kAtBars = 14 * kAtHalf;
 constexpr int kAtSmem = kAtBars + 128 + 1024;
-
-constexpr int kAtThreads = 160;                 // four softmax warps + one control warp
+constexpr int kAtGroups = 2;                    // 128-row groups per block
+constexpr int kAtBlockRows = kAtGroups * kAtRows;
+constexpr int kAtThreads = (4 * kAtGroups + 1) * 32;
 
 __global__ void __launch_bounds__(kAtThreads, 1) prefill_attention_tc_kernel(
     const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_k,
@@ -89,115 +92,105 @@ __global__ void __launch_bounds__(kAtThreads, 1) prefill_attention_tc_kernel(
     extern __shared__ unsigned char smem_raw[];
     unsigned char* smem = reinterpret_cast<unsigned char*>(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
     unsigned long long* q_bar = reinterpret_cast<unsigned long long*>(smem + kAtBars);
-    unsigned long long* k_bar = q_bar + 1;          // [2]
-    unsigned long long* v_bar = k_bar + 2;          // [2]
-    unsigned long long* s_bar = v_bar + 2;          // completes once per tile: S ready
-    unsigned long long* o_bar = s_bar + 1;          // completes once per tile: O updated
-    unsigned long long* p_bar = o_bar + 1;          // completes once per tile: all 128 rows of P written
-    unsigned* tmem_slot = reinterpret_cast<unsigned*>(p_bar + 1);
+    unsigned long long* k_bar = q_bar + 1;          // [2] stages of keys
+    unsigned long long* v_bar = k_bar + 2;          // the stage of values
+    unsigned long long* s_bar = v_bar + 1;          // [2] per group, once per tile: S ready
+    unsigned long long* o_bar = s_bar + 2;          // [2] per group, once per tile: O updated
+    unsigned long long* p_bar = o_bar + 2;          // [2] per group, once per tile: all 128 rows of P written
+    unsigned* tmem_slot = reinterpret_cast<unsigned*>(p_bar + 2);
 
-    // Which request and which 128-row tile of it (heaviest tiles first).
+    // Which request and which 256-row tile of it (heaviest tiles first).
     const int block = gridDim.x - 1 - blockIdx.x;
     int lo = 0, hi = num_requests - 1;
     while (lo < hi) {
         const int mid = (lo + hi + 1) >> 1;
-        if (query_start[mid] / kAtRows + mid <= block) lo = mid; else hi = mid - 1;
+        if (query_start[mid] / kAtBlockRows + mid <= block) lo = mid; else hi = mid - 1;
     }
     const int request = lo;
     const int q_begin = query_start[request];
     const int q_len = query_start[request + 1] - q_begin;
-    const int tile_first = (block - (q_begin / kAtRows + request)) * kAtRows;
+    const int tile_first = (block - (q_begin / kAtBlockRows + request)) * kAtBlockRows;
     if (tile_first >= q_len) return;
-    const int rows_here = min(kAtRows, q_len - tile_first);
+    const int rows_here = min(kAtBlockRows, q_len - tile_first);
     const int seq_len = seq_lens[request];
     const int past = seq_len - q_len;
     const int head = blockIdx.y;
     const int kv_head = head / (nq / nkv);
     const int* table = block_table + (size_t)request * max_pages;
-    const int tid = threadIdx.x, warp = tid >> 5;
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
 
     const int first_pos = past + tile_first;
-    const int last_pos = first_pos + rows_here - 1;
     int k_first = window > 0 ? max(0, first_pos - window + 1) : 0;
     k_first = (k_first / page_size) * page_size;
-    const int k_end = last_pos + 1;
-    const int tiles = (k_end - k_first + kAtKeys - 1) / kAtKeys;
+    // Tiles of keys each group visits (a group without rows visits none).
+    int group_tiles[kAtGroups];
+#pragma unroll
+    for (int g = 0; g < kAtGroups; ++g) {
+        const int rows_g = min(kAtRows, rows_here - g * kAtRows);
+        group_tiles[g] = rows_g > 0 ? (first_pos + g * kAtRows + rows_g - k_first + kAtKeys - 1) / kAtKeys : 0;
+    }
+    const int tiles = max(group_tiles[0], group_tiles[1]);
     const int pages_per_tile = kAtKeys / page_size;
     const int table_len = (seq_len + page_size - 1) / page_size;
 
     if (tid == 0) {
         mbar_init(q_bar, 1);
         mbar_init(k_bar, 1); mbar_init(k_bar + 1, 1);
-        mbar_init(v_bar, 1); mbar_init(v_bar + 1, 1);
-        mbar_init(s_bar, 1);
-        mbar_init(o_bar, 1);
-        mbar_init(p_bar, kAtRows);
+        mbar_init(v_bar, 1);
+        for (int g = 0; g < kAtGroups; ++g) {
+            mbar_init(s_bar + g, 1);
+            mbar_init(o_bar + g, 1);
+            mbar_init(p_bar + g, kAtRows);
+        }
         asm volatile("fence.mbarrier_init.release.cluster;\n" ::: "memory");
     }
     if (warp == 0) {
         __syncwarp();
-        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;\n" ::"r"(smem_u32(tmem_slot)), "r"(256));
+        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;\n" ::"r"(smem_u32(tmem_slot)), "r"(512));
         asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;\n" ::);
     }
     // Value rows that no copy fills (positions past the request's pages) must not hold
     // bit patterns of NaN: their probabilities are zero, and 0 x NaN would poison O.
-    for (int i = tid; i < 4 * kAtHalf / 16; i += blockDim.x)
+    for (int i = tid; i < 2 * kAtHalf / 16; i += blockDim.x)
         reinterpret_cast<uint4*>(smem + kAtV)[i] = make_uint4(0, 0, 0, 0);
     asm volatile("fence.proxy.async.shared::cta;\n" ::: "memory");
     asm volatile("tcgen05.fence::before_thread_sync;\n" ::: "memory");
     __syncthreads();
     asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory");
-    const unsigned tmem_s = *tmem_slot, tmem_o = tmem_s + kAtKeys;
+    const unsigned tmem_base = *tmem_slot;          // S of group g at columns g * 128, O at 256 + g * 128
     bool ok = true;
-
-    // ---- copies, issued by thread 0 ----
-    auto load_k = [&](int t) {
-        const int s = t & 1;
-        const int first_page = (k_first + t * kAtKeys) / page_size;
-        int valid = 0;
-        for (int j = 0; j < pages_per_tile; ++j)
-            if (first_page + j < table_len && table[first_page + j] >= 0) ++valid;
-        mbar_expect_tx(k_bar + s, (unsigned)valid * page_size * kAtD * 2);
-        for (int j = 0; j < pages_per_tile; ++j) {
-            if (first_page + j >= table_len) continue;
-            const int page = table[first_page + j];
-            if (page < 0) continue;
-            const int row = (page * nkv + kv_head) * page_size;
-            unsigned char* dst = smem + kAtK + s * 2 * kAtHalf + j * page_size * 128;
-            tma_load_2d(dst, &map_k, 0, row, k_bar + s);
-            tma_load_2d(dst + kAtHalf, &map_k, 64, row, k_bar + s);
-        }
-    };
-    auto load_v = [&](int t) {
-        const int s = t & 1;
-        const int first_page = (k_first + t * kAtKeys) / page_size;
-        int valid = 0;
-        for (int j = 0; j < pages_per_tile; ++j)
-            if (first_page + j < table_len && table[first_page + j] >= 0) ++valid;
-        mbar_expect_tx(v_bar + s, (unsigned)valid * page_size * kAtD * 2);
-        for (int j = 0; j < pages_per_tile; ++j) {
-            if (first_page + j >= table_len) continue;
-            const int page = table[first_page + j];
-            if (page < 0) continue;
-            const int row = (page * nkv + kv_head) * page_size;
-            unsigned char* dst = smem + kAtV + s * 2 * kAtHalf + j * page_size * 128;
-            tma_load_2d(dst, &map_v, 0, row, v_bar + s);
-            tma_load_2d(dst + kAtHalf, &map_v, 64, row, v_bar + s);
-        }
-    };
     float row_max = -INFINITY, row_sum = 0.0f;
-    const unsigned idesc_s = umma_idesc(kAtKeys);                        // both operands K-major
-    const unsigned idesc_o = umma_idesc(kAtD) | (1u << 16);              // B (values) MN-major
 
-    if (warp == 4) {
+    if (warp == 4 * kAtGroups) {
         // -------- control warp: one thread requests the copies and issues the MMAs --------
-        if (tid == 128) {
-            mbar_expect_tx(q_bar, 2 * kAtHalf);
-            tma_load_2d(smem + kAtQ, &map_q, head * kAtD, q_begin + tile_first, q_bar);
-            tma_load_2d(smem + kAtQ + kAtHalf, &map_q, head * kAtD + 64, q_begin + tile_first, q_bar);
-            load_k(0);
-            load_v(0);
-            if (tiles > 1) load_k(1);
+        if (lane == 0) {
+            auto load_kv = [&](const CUtensorMap* map, unsigned char* stage, unsigned long long* bar, int t) {
+                const int first_page = (k_first + t * kAtKeys) / page_size;
+                int valid = 0;
+                for (int j = 0; j < pages_per_tile; ++j)
+                    if (first_page + j < table_len && table[first_page + j] >= 0) ++valid;
+                mbar_expect_tx(bar, (unsigned)valid * page_size * kAtD * 2);
+                for (int j = 0; j < pages_per_tile; ++j) {
+                    if (first_page + j >= table_len) continue;
+                    const int page = table[first_page + j];
+                    if (page < 0) continue;
+                    const int row = (page * nkv + kv_head) * page_size;
+                    unsigned char* dst = stage + j * page_size * 128;
+                    tma_load_2d(dst, map, 0, row, bar);
+                    tma_load_2d(dst + kAtHalf, map, 64, row, bar);
+                }
+            };
+            const unsigned idesc_s = umma_idesc(kAtKeys);                        // both operands K-major
+            const unsigned idesc_o = umma_idesc(kAtD) | (1u << 16);              // B (values) MN-major
+            const int groups_here = rows_here > kAtRows ? 2 : 1;
+            mbar_expect_tx(q_bar, (unsigned)groups_here * 2 * kAtHalf);
+            for (int g = 0; g < groups_here; ++g) {
+                tma_load_2d(smem + kAtQ + g * 2 * kAtHalf, &map_q, head * kAtD, q_begin + tile_first + g * kAtRows, q_bar);
+                tma_load_2d(smem + kAtQ + g * 2 * kAtHalf + kAtHalf, &map_q, head * kAtD + 64,
+                            q_begin + tile_first + g * kAtRows, q_bar);
+            }
+            load_kv(&map_k, smem + kAtK, k_bar, 0);
+            if (tiles > 1) load_kv(&map_k, smem + kAtK + 2 * kAtHalf, k_bar + 1, 1);
             for (int t = 0; t < tiles && ok; ++t) {
                 const int s = t & 1;
                 bool ready = mbar_wait(k_bar + s, (t >> 1) & 1);
@@ -205,39 +198,47 @@ __global__ void __launch_bounds__(kAtThreads, 1) prefill_attention_tc_kernel(
                 if (!ready) { atomicExch(error_flag, 21); ok = false; break; }
                 asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory");
                 const unsigned char* k_tile = smem + kAtK + s * 2 * kAtHalf;
+                for (int g = 0; g < kAtGroups; ++g) {
+                    if (t >= group_tiles[g]) continue;
+                    const unsigned char* q_tile = smem + kAtQ + g * 2 * kAtHalf;
 #pragma unroll
-                for (int j = 0; j < kAtD / 16; ++j)
-                    umma_bf16(tmem_s, umma_desc(smem + kAtQ + (j >> 2) * kAtHalf, (j & 3) * 32),
-                              umma_desc(k_tile + (j >> 2) * kAtHalf, (j & 3) * 32), idesc_s, j > 0);
-                umma_commit(s_bar);
-                // When S of tile t is ready, P V of tile t - 1 is done as well: stage s of K and
-                // the other stage of V are free for the tiles to come.
-                if (!mbar_wait(s_bar, t & 1)) { atomicExch(error_flag, 22); ok = false; break; }
-                if (t + 2 < tiles) load_k(t + 2);
-                if (t + 1 < tiles) load_v(t + 1);
-                if (!mbar_wait(p_bar, t & 1) || !mbar_wait(v_bar + s, (t >> 1) & 1)) {
-                    atomicExch(error_flag, 23);
-                    ok = false;
-                    break;
+                    for (int j = 0; j < kAtD / 16; ++j)
+                        umma_bf16(tmem_base + g * kAtKeys, umma_desc(q_tile + (j >> 2) * kAtHalf, (j & 3) * 32),
+                                  umma_desc(k_tile + (j >> 2) * kAtHalf, (j & 3) * 32), idesc_s, j > 0);
+                    umma_commit(s_bar + g);
                 }
-                asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory");
-                const unsigned char* v_tile = smem + kAtV + s * 2 * kAtHalf;
+                // S of tile t ready means P V of tile t - 1 is done: the stage of V and stage s of K are free.
+                for (int g = 0; g < kAtGroups; ++g)
+                    if (t < group_tiles[g] && !mbar_wait(s_bar + g, t & 1)) { atomicExch(error_flag, 22); ok = false; }
+                if (!ok) break;
+                load_kv(&map_v, smem + kAtV, v_bar, t);
+                if (t + 2 < tiles) load_kv(&map_k, smem + kAtK + s * 2 * kAtHalf, k_bar + s, t + 2);
+                if (!mbar_wait(v_bar, t & 1)) { atomicExch(error_flag, 23); ok = false; break; }
+                for (int g = 0; g < kAtGroups; ++g) {
+                    if (t >= group_tiles[g]) continue;
+                    if (!mbar_wait(p_bar + g, t & 1)) { atomicExch(error_flag, 24); ok = false; break; }
+                    asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory");
+                    const unsigned char* p_tile = smem + kAtP + g * 2 * kAtHalf;
 #pragma unroll
-                for (int j = 0; j < kAtKeys / 16; ++j)
-                    umma_bf16(tmem_o, umma_desc(smem + kAtP + (j >> 2) * kAtHalf, (j & 3) * 32),
-                              umma_desc_mn(v_tile, j * 16 * 128, kAtHalf), idesc_o, t > 0 || j > 0);
-                umma_commit(o_bar);
+                    for (int j = 0; j < kAtKeys / 16; ++j)
+                        umma_bf16(tmem_base + 2 * kAtKeys + g * kAtD, umma_desc(p_tile + (j >> 2) * kAtHalf, (j & 3) * 32),
+                                  umma_desc_mn(smem + kAtV, j * 16 * 128, kAtHalf), idesc_o, t > 0 || j > 0);
+                    umma_commit(o_bar + g);
+                }
             }
         }
     } else {
-        // -------- softmax warps: thread = query row = lane of tensor memory --------
-        const int row = tid;
-        const int q_pos = first_pos + row;
-        const unsigned lane_base = (unsigned)(warp * 32) << 16;
-        unsigned char* p_row = smem + kAtP + (row >> 3) * 1024 + (row & 7) * 128;
-        for (int t = 0; t < tiles; ++t) {
+        // -------- softmax warps: a thread is a query row, which is a lane of tensor memory --------
+        const int g = warp >> 2;
+        const int row = (warp & 3) * 32 + lane;                 // row within the group
+        const int my_tiles = group_tiles[g];
+        const int q_pos = first_pos + g * kAtRows + row;
+        const unsigned lane_base = (unsigned)((warp & 3) * 32) << 16;
+        const unsigned tmem_s = tmem_base + g * kAtKeys, tmem_o = tmem_base + 2 * kAtKeys + g * kAtD;
+        unsigned char* p_row = smem + kAtP + g * 2 * kAtHalf + (row >> 3) * 1024 + (row & 7) * 128;
+        for (int t = 0; t < my_tiles; ++t) {
             const int k0 = k_first + t * kAtKeys;
-            if (ok && !mbar_wait(s_bar, t & 1)) { atomicExch(error_flag, 24); ok = false; }
+            if (ok && !mbar_wait(s_bar + g, t & 1)) { atomicExch(error_flag, 25); ok = false; }
             ok = __all_sync(0xffffffffu, ok);
             asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory");
             // pass 1: the row's maximum
@@ -303,46 +304,42 @@ __global__ void __launch_bounds__(kAtThreads, 1) prefill_attention_tc_kernel(
             }
             asm volatile("fence.proxy.async.shared::cta;\n" ::: "memory");
             asm volatile("tcgen05.fence::before_thread_sync;\n" ::: "memory");
-            mbar_arrive(p_bar);
+            mbar_arrive(p_bar + g);
         }
-    }
 
-    // ---- O / sum to the output ----
-    if (warp < 4) {
-    const int row = tid;
-    const unsigned lane_base = (unsigned)(warp * 32) << 16;
-    if (tiles > 0 && !mbar_wait(o_bar, (tiles - 1) & 1)) { atomicExch(error_flag, 25); ok = false; }
-    asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory");
-    const float inv = row_sum > 0.0f ? 1.0f / row_sum : 0.0f;
-    __nv_bfloat16* dst = out + ((size_t)(q_begin + tile_first + row) * nq + head) * kAtD;
+        // ---- O / sum to the output ----
+        if (my_tiles > 0 && !mbar_wait(o_bar + g, (my_tiles - 1) & 1)) { atomicExch(error_flag, 26); ok = false; }
+        ok = __all_sync(0xffffffffu, ok);
+        asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory");
+        const float inv = row_sum > 0.0f ? 1.0f / row_sum : 0.0f;
+        const int row_in_block = g * kAtRows + row;
+        __nv_bfloat16* dst = out + ((size_t)(q_begin + tile_first + row_in_block) * nq + head) * kAtD;
+        if (my_tiles > 0) {
 #pragma unroll
-    for (int c = 0; c < 4; ++c) {
-        float v[32];
-        if (tiles > 0) tmem_ld32(tmem_o + lane_base + c * 32, v);
-        else
+            for (int c = 0; c < 4; ++c) {
+                float v[32];
+                tmem_ld32(tmem_o + lane_base + c * 32, v);
+                if (row_in_block < rows_here) {
 #pragma unroll
-            for (int e = 0; e < 32; ++e) v[e] = 0.0f;
-        if (row < rows_here) {
-#pragma unroll
-            for (int q4 = 0; q4 < 4; ++q4) {
-                uint4 packed;
-                __nv_bfloat162 h0 = __floats2bfloat162_rn(v[q4 * 8 + 0] * inv, v[q4 * 8 + 1] * inv);
-                __nv_bfloat162 h1 = __floats2bfloat162_rn(v[q4 * 8 + 2] * inv, v[q4 * 8 + 3] * inv);
-                __nv_bfloat162 h2 = __floats2bfloat162_rn(v[q4 * 8 + 4] * inv, v[q4 * 8 + 5] * inv);
-                __nv_bfloat162 h3 = __floats2bfloat162_rn(v[q4 * 8 + 6] * inv, v[q4 * 8 + 7] * inv);
-                packed.x = *reinterpret_cast<unsigned*>(&h0);
-                packed.y = *reinterpret_cast<unsigned*>(&h1);
-                packed.z = *reinterpret_cast<unsigned*>(&h2);
-                packed.w = *reinterpret_cast<unsigned*>(&h3);
-                *reinterpret_cast<uint4*>(dst + c * 32 + q4 * 8) = packed;
+                    for (int q4 = 0; q4 < 4; ++q4) {
+                        uint4 packed;
+                        __nv_bfloat162 h0 = __floats2bfloat162_rn(v[q4 * 8 + 0] * inv, v[q4 * 8 + 1] * inv);
+                        __nv_bfloat162 h1 = __floats2bfloat162_rn(v[q4 * 8 + 2] * inv, v[q4 * 8 + 3] * inv);
+                        __nv_bfloat162 h2 = __floats2bfloat162_rn(v[q4 * 8 + 4] * inv, v[q4 * 8 + 5] * inv);
+                        __nv_bfloat162 h3 = __floats2bfloat162_rn(v[q4 * 8 + 6] * inv, v[q4 * 8 + 7] * inv);
+                        packed.x = *reinterpret_cast<unsigned*>(&h0);
+                        packed.y = *reinterpret_cast<unsigned*>(&h1);
+                        packed.z = *reinterpret_cast<unsigned*>(&h2);
+                        packed.w = *reinterpret_cast<unsigned*>(&h3);
+                        *reinterpret_cast<uint4*>(dst + c * 32 + q4 * 8) = packed;
+                    }
+                }
             }
         }
     }
-    }
-    (void)ok;
     asm volatile("tcgen05.fence::before_thread_sync;\n" ::: "memory");
     __syncthreads();
-    if (warp == 0) asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;\n" ::"r"(tmem_s), "r"(256));
+    if (warp == 0) asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;\n" ::"r"(tmem_base), "r"(512));
 }
 
 }  // namespace b200
