@@ -2,23 +2,30 @@
 // (tcgen05, accumulators in tensor memory), head size 128, bfloat16.
 //
 // One block = 256 consecutive query tokens of one request x one query head, as two
-// groups of 128 rows.  Each group has four softmax warps; a thread owns one query row,
-// which is one lane of tensor memory, so the softmax needs no exchange between threads,
-// and the two groups share every tile of keys and values.  A ninth warp requests the
-// copies and issues the MMAs.  Per tile of 128 keys and per group:
+// groups of 128 rows that share every tile of keys and values.  Ten warps:
+//   0-7  softmax, four per group; a thread owns one query row, which is one lane of
+//        tensor memory, so the softmax needs no exchange between threads;
+//   8    one thread issues the MMAs;
+//   9    requests the copies: lane j brings in page j of a tile (keys, then values),
+//        two stages each, so that a tile's pages arrive while the tile before is in use.
+// Per tile of 128 keys and per group:
 //   S = Q K^T       8 x tcgen05.mma (M 128, N 128, K 16), Q and K from shared memory
 //                   (K-major, 128-byte swizzle, brought in by tensor copies page by page);
-//   softmax         each thread reads its row of S from tensor memory twice (maximum,
-//                   then exponentials), keeps running maximum and sum in float32,
-//                   writes P as bfloat16 into shared memory in the operand layout and
-//                   rescales its row of O in tensor memory when the maximum moved;
-//   O += P V        8 x tcgen05.mma with V read straight from its pages' layout
-//                   ([key][channel], i.e. the "MN-major" operand form).
-// tcgen05.commit after each batch of MMAs arrives on an mbarrier (per group one for the S
-// batches, one for the O batches); because the tensor pipe runs batches in order, "S of
-// tile t is ready" also means "P V of tile t - 1 is done", which frees the P buffer, the
-// V stage and O for rescaling.  Keys of tile t + 2 and values of tile t are requested when
-// S of tile t is ready.
+//   softmax         each thread reads its row of S (128 floats) from tensor memory once,
+//                   keeps a reference exponent and the running sum in float32, and writes
+//                   P as bfloat16 pairs back over the first 64 columns of S.  The
+//                   reference moves only when the row's maximum exceeds it by more than
+//                   2^8; then the thread rescales its row of O in tensor memory.  (Any
+//                   reference gives the same quotient O / sum; a stale one only shifts
+//                   the exponent range of P, which bfloat16 has to spare.)
+//   O += P V        8 x tcgen05.mma with P read from tensor memory and V straight from
+//                   its pages' layout ([key][channel], the "MN-major" operand form).
+// The MMA thread alternates between the groups (P V of tile t, then S of tile t + 1, for
+// one group, then for the other), so one group's MMAs run while the other group is in its
+// softmax.  The tensor pipe runs MMAs in the order of issue: S of tile t + 1 overwrites P
+// of tile t only after P V of tile t has read it, and "S of tile t + 1 is ready" also
+// means that O may be rescaled.  tcgen05.commit hands the stages of K and V back to the
+// copying warp.
 // Masking and arguments are those of attention_generic.cu.  Waits are bounded.
 #pragma once
 
@@ -45,6 +52,34 @@ __device__ __forceinline__ unsigned long long umma_desc_mn(const void* smem_tile
     return desc;
 }
 
+__device__ __forceinline__ void umma_bf16_a_tmem(unsigned tmem_d, unsigned tmem_a, unsigned long long b,
+                                                 unsigned idesc, bool accumulate) {
+    asm volatile(
+        "{\n.reg .pred p;\nsetp.ne.b32 p, %4, 0;\n"
+        "tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], %2, %3, p;\n}\n" ::"r"(tmem_d),
+        "r"(tmem_a), "l"(b), "r"(idesc), "r"((unsigned)accumulate)
+        : "memory");
+}
+
+__device__ __forceinline__ float exp2_approx(float x) {
+    float y;
+    asm("ex2.approx.ftz.f32 %0, %1;\n" : "=f"(y) : "f"(x));
+    return y;
+}
+
+// Issue the read of 32 columns into v[0..31]; the values are valid after tmem_ld_wait().
+__device__ __forceinline__ void tmem_ld32_issue(unsigned taddr, float* v) {
+    asm volatile(
+        "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
+        "{%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,%16,%17,%18,%19,%20,%21,%22,%23,%24,%25,%26,%27,%28,%29,%30,%31}, [%32];\n"
+        : "=f"(v[0]), "=f"(v[1]), "=f"(v[2]), "=f"(v[3]), "=f"(v[4]), "=f"(v[5]), "=f"(v[6]), "=f"(v[7]),
+          "=f"(v[8]), "=f"(v[9]), "=f"(v[10]), "=f"(v[11]), "=f"(v[12]), "=f"(v[13]), "=f"(v[14]), "=f"(v[15]),
+          "=f"(v[16]), "=f"(v[17]), "=f"(v[18]), "=f"(v[19]), "=f"(v[20]), "=f"(v[21]), "=f"(v[22]), "=f"(v[23]),
+          "=f"(v[24]), "=f"(v[25]), "=f"(v[26]), "=f"(v[27]), "=f"(v[28]), "=f"(v[29]), "=f"(v[30]), "=f"(v[31])
+        : "r"(taddr));
+}
+__device__ __forceinline__ void tmem_ld_wait() { asm volatile("tcgen05.wait::ld.sync.aligned;\n" ::: "memory"); }
+
 __device__ __forceinline__ void tmem_ld32(unsigned taddr, float (&v)[32]) {
     unsigned r[32];
     asm volatile(
@@ -58,6 +93,17 @@ __device__ __forceinline__ void tmem_ld32(unsigned taddr, float (&v)[32]) {
     asm volatile("tcgen05.wait::ld.sync.aligned;\n" ::: "memory");
 #pragma unroll
     for (int i = 0; i < 32; ++i) v[i] = __uint_as_float(r[i]);
+}
+
+__device__ __forceinline__ void tmem_st32_bits(unsigned taddr, const unsigned* v) {
+    asm volatile(
+        "tcgen05.st.sync.aligned.32x32b.x32.b32 [%0], "
+        "{%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,%16,%17,%18,%19,%20,%21,%22,%23,%24,%25,%26,%27,%28,%29,%30,%31,%32};\n" ::"r"(taddr),
+        "r"(v[0]), "r"(v[1]), "r"(v[2]), "r"(v[3]), "r"(v[4]), "r"(v[5]), "r"(v[6]), "r"(v[7]),
+        "r"(v[8]), "r"(v[9]), "r"(v[10]), "r"(v[11]), "r"(v[12]), "r"(v[13]), "r"(v[14]), "r"(v[15]),
+        "r"(v[16]), "r"(v[17]), "r"(v[18]), "r"(v[19]), "r"(v[20]), "r"(v[21]), "r"(v[22]), "r"(v[23]),
+        "r"(v[24]), "r"(v[25]), "r"(v[26]), "r"(v[27]), "r"(v[28]), "r"(v[29]), "r"(v[30]), "r"(v[31])
+        : "memory");
 }
 
 __device__ __forceinline__ void tmem_st32(unsigned taddr, const float (&v)[32]) {
@@ -75,13 +121,15 @@ __device__ __forceinline__ void tmem_st32(unsigned taddr, const float (&v)[32]) 
         : "memory");
 }
 
-// Shared memory (offsets from a 1024-byte aligned base): Q 2 x 32 KB, P 2 x 32 KB, two
-// stages of K (32 KB each), one of V (32 KB), barriers.
-constexpr int kAtQ = 0, kAtP = 4 * kAtHalf, kAtK = 8 * kAtHalf, kAtV = 12 * kAtHalf, kAtBars = 14 * kAtHalf;
-constexpr int kAtSmem = kAtBars + 128 + 1024;
+// Shared memory (offsets from a 1024-byte aligned base): Q 2 x 32 KB, two stages of K and
+// two of V (32 KB each), barriers.
+constexpr int kAtQ = 0, kAtK = 4 * kAtHalf, kAtV = 8 * kAtHalf, kAtBars = 12 * kAtHalf;
+constexpr int kAtSmem = kAtBars + 256 + 1024;
 constexpr int kAtGroups = 2;                    // 128-row groups per block
 constexpr int kAtBlockRows = kAtGroups * kAtRows;
-constexpr int kAtThreads = (4 * kAtGroups + 1) * 32;
+constexpr int kAtMmaWarp = 4 * kAtGroups, kAtCopyWarp = kAtMmaWarp + 1;
+constexpr int kAtThreads = (kAtCopyWarp + 1) * 32;
+constexpr float kAtRescaleStep = 8.0f;          // the reference exponent moves in steps larger than this
 
 __global__ void __launch_bounds__(kAtThreads, 1) prefill_attention_tc_kernel(
     const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_k,
@@ -92,12 +140,14 @@ __global__ void __launch_bounds__(kAtThreads, 1) prefill_attention_tc_kernel(
     extern __shared__ unsigned char smem_raw[];
     unsigned char* smem = reinterpret_cast<unsigned char*>(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
     unsigned long long* q_bar = reinterpret_cast<unsigned long long*>(smem + kAtBars);
-    unsigned long long* k_bar = q_bar + 1;          // [2] stages of keys
-    unsigned long long* v_bar = k_bar + 2;          // the stage of values
-    unsigned long long* s_bar = v_bar + 1;          // [2] per group, once per tile: S ready
-    unsigned long long* o_bar = s_bar + 2;          // [2] per group, once per tile: O updated
-    unsigned long long* p_bar = o_bar + 2;          // [2] per group, once per tile: all 128 rows of P written
-    unsigned* tmem_slot = reinterpret_cast<unsigned*>(p_bar + 2);
+    unsigned long long* k_full = q_bar + 1;         // [2] keys of a stage have arrived
+    unsigned long long* v_full = k_full + 2;        // [2] values of a stage have arrived
+    unsigned long long* k_free = v_full + 2;        // [2] both groups' S MMAs have read the stage
+    unsigned long long* v_free = k_free + 2;        // [2] both groups' P V MMAs have read the stage
+    unsigned long long* s_bar = v_free + 2;         // [2] per group, once per tile: S ready
+    unsigned long long* p_bar = s_bar + 2;          // [2] per group, once per tile: all 128 rows of P written
+    unsigned long long* o_bar = p_bar + 2;          // [2] per group, once: O complete
+    unsigned* tmem_slot = reinterpret_cast<unsigned*>(o_bar + 2);
 
     // Which request and which 256-row tile of it (heaviest tiles first).
     const int block = gridDim.x - 1 - blockIdx.x;
@@ -135,12 +185,16 @@ __global__ void __launch_bounds__(kAtThreads, 1) prefill_attention_tc_kernel(
 
     if (tid == 0) {
         mbar_init(q_bar, 1);
-        mbar_init(k_bar, 1); mbar_init(k_bar + 1, 1);
-        mbar_init(v_bar, 1);
+        for (int s = 0; s < 2; ++s) {
+            mbar_init(k_full + s, 1);
+            mbar_init(v_full + s, 1);
+            mbar_init(k_free + s, kAtGroups);
+            mbar_init(v_free + s, kAtGroups);
+        }
         for (int g = 0; g < kAtGroups; ++g) {
             mbar_init(s_bar + g, 1);
-            mbar_init(o_bar + g, 1);
             mbar_init(p_bar + g, kAtRows);
+            mbar_init(o_bar + g, 1);
         }
         asm volatile("fence.mbarrier_init.release.cluster;\n" ::: "memory");
     }
@@ -151,37 +205,33 @@ __global__ void __launch_bounds__(kAtThreads, 1) prefill_attention_tc_kernel(
     }
     // Value rows that no copy fills (positions past the request's pages) must not hold
     // bit patterns of NaN: their probabilities are zero, and 0 x NaN would poison O.
-    for (int i = tid; i < 2 * kAtHalf / 16; i += blockDim.x)
+    for (int i = tid; i < 4 * kAtHalf / 16; i += blockDim.x)
         reinterpret_cast<uint4*>(smem + kAtV)[i] = make_uint4(0, 0, 0, 0);
     asm volatile("fence.proxy.async.shared::cta;\n" ::: "memory");
     asm volatile("tcgen05.fence::before_thread_sync;\n" ::: "memory");
     __syncthreads();
     asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory");
-    const unsigned tmem_base = *tmem_slot;          // S of group g at columns g * 128, O at 256 + g * 128
+    const unsigned tmem_base = *tmem_slot;          // S (and P) of group g at columns g * 128, O at 256 + g * 128
     bool ok = true;
-    float row_max = -INFINITY, row_sum = 0.0f;
 
-    if (warp == 4 * kAtGroups) {
-        // -------- control warp: one thread requests the copies and issues the MMAs --------
+    if (warp == kAtCopyWarp) {
+        // -------- copies: lane j owns page j of every tile --------
+        auto table_entry = [&](int t) {
+            const int index = (k_first + t * kAtKeys) / page_size + lane;
+            return (lane < pages_per_tile && index < table_len) ? table[index] : -1;
+        };
+        auto request_pages = [&](const CUtensorMap* map, unsigned char* stage, unsigned long long* bar, int page) {
+            const unsigned valid = __ballot_sync(0xffffffffu, page >= 0);
+            if (lane == 0) mbar_expect_tx(bar, (unsigned)__popc(valid) * page_size * kAtD * 2);
+            __syncwarp();
+            if (page >= 0) {
+                const int row = (page * nkv + kv_head) * page_size;
+                unsigned char* dst = stage + lane * page_size * 128;
+                tma_load_2d(dst, map, 0, row, bar);
+                tma_load_2d(dst + kAtHalf, map, 64, row, bar);
+            }
+        };
         if (lane == 0) {
-            auto load_kv = [&](const CUtensorMap* map, unsigned char* stage, unsigned long long* bar, int t) {
-                const int first_page = (k_first + t * kAtKeys) / page_size;
-                int valid = 0;
-                for (int j = 0; j < pages_per_tile; ++j)
-                    if (first_page + j < table_len && table[first_page + j] >= 0) ++valid;
-                mbar_expect_tx(bar, (unsigned)valid * page_size * kAtD * 2);
-                for (int j = 0; j < pages_per_tile; ++j) {
-                    if (first_page + j >= table_len) continue;
-                    const int page = table[first_page + j];
-                    if (page < 0) continue;
-                    const int row = (page * nkv + kv_head) * page_size;
-                    unsigned char* dst = stage + j * page_size * 128;
-                    tma_load_2d(dst, map, 0, row, bar);
-                    tma_load_2d(dst + kAtHalf, map, 64, row, bar);
-                }
-            };
-            const unsigned idesc_s = umma_idesc(kAtKeys);                        // both operands K-major
-            const unsigned idesc_o = umma_idesc(kAtD) | (1u << 16);              // B (values) MN-major
             const int groups_here = rows_here > kAtRows ? 2 : 1;
             mbar_expect_tx(q_bar, (unsigned)groups_here * 2 * kAtHalf);
             for (int g = 0; g < groups_here; ++g) {
@@ -189,43 +239,61 @@ __global__ void __launch_bounds__(kAtThreads, 1) prefill_attention_tc_kernel(
                 tma_load_2d(smem + kAtQ + g * 2 * kAtHalf + kAtHalf, &map_q, head * kAtD + 64,
                             q_begin + tile_first + g * kAtRows, q_bar);
             }
-            load_kv(&map_k, smem + kAtK, k_bar, 0);
-            if (tiles > 1) load_kv(&map_k, smem + kAtK + 2 * kAtHalf, k_bar + 1, 1);
-            for (int t = 0; t < tiles && ok; ++t) {
+        }
+        int next_page = table_entry(0);
+        for (int t = 0; t < tiles; ++t) {
+            const int s = t & 1, page = next_page;
+            const unsigned freed = ((t >> 1) & 1) ^ 1;      // phase in which tile t - 2 left the stage
+            if (t + 1 < tiles) next_page = table_entry(t + 1);
+            if (t >= 2 && !mbar_wait(k_free + s, freed)) { atomicExch(error_flag, 21); ok = false; }
+            if (!__all_sync(0xffffffffu, ok)) break;
+            request_pages(&map_k, smem + kAtK + s * 2 * kAtHalf, k_full + s, page);
+            if (t >= 2 && !mbar_wait(v_free + s, freed)) { atomicExch(error_flag, 22); ok = false; }
+            if (!__all_sync(0xffffffffu, ok)) break;
+            request_pages(&map_v, smem + kAtV + s * 2 * kAtHalf, v_full + s, page);
+        }
+    } else if (warp == kAtMmaWarp) {
+        // -------- one thread issues every MMA, alternating between the groups --------
+        if (lane == 0) {
+            const unsigned idesc_s = umma_idesc(kAtKeys);                        // both operands K-major
+            const unsigned idesc_o = umma_idesc(kAtD) | (1u << 16);              // B (values) MN-major
+            auto issue_s = [&](int g, int t) {                                   // S_g = Q_g K(t)^T
                 const int s = t & 1;
-                bool ready = mbar_wait(k_bar + s, (t >> 1) & 1);
-                if (t == 0) ready = ready && mbar_wait(q_bar, 0);
-                if (!ready) { atomicExch(error_flag, 21); ok = false; break; }
+                if (t >= group_tiles[g]) { mbar_arrive(k_free + s); return true; }
+                if (!mbar_wait(k_full + s, (t >> 1) & 1)) return false;
                 asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory");
+                const unsigned char* q_tile = smem + kAtQ + g * 2 * kAtHalf;
                 const unsigned char* k_tile = smem + kAtK + s * 2 * kAtHalf;
-                for (int g = 0; g < kAtGroups; ++g) {
-                    if (t >= group_tiles[g]) continue;
-                    const unsigned char* q_tile = smem + kAtQ + g * 2 * kAtHalf;
 #pragma unroll
-                    for (int j = 0; j < kAtD / 16; ++j)
-                        umma_bf16(tmem_base + g * kAtKeys, umma_desc(q_tile + (j >> 2) * kAtHalf, (j & 3) * 32),
-                                  umma_desc(k_tile + (j >> 2) * kAtHalf, (j & 3) * 32), idesc_s, j > 0);
-                    umma_commit(s_bar + g);
-                }
-                // S of tile t ready means P V of tile t - 1 is done: the stage of V and stage s of K are free.
-                for (int g = 0; g < kAtGroups; ++g)
-                    if (t < group_tiles[g] && !mbar_wait(s_bar + g, t & 1)) { atomicExch(error_flag, 22); ok = false; }
-                if (!ok) break;
-                load_kv(&map_v, smem + kAtV, v_bar, t);
-                if (t + 2 < tiles) load_kv(&map_k, smem + kAtK + s * 2 * kAtHalf, k_bar + s, t + 2);
-                if (!mbar_wait(v_bar, t & 1)) { atomicExch(error_flag, 23); ok = false; break; }
-                for (int g = 0; g < kAtGroups; ++g) {
-                    if (t >= group_tiles[g]) continue;
-                    if (!mbar_wait(p_bar + g, t & 1)) { atomicExch(error_flag, 24); ok = false; break; }
-                    asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory");
-                    const unsigned char* p_tile = smem + kAtP + g * 2 * kAtHalf;
+                for (int j = 0; j < kAtD / 16; ++j)
+                    umma_bf16(tmem_base + g * kAtKeys, umma_desc(q_tile + (j >> 2) * kAtHalf, (j & 3) * 32),
+                              umma_desc(k_tile + (j >> 2) * kAtHalf, (j & 3) * 32), idesc_s, j > 0);
+                umma_commit(s_bar + g);
+                umma_commit(k_free + s);
+                return true;
+            };
+            auto issue_o = [&](int g, int t) {                                   // O_g += P_g V(t)
+                const int s = t & 1;
+                if (t >= group_tiles[g]) { mbar_arrive(v_free + s); return true; }
+                if (!mbar_wait(p_bar + g, t & 1) || !mbar_wait(v_full + s, (t >> 1) & 1)) return false;
+                asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory");
+                const unsigned char* v_tile = smem + kAtV + s * 2 * kAtHalf;
 #pragma unroll
-                    for (int j = 0; j < kAtKeys / 16; ++j)
-                        umma_bf16(tmem_base + 2 * kAtKeys + g * kAtD, umma_desc(p_tile + (j >> 2) * kAtHalf, (j & 3) * 32),
-                                  umma_desc_mn(smem + kAtV, j * 16 * 128, kAtHalf), idesc_o, t > 0 || j > 0);
-                    umma_commit(o_bar + g);
+                for (int j = 0; j < kAtKeys / 16; ++j)
+                    umma_bf16_a_tmem(tmem_base + 2 * kAtKeys + g * kAtD, tmem_base + g * kAtKeys + j * 8,
+                                     umma_desc_mn(v_tile, j * 16 * 128, kAtHalf), idesc_o, t > 0 || j > 0);
+                umma_commit(v_free + s);
+                if (t == group_tiles[g] - 1) umma_commit(o_bar + g);
+                return true;
+            };
+            ok = mbar_wait(q_bar, 0);
+            for (int g = 0; g < kAtGroups && ok; ++g) ok = issue_s(g, 0);
+            for (int t = 0; t < tiles && ok; ++t)
+                for (int g = 0; g < kAtGroups && ok; ++g) {
+                    ok = issue_o(g, t);
+                    if (ok && t + 1 < tiles) ok = issue_s(g, t + 1);
                 }
-            }
+            if (!ok) atomicExch(error_flag, 23);
         }
     } else {
         // -------- softmax warps: a thread is a query row, which is a lane of tensor memory --------
@@ -233,92 +301,86 @@ __global__ void __launch_bounds__(kAtThreads, 1) prefill_attention_tc_kernel(
         const int row = (warp & 3) * 32 + lane;                 // row within the group
         const int my_tiles = group_tiles[g];
         const int q_pos = first_pos + g * kAtRows + row;
+        const int warp_first = first_pos + g * kAtRows + (warp & 3) * 32, warp_last = warp_first + 31;
         const unsigned lane_base = (unsigned)((warp & 3) * 32) << 16;
-        const unsigned tmem_s = tmem_base + g * kAtKeys, tmem_o = tmem_base + 2 * kAtKeys + g * kAtD;
-        unsigned char* p_row = smem + kAtP + g * 2 * kAtHalf + (row >> 3) * 1024 + (row & 7) * 128;
+        const unsigned tmem_s = tmem_base + g * kAtKeys + lane_base;
+        const unsigned tmem_o = tmem_base + 2 * kAtKeys + g * kAtD + lane_base;
+        float row_ref = -INFINITY, row_sum = 0.0f;              // reference exponent, sum of exp2(s - reference)
         for (int t = 0; t < my_tiles; ++t) {
             const int k0 = k_first + t * kAtKeys;
             if (ok && !mbar_wait(s_bar + g, t & 1)) { atomicExch(error_flag, 25); ok = false; }
             ok = __all_sync(0xffffffffu, ok);
             asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory");
-            // pass 1: the row's maximum
-            float tile_max = -INFINITY;
+            // The whole row of S (128 values) in registers: one round trip to tensor memory.
+            float sv[kAtKeys];
 #pragma unroll
-            for (int c = 0; c < 4; ++c) {
-                float v[32];
-                tmem_ld32(tmem_s + lane_base + c * 32, v);
+            for (int c = 0; c < 4; ++c) tmem_ld32_issue(tmem_s + c * 32, sv + c * 32);
+            tmem_ld_wait();
+            // A tile wholly visible to every row of this warp (before its first query, inside
+            // every window) needs no mask; only tiles on the diagonal or at a window's edge do.
+            const bool all_visible = k0 + kAtKeys - 1 <= warp_first && (window <= 0 || k0 > warp_last - window);
+            if (!all_visible) {
 #pragma unroll
-                for (int e = 0; e < 32; ++e) {
-                    const int kp = k0 + c * 32 + e;
+                for (int e = 0; e < kAtKeys; ++e) {
+                    const int kp = k0 + e;
                     bool visible = kp <= q_pos;
                     if (window > 0) visible = visible && (kp > q_pos - window);
-                    if (visible) tile_max = fmaxf(tile_max, v[e] * scale_log2);
+                    if (!visible) sv[e] = -INFINITY;
                 }
             }
-            const float new_max = fmaxf(row_max, tile_max);
-            const float ref = new_max == -INFINITY ? 0.0f : new_max;
-            const float alpha = exp2f(row_max - ref);
-            row_max = new_max;
-            // pass 2: exponentials, their sum, P in the operand layout
+            float tile_max = sv[0];
+#pragma unroll
+            for (int e = 1; e < kAtKeys; ++e) tile_max = fmaxf(tile_max, sv[e]);
+            tile_max *= scale_log2;                                           // scale_log2 > 0
+            const bool moved = tile_max > row_ref + kAtRescaleStep;           // also the first finite maximum
+            const float new_ref = moved ? tile_max : row_ref;
+            const float ref = new_ref == -INFINITY ? 0.0f : new_ref;
+            const float alpha = moved ? exp2_approx(row_ref - ref) : 1.0f;    // exp2(-inf) = 0
+            row_ref = new_ref;
             float tile_sum = 0.0f;
 #pragma unroll
-            for (int c = 0; c < 4; ++c) {
-                float v[32];
-                tmem_ld32(tmem_s + lane_base + c * 32, v);
+            for (int c = 0; c < 2; ++c) {
+                // keys c * 64 .. c * 64 + 63 as 32 columns of bfloat16 pairs (even key in the low half)
+                unsigned packed[32];
 #pragma unroll
                 for (int e = 0; e < 32; ++e) {
-                    const int kp = k0 + c * 32 + e;
-                    bool visible = kp <= q_pos;
-                    if (window > 0) visible = visible && (kp > q_pos - window);
-                    v[e] = visible ? exp2f(v[e] * scale_log2 - ref) : 0.0f;
-                    tile_sum += v[e];
+                    const float p0 = exp2_approx(fmaf(sv[c * 64 + 2 * e], scale_log2, -ref));
+                    const float p1 = exp2_approx(fmaf(sv[c * 64 + 2 * e + 1], scale_log2, -ref));
+                    tile_sum += p0 + p1;
+                    const __nv_bfloat162 pair = __floats2bfloat162_rn(p0, p1);
+                    packed[e] = *reinterpret_cast<const unsigned*>(&pair);
                 }
-                // 32 keys = 4 chunks of 16 bytes; keys c*32.. lie in block (c >> 1), chunks (c & 1) * 4 ..
-#pragma unroll
-                for (int q4 = 0; q4 < 4; ++q4) {
-                    const int chunk = (c & 1) * 4 + q4;
-                    uint4 packed;
-                    __nv_bfloat162 h0 = __floats2bfloat162_rn(v[q4 * 8 + 0], v[q4 * 8 + 1]);
-                    __nv_bfloat162 h1 = __floats2bfloat162_rn(v[q4 * 8 + 2], v[q4 * 8 + 3]);
-                    __nv_bfloat162 h2 = __floats2bfloat162_rn(v[q4 * 8 + 4], v[q4 * 8 + 5]);
-                    __nv_bfloat162 h3 = __floats2bfloat162_rn(v[q4 * 8 + 6], v[q4 * 8 + 7]);
-                    packed.x = *reinterpret_cast<unsigned*>(&h0);
-                    packed.y = *reinterpret_cast<unsigned*>(&h1);
-                    packed.z = *reinterpret_cast<unsigned*>(&h2);
-                    packed.w = *reinterpret_cast<unsigned*>(&h3);
-                    *reinterpret_cast<uint4*>(p_row + (c >> 1) * kAtHalf + ((chunk ^ (row & 7)) << 4)) = packed;
-                }
+                tmem_st32_bits(tmem_s + c * 32, packed);
             }
             row_sum = row_sum * alpha + tile_sum;
-            // rescale O where the maximum moved (a whole warp at a time: the accesses are collective)
-            if (t > 0 && ok && __any_sync(0xffffffffu, alpha != 1.0f)) {
+            // rescale O where the reference moved (a whole warp at a time: the accesses are collective)
+            if (t > 0 && ok && __any_sync(0xffffffffu, moved)) {
 #pragma unroll
                 for (int c = 0; c < 4; ++c) {
                     float v[32];
-                    tmem_ld32(tmem_o + lane_base + c * 32, v);
+                    tmem_ld32(tmem_o + c * 32, v);
 #pragma unroll
                     for (int e = 0; e < 32; ++e) v[e] *= alpha;
-                    tmem_st32(tmem_o + lane_base + c * 32, v);
+                    tmem_st32(tmem_o + c * 32, v);
                 }
-                asm volatile("tcgen05.wait::st.sync.aligned;\n" ::: "memory");
             }
-            asm volatile("fence.proxy.async.shared::cta;\n" ::: "memory");
+            asm volatile("tcgen05.wait::st.sync.aligned;\n" ::: "memory");
             asm volatile("tcgen05.fence::before_thread_sync;\n" ::: "memory");
             mbar_arrive(p_bar + g);
         }
 
         // ---- O / sum to the output ----
-        if (my_tiles > 0 && !mbar_wait(o_bar + g, (my_tiles - 1) & 1)) { atomicExch(error_flag, 26); ok = false; }
+        if (my_tiles > 0 && ok && !mbar_wait(o_bar + g, 0)) { atomicExch(error_flag, 26); ok = false; }
         ok = __all_sync(0xffffffffu, ok);
         asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory");
         const float inv = row_sum > 0.0f ? 1.0f / row_sum : 0.0f;
         const int row_in_block = g * kAtRows + row;
         __nv_bfloat16* dst = out + ((size_t)(q_begin + tile_first + row_in_block) * nq + head) * kAtD;
-        if (my_tiles > 0) {
+        if (my_tiles > 0 && ok) {
 #pragma unroll
             for (int c = 0; c < 4; ++c) {
                 float v[32];
-                tmem_ld32(tmem_o + lane_base + c * 32, v);
+                tmem_ld32(tmem_o + c * 32, v);
                 if (row_in_block < rows_here) {
 #pragma unroll
                     for (int q4 = 0; q4 < 4; ++q4) {
