@@ -149,4 +149,14 @@ def compile_all(verbose: bool = True) -> list[Path]:
     from concurrent.futures import ThreadPoolExecutor
     names = [name for name in LIBRARIES if (SOURCE_DIR / f"{name}.cu").is_file()]
     with ThreadPoolExecutor(max_workers=min(8, len(names) or 1)) as pool:
-        return list(pool.map(lambda n: compile_library(n, verbose), names))
+        built = list(pool.map(lambda n: compile_library(n, verbose), names))
+    # Libraries of earlier versions of the sources are of no use to anyone: drop them.
+    current = {path.name for path in built}
+    for path in {p.parent for p in built}:
+        for stale in path.glob("*.so"):
+            if stale.name not in current and stale.name.split("-")[0] in LIBRARIES:
+                try:
+                    stale.unlink()
+                except OSError:
+                    pass
+    return built
