@@ -203,7 +203,7 @@ def measure_e2e(runner, config, batch: int, prompt_len: int, steps: int, warmup:
     llm = engine.LLMEngine(engine.EngineConfig(
         engine.ModelConfig("(random weights)", "bfloat16", context),
         engine.CacheConfig(runner.storage.page_size, runner.storage.num_pages),
-        engine.SchedulerConfig(batch, prompt_len)), runner=runner)
+        engine.SchedulerConfig(batch, prompt_len, async_scheduling=True)), runner=runner)
     params = engine.SamplingParams(temperature=0.0, max_tokens=warmup + steps + batch + 8, ignore_eos=True)
     for i in range(batch):
         llm.add_request(f"e2e-{i}", random_prompt(config.vocab_size, prompt_len, seed=300 + i), params)
@@ -222,7 +222,8 @@ def measure_e2e(runner, config, batch: int, prompt_len: int, steps: int, warmup:
     # per step: the packed int32 inputs go up, one int32 token per request comes back
     h2d = llm.decode_graphs.last_h2d_bytes + batch * (4 * 4 + 8 * 2)
     return {"value": tokens / seconds, "unit": "tokens/s", "h2d_bytes_per_step": h2d,
-            "d2h_bytes_per_step": 4 * batch, "ms_per_step": 1000 * seconds / steps}
+            "d2h_bytes_per_step": 4 * batch, "ms_per_step": 1000 * seconds / steps,
+            "async_scheduling": True, "steps_ahead": llm.num_steps_ahead}
 
 
 def main() -> int:

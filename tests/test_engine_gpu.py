@@ -158,3 +158,59 @@ def test_failed_step_latches(folders):
     llm.engine.runner.step = original
     with pytest.raises(engine.EngineDeadError):
         llm.engine.step()
+
+
+def _generate_with_arrivals(llm, prompts, params, arrivals):
+    """Requests join at the given step numbers; returns the final output of each."""
+    engine_ = llm.engine
+    latest, step, added = {}, 0, 0
+    while added < len(prompts) or engine_.has_unfinished_requests():
+        while added < len(prompts) and arrivals[added] <= step:
+            engine_.add_request(f"r{added}", prompts[added], params[added])
+            added += 1
+        for output in engine_.step():
+            latest[output.request_id] = output
+        step += 1
+        assert step < 2000
+    return [latest[f"r{i}"] for i in range(len(prompts))]
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_steps_queued_ahead_give_the_same_tokens(folders, dtype):
+    """With ``async_scheduling`` the engine queues a decode step before the one before it
+    has reported its tokens.  Every request must end with the same tokens, finish for the
+    same reason and at the same length as without it: greedy and seeded rows, a stop id
+    that ends a request while its next step is already queued, ``max_tokens``,
+    ``min_tokens``, a request with penalties (which must fall back), and requests that
+    join while others decode."""
+    import vllm_from_scratch_b200 as engine
+    raw = tiny_configs.TINY_B
+    prompts = [helpers.random_tokens(raw["vocab_size"], n, seed=300 + i) for i, n in enumerate([9, 33, 17, 5, 21])]
+    arrivals = [0, 0, 0, 12, 30]
+    results = {}
+    for mode in (False, True):
+        llm = engine.LLM(folders["B"], dtype=dtype, max_model_len=160, block_size=8, max_num_seqs=4,
+                         max_num_batched_tokens=48, async_scheduling=mode)
+        if not mode:
+            # a stop id that a greedy request really produces, so that it ends "early"
+            probe = llm.generate([prompts[1]], engine.SamplingParams(temperature=0.0, max_tokens=24))[0]
+            stop_id = probe.token_ids[10]
+        params = [
+            engine.SamplingParams(temperature=0.0, max_tokens=40),
+            engine.SamplingParams(temperature=0.0, max_tokens=64, stop_token_ids=[stop_id]),
+            engine.SamplingParams(temperature=0.9, top_k=12, top_p=0.9, seed=5, max_tokens=33, min_tokens=4,
+                                  stop_token_ids=[stop_id]),
+            engine.SamplingParams(temperature=0.0, max_tokens=25, repetition_penalty=1.3, presence_penalty=0.2),
+            engine.SamplingParams(temperature=0.7, seed=11, max_tokens=50),
+        ]
+        results[mode] = _generate_with_arrivals(llm, prompts, params, arrivals)
+        llm.engine.runner.manager.check_invariants()
+        assert llm.engine.runner.manager.stats()["requests"] == 0
+        if mode:
+            assert llm.engine.num_steps_ahead > 20, "most decode steps should have been queued ahead"
+        else:
+            assert llm.engine.num_steps_ahead == 0
+    for index, (sync, ahead) in enumerate(zip(results[False], results[True])):
+        assert ahead.token_ids == sync.token_ids, f"request {index}"
+        assert ahead.finish_reason == sync.finish_reason and ahead.stop_reason == sync.stop_reason
+    assert results[True][1].finish_reason.name == "STOP" and len(results[True][1].token_ids) <= 11

@@ -158,3 +158,69 @@ def test_prefix_hit_shortens_the_second_prompt():
     scheduler.add_request(request("b", 13, max_tokens=1))
     plan, _ = run_step(scheduler)
     assert planned(plan)["b"] == (12, 1, True)
+
+
+# --------------------------------------------------------- a step planned ahead
+def _decoding(scheduler, names_and_lengths, **params):
+    for name, length in names_and_lengths:
+        scheduler.add_request(request(name, length, **params))
+    run_step(scheduler)                          # prompts
+    return scheduler.schedule()                  # the first pure decode step, not yet updated
+
+
+def test_schedule_ahead_continues_every_request_with_the_token_in_flight():
+    scheduler, cache = make(budget=16)
+    plan = _decoding(scheduler, [("a", 3), ("b", 5)], max_tokens=10)
+    assert planned(plan) == {"a": (3, 1, True), "b": (5, 1, True)}
+    ahead = scheduler.schedule_ahead(plan)
+    # the token that `plan` samples is the input: it sits at the next position
+    assert planned(ahead) == {"a": (4, 1, True), "b": (6, 1, True)}
+    outs = scheduler.update(plan, {"a": 7, "b": 7})
+    assert [len(o.token_ids) for o in outs] == [2, 2]
+    again = scheduler.schedule_ahead(ahead)
+    assert planned(again) == {"a": (5, 1, True), "b": (7, 1, True)}
+    scheduler.update(ahead, {"a": 8, "b": 8})
+    scheduler.update(again, {"a": 9, "b": 9})
+    assert scheduler.requests["a"].output_token_ids == [9, 7, 8, 9]
+    # nothing in flight any more: the ordinary schedule goes on from the same place
+    assert planned(scheduler.schedule()) == {"a": (6, 1, True), "b": (8, 1, True)}
+    cache.check_invariants()
+
+
+def test_schedule_ahead_leaves_out_what_ends_by_length_and_declines_when_unsure():
+    scheduler, cache = make(budget=16)
+    scheduler.add_request(request("short", 3, max_tokens=2))
+    scheduler.add_request(request("long", 3, max_tokens=9))
+    run_step(scheduler)
+    plan = scheduler.schedule()
+    ahead = scheduler.schedule_ahead(plan)       # "short" gets its second and last token from `plan`
+    assert planned(ahead) == {"long": (4, 1, True)}
+    outs = scheduler.update(plan, {"short": 5, "long": 5})
+    assert [o.finished for o in outs] == [True, False]
+    # a request that stops on a token while its next step is queued: that step's result is dropped
+    stopper, _ = make(budget=16)
+    stopper.add_request(request("s", 3, max_tokens=9, stop_token_ids=[42]))
+    run_step(stopper)
+    plan = stopper.schedule()
+    ahead = stopper.schedule_ahead(plan)
+    outs = stopper.update(plan, {"s": 42})
+    assert outs[0].finished and outs[0].finish_reason.name == "STOP"
+    assert stopper.update(ahead, {"s": 1}) == [] and not stopper.has_unfinished_requests()
+    stopper.cache.check_invariants()
+    assert stopper.cache.stats()["requests"] == 0
+
+    # declines: someone waits; a prompt portion was in the step; penalties; no page left
+    waiting, _ = make(seqs=1, budget=16)
+    plan = _decoding(waiting, [("a", 3), ("b", 3)], max_tokens=9)
+    assert waiting.schedule_ahead(plan) is None
+    portion, _ = make(budget=4)
+    portion.add_request(request("a", 3, max_tokens=9))
+    portion.add_request(request("b", 9, max_tokens=9))
+    run_step(portion)
+    assert portion.schedule_ahead(portion.schedule()) is None
+    penal, _ = make(budget=16)
+    assert penal.schedule_ahead(_decoding(penal, [("a", 3)], max_tokens=9, repetition_penalty=1.2)) is None
+    full, cache = make(pages=2, page_size=4, budget=16)
+    plan = _decoding(full, [("a", 7)], max_tokens=9)         # 8 tokens fill both pages
+    assert full.schedule_ahead(plan) is None
+    cache.check_invariants()

@@ -58,6 +58,10 @@ class SchedulerConfig:
     max_num_seqs: int = 8               # most requests running at once
     max_num_batched_tokens: int = 64    # token budget of one step
     policy: str = "fcfs"                # or "priority"
+    # Queue the next decode step on the GPU before the tokens of the running one have
+    # come back to the host (they are fed on the device); what a stopped request
+    # computed one step too far is thrown away.  The reference has no such mode.
+    async_scheduling: bool = False
 
     def __post_init__(self) -> None:
         if self.max_num_seqs <= 0:

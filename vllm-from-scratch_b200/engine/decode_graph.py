@@ -77,8 +77,12 @@ class DecodeGraphs:
             self._pool = graph.pool()
         return _Captured(graph, packed, meta, logits, (rows, ctx, token_ids))
 
-    def run(self, entries: list[StepEntry]) -> torch.Tensor | None:
-        """The same result as ``StepFunction.run`` for a batch of single tokens."""
+    def run(self, entries: list[StepEntry],
+            device_tokens: tuple[torch.Tensor, list[int]] | None = None) -> torch.Tensor | None:
+        """The same result as ``StepFunction.run`` for a batch of single tokens.
+        ``device_tokens = (ids, rows)``: entry i's token is ``ids[rows[i]]``, an int32
+        tensor on the device (the ids an earlier step sampled, which the host may not
+        have yet); the entries' own token values are then ignored."""
         size = self._bucket(len(entries))
         self.runner.storage.zero_slots(self.runner.manager.take_fresh_slots())
         # Every row's logits are computed; only the wanted ones are handed back.
@@ -90,6 +94,16 @@ class DecodeGraphs:
             captured = self._graphs[size] = self._capture(size, host, meta)
         captured.packed.copy_(host, non_blocking=True)
         self.last_h2d_bytes = host.numel() * host.element_size()
+        if device_tokens is not None:
+            ids, rows = device_tokens
+            count = len(entries)
+            token_ids = captured.keep_alive[2]
+            if rows == list(range(count)):
+                token_ids[:count].copy_(ids[:count])
+            else:
+                index = torch.tensor(rows, dtype=torch.int64).to(ids.device, non_blocking=True)
+                token_ids[:count].copy_(ids.index_select(0, index))
+                self.last_h2d_bytes += 8 * count
         captured.graph.replay()
         self.replays += 1
         if not wanted:

@@ -32,6 +32,30 @@ class EngineDeadError(RuntimeError):
     pass
 
 
+class _InFlight:
+    """A step whose work is queued on the GPU: the plan, the requests that sample (in
+    row order), their ids on the device, and the pinned copy on its way to the host."""
+
+    def __init__(self, plan: SchedulerOutput, sampling: list[Request], tokens: torch.Tensor | None,
+                 host: torch.Tensor | None) -> None:
+        self.plan, self.sampling, self.tokens, self.host = plan, sampling, tokens, host
+        self.arrived: torch.cuda.Event | None = None
+        if tokens is not None and host is not None:
+            host[:tokens.shape[0]].copy_(tokens, non_blocking=True)
+            self.arrived = torch.cuda.Event()
+            self.arrived.record()
+
+    def wait(self) -> dict[str, int]:
+        if self.tokens is None:
+            return {}
+        if self.arrived is not None:
+            self.arrived.synchronize()
+            values = self.host[:len(self.sampling)].tolist()
+        else:
+            values = self.tokens.tolist()
+        return {request.request_id: token for request, token in zip(self.sampling, values)}
+
+
 class LLMEngine:
     def __init__(self, config: EngineConfig, runner: ModelRunner | None = None) -> None:
         self.config = config
@@ -45,6 +69,9 @@ class LLMEngine:
         self._failure: BaseException | None = None
         self._first_inputs: dict | None = None
         self.num_steps = 0
+        self.num_steps_ahead = 0            # steps queued before their input tokens reached the host
+        self._pending: _InFlight | None = None
+        self._host_tokens: list[torch.Tensor] = []
         self.decode_graphs = None
         if not model.enforce_eager and self.runner.device.type == "cuda":
             from .decode_graph import DecodeGraphs
@@ -88,35 +115,72 @@ class LLMEngine:
             raise
 
     def _step(self) -> list[RequestOutput]:
-        plan = self.scheduler.schedule()
-        self.num_steps += 1
-        if not plan.scheduled:
-            return []
-        sampled = self._execute(plan)
-        return self.scheduler.update(plan, sampled)
+        current, self._pending = self._pending, None
+        if current is None:
+            plan = self.scheduler.schedule()
+            self.num_steps += 1
+            if not plan.scheduled:
+                return []
+            current = self._execute(plan)
+        if self._overlaps():
+            # Queue the step after this one before waiting for this one's tokens.
+            ahead = self.scheduler.schedule_ahead(current.plan)
+            if ahead is not None:
+                self.num_steps += 1
+                self.num_steps_ahead += 1
+                self._pending = self._execute(ahead, previous=current)
+        outputs = self.scheduler.update(current.plan, current.wait())
+        if self._pending is not None and not self.scheduler.has_unfinished_requests():
+            self._pending = None            # everyone stopped: what was queued ahead is of no use
+        return outputs
 
-    def _execute(self, plan: SchedulerOutput) -> dict[str, int]:
+    def _overlaps(self) -> bool:
+        return (self.config.scheduler_config.async_scheduling and self.decode_graphs is not None
+                and self.runner.device.type == "cuda")
+
+    def _pinned(self, rows: int) -> torch.Tensor | None:
+        """One of two pinned buffers for the sampled ids (two steps may be in flight)."""
+        if self.runner.device.type != "cuda":
+            return None
+        if not self._host_tokens:
+            size = max(rows, self.config.scheduler_config.max_num_seqs)
+            self._host_tokens = [torch.empty(size, dtype=torch.int32, pin_memory=True) for _ in range(2)]
+        self._host_tokens.reverse()
+        buffer = self._host_tokens[0]
+        return buffer if buffer.shape[0] >= rows else None
+
+    def _execute(self, plan: SchedulerOutput, previous: _InFlight | None = None) -> _InFlight:
+        """Queue the plan's batch and its sampling.  With ``previous`` the plan was made
+        ahead: every request's token is the one ``previous`` sampled, taken on the device."""
         entries = []
         sampling = []
         for item in plan.scheduled:
             request = item.request
-            tokens = request.all_token_ids[item.start:item.start + item.num_tokens]
+            if previous is None:
+                tokens = request.all_token_ids[item.start:item.start + item.num_tokens]
+            else:
+                tokens = [0]                    # replaced on the device
             entries.append(StepEntry(request.request_id, tokens, item.start,
                                      [item.num_tokens - 1] if item.samples else []))
             if item.samples:
                 sampling.append(request)
-        if self.decode_graphs is not None and self.decode_graphs.accepts(entries):
+        if previous is not None:
+            row_of = {request.request_id: row for row, request in enumerate(previous.sampling)}
+            rows = [row_of[item.request.request_id] for item in plan.scheduled]
+            logits = self.decode_graphs.run(entries, device_tokens=(previous.tokens, rows))
+        elif self.decode_graphs is not None and self.decode_graphs.accepts(entries):
             logits = self.decode_graphs.run(entries)
         else:
             logits = self.runner.step(entries)
         if self._first_inputs is None:
             self._first_inputs = self._describe_inputs(plan)
         if not sampling:
-            return {}
-        tokens = self.sampler.sample(
+            return _InFlight(plan, [], None, None)
+        tokens = self.sampler.sample_device(
             logits, [r.sampling_params for r in sampling], [r.seed for r in sampling],
-            [r.prompt_token_ids for r in sampling], [r.output_token_ids for r in sampling])
-        return {request.request_id: token for request, token in zip(sampling, tokens)}
+            [r.prompt_token_ids for r in sampling], [r.output_token_ids for r in sampling],
+            ahead=0 if previous is None else 1)
+        return _InFlight(plan, sampling, tokens, self._pinned(len(sampling)))
 
     # -------------------------------------------------------------------- trace
     def _describe_inputs(self, plan: SchedulerOutput) -> dict | None:
@@ -147,13 +211,14 @@ class LLM:
     def __init__(self, model: str | Path, dtype: str = "bfloat16", max_model_len: int = 4096,
                  block_size: int = 16, num_gpu_blocks: int | None = None, max_num_seqs: int = 8,
                  max_num_batched_tokens: int = 2048, enable_prefix_caching: bool = False,
-                 enforce_eager: bool = False, seed: int = 0, device: str = "cuda") -> None:
+                 enforce_eager: bool = False, seed: int = 0, device: str = "cuda",
+                 async_scheduling: bool = False) -> None:
         if num_gpu_blocks is None:
             num_gpu_blocks = max_num_seqs * -(-max_model_len // block_size)
         self.engine = LLMEngine(EngineConfig(
             ModelConfig(str(model), dtype, max_model_len, enforce_eager, seed),
             CacheConfig(block_size, num_gpu_blocks, enable_prefix_caching),
-            SchedulerConfig(max_num_seqs, max_num_batched_tokens), device))
+            SchedulerConfig(max_num_seqs, max_num_batched_tokens, async_scheduling=async_scheduling), device))
         self._counter = 0
 
     def generate(self, prompt_token_ids: Sequence[Sequence[int]],

@@ -197,6 +197,46 @@ class Scheduler:
         })
         return output
 
+    def schedule_ahead(self, previous: SchedulerOutput) -> SchedulerOutput | None:
+        """The decode step after ``previous``, planned while ``previous`` still runs: every
+        request of it that cannot end by length goes on with the one token that
+        ``previous`` samples, which the host does not know yet.  Declines (``None``)
+        whenever that is not plainly the next step: something waits, ``previous`` was not
+        a pure decode step or preempted, a page is missing (no preemption on a guess), or
+        a request samples with penalties (they need the unknown token)."""
+        if self.waiting or previous.preempted_ids or not previous.scheduled:
+            return None
+        if len(previous.scheduled) != len(self.running):
+            return None
+        chosen: list[Request] = []
+        for item in previous.scheduled:
+            request = item.request
+            if (not item.samples or item.num_tokens != 1 or request.status is not RequestStatus.RUNNING
+                    or request.num_computed_tokens != request.num_tokens
+                    or request.sampling_params.has_penalties):
+                return None
+            produced = len(request.output_token_ids) + 1            # with the token in flight
+            if produced >= request.sampling_params.max_tokens or request.num_tokens + 1 >= self.max_model_len:
+                continue                                            # ends by length when that token arrives
+            chosen.append(request)
+        if not chosen:
+            return None
+        for request in chosen:
+            if not self.cache.allocate(request.request_id, request.num_computed_tokens + 1):
+                return None             # pages taken so far stay with their requests for the next step
+        output = SchedulerOutput(finished_ids=[])
+        for request in chosen:
+            output.scheduled.append(ScheduledRequest(request, request.num_computed_tokens, 1, samples=True))
+            request.num_computed_tokens += 1
+        self.step_count += 1
+        self.trace.append({
+            "step": self.step_count,
+            "scheduled": {item.request.request_id: 1 for item in output.scheduled},
+            "preempted": [], "running": len(self.running), "waiting": 0,
+            "free_pages": [pool.num_free for pool in self.cache.pools], "ahead": True,
+        })
+        return output
+
     def _check_progress(self, output: SchedulerOutput) -> None:
         if output.total_num_scheduled_tokens or not self.has_unfinished_requests():
             self._idle_steps = 0

@@ -37,18 +37,24 @@ class Sampler:
         tokens = self.sample_device(logits, params, seeds, prompts, outputs)
         return tokens.tolist()
 
-    def sample_device(self, logits, params, seeds, prompts, outputs) -> torch.Tensor:
+    def sample_device(self, logits, params, seeds, prompts, outputs, ahead: int = 0) -> torch.Tensor:
+        """The sampled ids as an int32 tensor on the device, without waiting for them.
+        ``ahead``: how many output tokens of every row are still on their way to the
+        host and so missing from ``outputs`` (they count for the draw index and for
+        ``min_tokens``; rows with penalties cannot be sampled ahead)."""
         rows = logits.shape[0]
         if rows != len(params):
             raise ValueError(f"{rows} rows of logits for {len(params)} requests")
+        if ahead and any(p.has_penalties for p in params):
+            raise ValueError("penalties need every earlier token: such rows cannot be sampled ahead")
         self._penalties(logits, params, prompts, outputs)
-        self._min_tokens(logits, params, outputs)
+        self._min_tokens(logits, params, outputs, ahead)
         temperature = np.array([p.temperature for p in params], dtype=np.float32)
         top_k = np.array([p.top_k if p.top_k > 0 else 0 for p in params], dtype=np.int32)
         top_p = np.array([p.top_p for p in params], dtype=np.float32)
         min_p = np.array([p.min_p for p in params], dtype=np.float32)
         seed = np.array([s & 0x7FFFFFFFFFFFFFFF for s in seeds], dtype=np.int64)
-        draw = np.array([len(o) for o in outputs], dtype=np.int64)
+        draw = np.array([len(o) + ahead for o in outputs], dtype=np.int64)
         tokens = torch.empty(rows, dtype=torch.int32, device=logits.device)
         kernels.sample(logits, self._to_device(temperature), self._to_device(top_k),
                        self._to_device(top_p), self._to_device(min_p), self._to_device(seed),
@@ -75,10 +81,10 @@ class Sampler:
             self._to_device(np.array([p.frequency_penalty for p in params], dtype=np.float32)),
             self._to_device(np.array([p.presence_penalty for p in params], dtype=np.float32)))
 
-    def _min_tokens(self, logits, params, outputs) -> None:
+    def _min_tokens(self, logits, params, outputs, ahead: int = 0) -> None:
         rows, tokens = [], []
         for row, (p, output) in enumerate(zip(params, outputs)):
-            if len(output) < p.min_tokens:
+            if len(output) + ahead < p.min_tokens:
                 for token in sorted(p.all_stop_token_ids):
                     rows.append(row)
                     tokens.append(token)
