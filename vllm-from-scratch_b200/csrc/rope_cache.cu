@@ -79,6 +79,76 @@ __global__ void head_norm_rope_cache_kernel(
     }
 }
 
+// The same work for many tokens at once (portions of prompts), bfloat16, rotation over the
+// whole head: one block per token.  The token's sines and cosines are computed once and
+// shared by all of its heads through shared memory; half a warp owns a head, each lane
+// PER elements of the first half and the matching PER of the second, read and written as
+// one vector each.
+template <int D>
+__global__ void __launch_bounds__(128) head_norm_rope_cache_token_kernel(
+    const __nv_bfloat16* __restrict__ qkv, const int* __restrict__ positions, const int* __restrict__ slots,
+    const float* __restrict__ q_weight, const float* __restrict__ k_weight,
+    const float* __restrict__ inv_freq, __nv_bfloat16* __restrict__ q_out, __nv_bfloat16* __restrict__ k_pages,
+    __nv_bfloat16* __restrict__ v_pages, int nq, int nkv, int page_size, float eps) {
+    constexpr int HALF = D / 2, PER = HALF / 16;
+    struct alignas(2 * PER) Vec { __nv_bfloat16 v[PER]; };
+    __shared__ float sin_s[HALF], cos_s[HALF];
+    const int token = blockIdx.x;
+    const float pos = (float)positions[token];
+    for (int j = threadIdx.x; j < HALF; j += blockDim.x) sincosf(pos * inv_freq[j], &sin_s[j], &cos_s[j]);
+    __syncthreads();
+    const int half_warp = threadIdx.x >> 4, sub = threadIdx.x & 15;
+    const int total_heads = nq + 2 * nkv;
+    const int slot = k_pages ? slots[token] : -1;
+    const int page = slot >= 0 ? slot / page_size : 0, offset = slot >= 0 ? slot - page * page_size : 0;
+    const unsigned mask = 0xFFFFu << (threadIdx.x & 16);
+    for (int head = half_warp; head < total_heads; head += 8) {
+        const bool is_q = head < nq, is_k = !is_q && head < nq + nkv;
+        if (!is_q && slot < 0) continue;                        // nothing is stored for this token
+        const __nv_bfloat16* src = qkv + ((size_t)token * total_heads + head) * D + sub * PER;
+        __nv_bfloat16* dst;
+        if (is_q) {
+            dst = q_out + ((size_t)token * nq + head) * D;
+        } else {
+            const int kv_head = is_k ? head - nq : head - nq - nkv;
+            dst = (is_k ? k_pages : v_pages) + (((size_t)page * nkv + kv_head) * page_size + offset) * D;
+        }
+        dst += sub * PER;
+        const Vec lo = *reinterpret_cast<const Vec*>(src), hi = *reinterpret_cast<const Vec*>(src + HALF);
+        if (!is_q && !is_k) {                                   // values: copied as they are
+            *reinterpret_cast<Vec*>(dst) = lo;
+            *reinterpret_cast<Vec*>(dst + HALF) = hi;
+            continue;
+        }
+        float x1[PER], x2[PER];
+#pragma unroll
+        for (int e = 0; e < PER; ++e) { x1[e] = __bfloat162float(lo.v[e]); x2[e] = __bfloat162float(hi.v[e]); }
+        const float* weight = is_q ? q_weight : k_weight;
+        if (weight) {
+            float sum_sq = 0.0f;
+#pragma unroll
+            for (int e = 0; e < PER; ++e) sum_sq = fmaf(x1[e], x1[e], fmaf(x2[e], x2[e], sum_sq));
+#pragma unroll
+            for (int step = 8; step > 0; step >>= 1) sum_sq += __shfl_xor_sync(mask, sum_sq, step);
+            const float inv = rsqrtf(sum_sq / (float)D + eps);
+#pragma unroll
+            for (int e = 0; e < PER; ++e) {
+                x1[e] = x1[e] * inv * weight[sub * PER + e];
+                x2[e] = x2[e] * inv * weight[HALF + sub * PER + e];
+            }
+        }
+        Vec out_lo, out_hi;
+#pragma unroll
+        for (int e = 0; e < PER; ++e) {
+            const float s = sin_s[sub * PER + e], c = cos_s[sub * PER + e];
+            out_lo.v[e] = __float2bfloat16_rn(x1[e] * c - x2[e] * s);
+            out_hi.v[e] = __float2bfloat16_rn(x2[e] * c + x1[e] * s);
+        }
+        *reinterpret_cast<Vec*>(dst) = out_lo;
+        *reinterpret_cast<Vec*>(dst + HALF) = out_hi;
+    }
+}
+
 }  // namespace b200
 
 // dtype: 0 = float32, 1 = bfloat16.  q_weight / k_weight may be null (no head
@@ -98,6 +168,18 @@ B200_EXPORT int b200_head_norm_rope_cache(
     if ((k_pages == nullptr) != (v_pages == nullptr))
         return fail("head_norm_rope_cache", "key and value pages must be given together");
     if (k_pages && page_size <= 0) return fail("head_norm_rope_cache", "page_size must be positive");
+    // Many tokens: the kernel that shares a token's sines and cosines between its heads.
+    const bool aligned = (((uintptr_t)qkv | (uintptr_t)q_out | (uintptr_t)k_pages | (uintptr_t)v_pages) & 15) == 0;
+    if (dtype == 1 && num_tokens >= 32 && rotary_dim == d && (d == 64 || d == 128 || d == 256) && aligned) {
+#define B200_CASE(D)                                                                                     \
+        if (d == D)                                                                                      \
+            head_norm_rope_cache_token_kernel<D><<<num_tokens, 128, 0, stream>>>(                        \
+                (const __nv_bfloat16*)qkv, positions, slots, q_weight, k_weight, inv_freq,              \
+                (__nv_bfloat16*)q_out, (__nv_bfloat16*)k_pages, (__nv_bfloat16*)v_pages, nq, nkv, page_size, eps);
+        B200_CASE(64) B200_CASE(128) B200_CASE(256)
+#undef B200_CASE
+        return check_launch("head_norm_rope_cache");
+    }
     const int warps = 4;
     const int total_heads = nq + 2 * nkv;
     dim3 grid(num_tokens, (total_heads + warps - 1) / warps);
