@@ -87,8 +87,9 @@ B200_EXPORT int b200_prefill_attention_tc_bf16(
         error_flag[device] = static_cast<int*>(found);
     }
     const CUtensorMap* map_q = tensor_map_for(q, num_tokens, nq * d, kAtRows);   // one group of rows per copy
-    const CUtensorMap* map_k = tensor_map_for(k_pages, num_pages * nkv * page_size, d, page_size);
-    const CUtensorMap* map_v = tensor_map_for(v_pages, num_pages * nkv * page_size, d, page_size);
+    const int copy_rows = page_size < kAtKeys ? page_size : kAtKeys;            // a page, or the part of it in one tile
+    const CUtensorMap* map_k = tensor_map_for(k_pages, num_pages * nkv * page_size, d, copy_rows);
+    const CUtensorMap* map_v = tensor_map_for(v_pages, num_pages * nkv * page_size, d, copy_rows);
     if (map_q == nullptr || map_k == nullptr || map_v == nullptr)
         return fail("prefill_attention_tc", "could not encode a tensor map");
     cudaError_t status = cudaFuncSetAttribute(prefill_attention_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kAtSmem);

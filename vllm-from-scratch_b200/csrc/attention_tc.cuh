@@ -2,30 +2,33 @@
 // (tcgen05, accumulators in tensor memory), head size 128, bfloat16.
 //
 // One block = 256 consecutive query tokens of one request x one query head, as two
-// groups of 128 rows that share every tile of keys and values.  Ten warps:
+// groups of 128 rows that share every tile of keys and values.  Eleven warps:
 //   0-7  softmax, four per group; a thread owns one query row, which is one lane of
 //        tensor memory, so the softmax needs no exchange between threads;
-//   8    one thread issues the MMAs;
-//   9    requests the copies: lane j brings in page j of a tile (keys, then values),
-//        two stages each, so that a tile's pages arrive while the tile before is in use.
-// Per tile of 128 keys and per group:
-//   S = Q K^T       8 x tcgen05.mma (M 128, N 128, K 16), Q and K from shared memory
-//                   (K-major, 128-byte swizzle, brought in by tensor copies page by page);
-//   softmax         each thread reads its row of S (128 floats) from tensor memory once,
+//   8-9  one thread per group issues the group's MMAs;
+//   10   requests the copies: lane j brings in page j of a tile (keys, then values),
+//        four stages each, so that tiles arrive while the tiles before them are in use.
+// Per tile of 64 keys and per group:
+//   S = Q K^T       8 x tcgen05.mma (M 128, N 64, K 16), Q and K from shared memory
+//                   (K-major, 128-byte swizzle, brought in by tensor copies page by page),
+//                   into one of the group's two S buffers in tensor memory;
+//   softmax         each thread reads its row of S (64 floats) from tensor memory once,
 //                   keeps a reference exponent and the running sum in float32, and writes
-//                   P as bfloat16 pairs back over the first 64 columns of S.  The
+//                   P as bfloat16 pairs back over the first 32 columns of the buffer.  The
 //                   reference moves only when the row's maximum exceeds it by more than
 //                   2^8; then the thread rescales its row of O in tensor memory.  (Any
 //                   reference gives the same quotient O / sum; a stale one only shifts
 //                   the exponent range of P, which bfloat16 has to spare.)
-//   O += P V        8 x tcgen05.mma with P read from tensor memory and V straight from
-//                   its pages' layout ([key][channel], the "MN-major" operand form).
-// The MMA thread alternates between the groups (P V of tile t, then S of tile t + 1, for
-// one group, then for the other), so one group's MMAs run while the other group is in its
-// softmax.  The tensor pipe runs MMAs in the order of issue: S of tile t + 1 overwrites P
-// of tile t only after P V of tile t has read it, and "S of tile t + 1 is ready" also
-// means that O may be rescaled.  tcgen05.commit hands the stages of K and V back to the
-// copying warp.
+//   O += P V        4 x tcgen05.mma (M 128, N 128, K 16) with P read from tensor memory
+//                   and V straight from its pages' layout ([key][channel], the "MN-major"
+//                   operand form).
+// With two S buffers a group's MMA thread issues S of tile t + 2 right after P V of tile t, so a
+// group's next S is complete before its softmax asks for it: the softmax warps run tile
+// after tile without waiting for the tensor pipe, and the two groups' MMAs fill each
+// other's gaps.  The tensor pipe runs MMAs in the order of issue: S of tile t + 2
+// overwrites P of tile t only after P V of tile t has read it.  O is rescaled only after
+// the P V before it has finished (mbarriers of its own, one for even and one for odd tiles).  tcgen05.commit hands the stages of
+// K and V back to the copying warp.
 // Masking and arguments are those of attention_generic.cu.  Waits are bounded.
 #pragma once
 
@@ -35,29 +38,40 @@ namespace b200 {
 
 constexpr int kAtD = 128;                       // head size
 constexpr int kAtRows = 128;                    // queries per block
-constexpr int kAtKeys = 128;                    // keys per tile
+constexpr int kAtKeys = 64;                     // keys per tile
 constexpr int kAtHalf = kAtRows * 64 * 2;       // one [128 x 64] bfloat16 block: 16 KB
 
-// Matrix descriptor of an operand whose M/N index is the contiguous one ([k][mn] rows of
-// 128 bytes, 128-byte swizzle): 64-wide blocks of the M/N index `lbo` bytes apart, groups
-// of 8 k-rows 1024 bytes apart.
-__device__ __forceinline__ unsigned long long umma_desc_mn(const void* smem_tile, int byte_offset, int lbo) {
-    const unsigned address = (smem_u32(smem_tile) + byte_offset) & 0x3FFFF;
-    unsigned long long desc = 0;
-    desc |= (unsigned long long)(address >> 4);
-    desc |= (unsigned long long)((lbo >> 4) & 0x3FFF) << 16;
-    desc |= (unsigned long long)(1024 >> 4) << 32;
-    desc |= (unsigned long long)1 << 46;
-    desc |= (unsigned long long)2 << 61;
-    return desc;
+// Operands whose M/N index is the contiguous one ([k][mn] rows of 128 bytes, 128-byte swizzle)
+// have their 64-wide blocks of the M/N index `lbo` bytes apart and groups of 8 k-rows 1024
+// bytes apart.
+//
+// The MMA thread is one thread issuing dependent integer instructions: building a 64-bit
+// descriptor for every MMA costs it more than the MMA costs the tensor pipe.  The upper
+// word of all descriptors here is one constant (8-row groups 1024 bytes apart, version 1,
+// 128-byte swizzle); the lower word is (address >> 4) plus the leading-offset field, so a
+// tile's descriptors are one word per tile and one add per MMA.
+constexpr unsigned kDescHi = (1024u >> 4) | (1u << 14) | (2u << 29);
+__device__ __forceinline__ unsigned desc_lo_k_major(const void* smem_tile) {
+    return ((smem_u32(smem_tile) & 0x3FFFF) >> 4) | (1u << 16);
 }
-
-__device__ __forceinline__ void umma_bf16_a_tmem(unsigned tmem_d, unsigned tmem_a, unsigned long long b,
-                                                 unsigned idesc, bool accumulate) {
+__device__ __forceinline__ unsigned desc_lo_mn_major(const void* smem_tile, int lbo) {
+    return ((smem_u32(smem_tile) & 0x3FFFF) >> 4) | ((unsigned)((lbo >> 4) & 0x3FFF) << 16);
+}
+template <bool ACCUMULATE>
+__device__ __forceinline__ void umma_ss(unsigned tmem_d, unsigned a_lo, unsigned b_lo, unsigned idesc) {
     asm volatile(
-        "{\n.reg .pred p;\nsetp.ne.b32 p, %4, 0;\n"
-        "tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], %2, %3, p;\n}\n" ::"r"(tmem_d),
-        "r"(tmem_a), "l"(b), "r"(idesc), "r"((unsigned)accumulate)
+        "{\n.reg .pred p;\n.reg .b64 da, db;\nsetp.ne.b32 p, %5, 0;\n"
+        "mov.b64 da, {%1, %3};\nmov.b64 db, {%2, %3};\n"
+        "tcgen05.mma.cta_group::1.kind::f16 [%0], da, db, %4, p;\n}\n" ::"r"(tmem_d),
+        "r"(a_lo), "r"(b_lo), "r"(kDescHi), "r"(idesc), "n"(ACCUMULATE ? 1 : 0)
+        : "memory");
+}
+__device__ __forceinline__ void umma_ts(unsigned tmem_d, unsigned tmem_a, unsigned b_lo, unsigned idesc, bool accumulate) {
+    asm volatile(
+        "{\n.reg .pred p;\n.reg .b64 db;\nsetp.ne.b32 p, %5, 0;\n"
+        "mov.b64 db, {%2, %3};\n"
+        "tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], db, %4, p;\n}\n" ::"r"(tmem_d),
+        "r"(tmem_a), "r"(b_lo), "r"(kDescHi), "r"(idesc), "r"((unsigned)accumulate)
         : "memory");
 }
 
@@ -121,13 +135,17 @@ __device__ __forceinline__ void tmem_st32(unsigned taddr, const float (&v)[32]) 
         : "memory");
 }
 
-// Shared memory (offsets from a 1024-byte aligned base): Q 2 x 32 KB, two stages of K and
-// two of V (32 KB each), barriers.
-constexpr int kAtQ = 0, kAtK = 4 * kAtHalf, kAtV = 8 * kAtHalf, kAtBars = 12 * kAtHalf;
-constexpr int kAtSmem = kAtBars + 256 + 1024;
+// Shared memory (offsets from a 1024-byte aligned base): Q 2 x 32 KB, four stages of K and
+// four of V (64 keys = 16 KB each), barriers.
+constexpr int kAtStages = 4;
+constexpr int kAtStageBytes = kAtKeys * kAtD * 2;           // 16 KB: two [64 x 64] blocks of 8 KB
+constexpr int kAtStageHalf = kAtStageBytes / 2;
+constexpr int kAtQ = 0, kAtK = 4 * kAtHalf, kAtV = kAtK + kAtStages * kAtStageBytes;
+constexpr int kAtBars = kAtV + kAtStages * kAtStageBytes;
+constexpr int kAtSmem = kAtBars + 512 + 1024;
 constexpr int kAtGroups = 2;                    // 128-row groups per block
 constexpr int kAtBlockRows = kAtGroups * kAtRows;
-constexpr int kAtMmaWarp = 4 * kAtGroups, kAtCopyWarp = kAtMmaWarp + 1;
+constexpr int kAtMmaWarp = 4 * kAtGroups, kAtCopyWarp = kAtMmaWarp + kAtGroups;   // one MMA warp per group
 constexpr int kAtThreads = (kAtCopyWarp + 1) * 32;
 constexpr float kAtRescaleStep = 8.0f;          // the reference exponent moves in steps larger than this
 
@@ -140,14 +158,14 @@ __global__ void __launch_bounds__(kAtThreads, 1) prefill_attention_tc_kernel(
     extern __shared__ unsigned char smem_raw[];
     unsigned char* smem = reinterpret_cast<unsigned char*>(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
     unsigned long long* q_bar = reinterpret_cast<unsigned long long*>(smem + kAtBars);
-    unsigned long long* k_full = q_bar + 1;         // [2] keys of a stage have arrived
-    unsigned long long* v_full = k_full + 2;        // [2] values of a stage have arrived
-    unsigned long long* k_free = v_full + 2;        // [2] both groups' S MMAs have read the stage
-    unsigned long long* v_free = k_free + 2;        // [2] both groups' P V MMAs have read the stage
-    unsigned long long* s_bar = v_free + 2;         // [2] per group, once per tile: S ready
-    unsigned long long* p_bar = s_bar + 2;          // [2] per group, once per tile: all 128 rows of P written
-    unsigned long long* o_bar = p_bar + 2;          // [2] per group, once: O complete
-    unsigned* tmem_slot = reinterpret_cast<unsigned*>(o_bar + 2);
+    unsigned long long* k_full = q_bar + 1;                 // [stages] keys of a stage have arrived
+    unsigned long long* v_full = k_full + kAtStages;        // [stages] values of a stage have arrived
+    unsigned long long* k_free = v_full + kAtStages;        // [stages] both groups' S MMAs have read the stage
+    unsigned long long* v_free = k_free + kAtStages;        // [stages] both groups' P V MMAs have read the stage
+    unsigned long long* s_bar = v_free + kAtStages;         // [group][buffer] S of a tile is in the buffer
+    unsigned long long* p_bar = s_bar + 2 * kAtGroups;      // [group][buffer] all 128 rows of P are in the buffer
+    unsigned long long* o_bar = p_bar + 2 * kAtGroups;      // [group][tile & 1] P V of the tile has been added to O
+    unsigned* tmem_slot = reinterpret_cast<unsigned*>(o_bar + 2 * kAtGroups);
 
     // Which request and which 256-row tile of it (heaviest tiles first).
     const int block = gridDim.x - 1 - blockIdx.x;
@@ -172,7 +190,8 @@ __global__ void __launch_bounds__(kAtThreads, 1) prefill_attention_tc_kernel(
     const int first_pos = past + tile_first;
     int k_first = window > 0 ? max(0, first_pos - window + 1) : 0;
     k_first = (k_first / page_size) * page_size;
-    // Tiles of keys each group visits (a group without rows visits none).
+    k_first = (k_first / kAtKeys) * kAtKeys;                // pages larger than a tile: start on a tile's edge too
+    // Tiles of 64 keys each group visits (a group without rows visits none).
     int group_tiles[kAtGroups];
 #pragma unroll
     for (int g = 0; g < kAtGroups; ++g) {
@@ -180,21 +199,25 @@ __global__ void __launch_bounds__(kAtThreads, 1) prefill_attention_tc_kernel(
         group_tiles[g] = rows_g > 0 ? (first_pos + g * kAtRows + rows_g - k_first + kAtKeys - 1) / kAtKeys : 0;
     }
     const int tiles = max(group_tiles[0], group_tiles[1]);
-    const int pages_per_tile = kAtKeys / page_size;
+    const int copy_rows = min(page_size, kAtKeys);          // rows of one tensor copy (the tensor maps' box)
+    const int copies_per_tile = kAtKeys / copy_rows;
     const int table_len = (seq_len + page_size - 1) / page_size;
 
     if (tid == 0) {
         mbar_init(q_bar, 1);
-        for (int s = 0; s < 2; ++s) {
+        for (int s = 0; s < kAtStages; ++s) {
             mbar_init(k_full + s, 1);
             mbar_init(v_full + s, 1);
             mbar_init(k_free + s, kAtGroups);
             mbar_init(v_free + s, kAtGroups);
         }
         for (int g = 0; g < kAtGroups; ++g) {
-            mbar_init(s_bar + g, 1);
-            mbar_init(p_bar + g, kAtRows);
-            mbar_init(o_bar + g, 1);
+            mbar_init(s_bar + 2 * g, 1);
+            mbar_init(s_bar + 2 * g + 1, 1);
+            mbar_init(p_bar + 2 * g, kAtRows);
+            mbar_init(p_bar + 2 * g + 1, kAtRows);
+            mbar_init(o_bar + 2 * g, 1);
+            mbar_init(o_bar + 2 * g + 1, 1);
         }
         asm volatile("fence.mbarrier_init.release.cluster;\n" ::: "memory");
     }
@@ -205,30 +228,34 @@ __global__ void __launch_bounds__(kAtThreads, 1) prefill_attention_tc_kernel(
     }
     // Value rows that no copy fills (positions past the request's pages) must not hold
     // bit patterns of NaN: their probabilities are zero, and 0 x NaN would poison O.
-    for (int i = tid; i < 4 * kAtHalf / 16; i += blockDim.x)
+    for (int i = tid; i < kAtStages * kAtStageBytes / 16; i += blockDim.x)
         reinterpret_cast<uint4*>(smem + kAtV)[i] = make_uint4(0, 0, 0, 0);
     asm volatile("fence.proxy.async.shared::cta;\n" ::: "memory");
     asm volatile("tcgen05.fence::before_thread_sync;\n" ::: "memory");
     __syncthreads();
     asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory");
-    const unsigned tmem_base = *tmem_slot;          // S (and P) of group g at columns g * 128, O at 256 + g * 128
+    // Tensor memory: group g has two S buffers of 64 columns at g * 128 (P over the first 32
+    // columns of its buffer) and O at 256 + g * 128.
+    const unsigned tmem_base = *tmem_slot;
     bool ok = true;
 
     if (warp == kAtCopyWarp) {
-        // -------- copies: lane j owns page j of every tile --------
-        auto table_entry = [&](int t) {
-            const int index = (k_first + t * kAtKeys) / page_size + lane;
-            return (lane < pages_per_tile && index < table_len) ? table[index] : -1;
+        // -------- copies: lane j owns the j-th page (or part of a page) of every tile --------
+        auto source_row = [&](int t) {          // first row of this lane's copy in the [pages x heads x page] x d matrix, or -1
+            const int key = k_first + t * kAtKeys + lane * copy_rows;
+            const int index = key / page_size;
+            if (lane >= copies_per_tile || index >= table_len) return -1;
+            const int page = table[index];
+            return page < 0 ? -1 : (page * nkv + kv_head) * page_size + (key - index * page_size);
         };
-        auto request_pages = [&](const CUtensorMap* map, unsigned char* stage, unsigned long long* bar, int page) {
-            const unsigned valid = __ballot_sync(0xffffffffu, page >= 0);
-            if (lane == 0) mbar_expect_tx(bar, (unsigned)__popc(valid) * page_size * kAtD * 2);
+        auto request_rows = [&](const CUtensorMap* map, unsigned char* stage, unsigned long long* bar, int row) {
+            const unsigned valid = __ballot_sync(0xffffffffu, row >= 0);
+            if (lane == 0) mbar_expect_tx(bar, (unsigned)__popc(valid) * copy_rows * kAtD * 2);
             __syncwarp();
-            if (page >= 0) {
-                const int row = (page * nkv + kv_head) * page_size;
-                unsigned char* dst = stage + lane * page_size * 128;
+            if (row >= 0) {
+                unsigned char* dst = stage + lane * copy_rows * 128;
                 tma_load_2d(dst, map, 0, row, bar);
-                tma_load_2d(dst + kAtHalf, map, 64, row, bar);
+                tma_load_2d(dst + kAtStageHalf, map, 64, row, bar);
             }
         };
         if (lane == 0) {
@@ -240,59 +267,75 @@ __global__ void __launch_bounds__(kAtThreads, 1) prefill_attention_tc_kernel(
                             q_begin + tile_first + g * kAtRows, q_bar);
             }
         }
-        int next_page = table_entry(0);
+        int next_row = source_row(0);
         for (int t = 0; t < tiles; ++t) {
-            const int s = t & 1, page = next_page;
-            const unsigned freed = ((t >> 1) & 1) ^ 1;      // phase in which tile t - 2 left the stage
-            if (t + 1 < tiles) next_page = table_entry(t + 1);
-            if (t >= 2 && !mbar_wait(k_free + s, freed)) { atomicExch(error_flag, 21); ok = false; }
+            const int s = t % kAtStages, row = next_row;
+            const unsigned freed = ((t / kAtStages) & 1) ^ 1;       // phase in which tile t - stages left the stage
+            if (t + 1 < tiles) next_row = source_row(t + 1);
+            if (t >= kAtStages && !mbar_wait(k_free + s, freed)) { atomicExch(error_flag, 21); ok = false; }
             if (!__all_sync(0xffffffffu, ok)) break;
-            request_pages(&map_k, smem + kAtK + s * 2 * kAtHalf, k_full + s, page);
-            if (t >= 2 && !mbar_wait(v_free + s, freed)) { atomicExch(error_flag, 22); ok = false; }
+            request_rows(&map_k, smem + kAtK + s * kAtStageBytes, k_full + s, row);
+            if (t >= kAtStages && !mbar_wait(v_free + s, freed)) { atomicExch(error_flag, 22); ok = false; }
             if (!__all_sync(0xffffffffu, ok)) break;
-            request_pages(&map_v, smem + kAtV + s * 2 * kAtHalf, v_full + s, page);
+            request_rows(&map_v, smem + kAtV + s * kAtStageBytes, v_full + s, row);
         }
-    } else if (warp == kAtMmaWarp) {
-        // -------- one thread issues every MMA, alternating between the groups --------
+    } else if (warp >= kAtMmaWarp) {
+        // -------- per group, one thread issues the group's MMAs --------
+        // The order is S(0), S(1), then for every tile t: P V(t), S(t + 2).  S(t + 2) goes
+        // into the buffer that P(t) leaves, and the pipe runs it after P V(t) has read P(t).
+        // A group's next S is therefore complete before its softmax asks for it, and the two
+        // groups' MMAs fill each other's gaps.  A group past its last tile still takes part
+        // in handing the stages back (the barriers count both groups).
         if (lane == 0) {
-            const unsigned idesc_s = umma_idesc(kAtKeys);                        // both operands K-major
-            const unsigned idesc_o = umma_idesc(kAtD) | (1u << 16);              // B (values) MN-major
-            auto issue_s = [&](int g, int t) {                                   // S_g = Q_g K(t)^T
-                const int s = t & 1;
-                if (t >= group_tiles[g]) { mbar_arrive(k_free + s); return true; }
-                if (!mbar_wait(k_full + s, (t >> 1) & 1)) return false;
+            const int g = warp - kAtMmaWarp;
+            const int my_tiles = group_tiles[g];
+            const unsigned idesc_s = umma_idesc(kAtKeys);                        // both operands K-major, N = 64
+            const unsigned idesc_o = umma_idesc(kAtD) | (1u << 16);              // B (values) MN-major, N = 128
+            const unsigned q_lo = desc_lo_k_major(smem + kAtQ + g * 2 * kAtHalf);
+            const unsigned k_lo = desc_lo_k_major(smem + kAtK);
+            const unsigned v_lo = desc_lo_mn_major(smem + kAtV, kAtStageHalf);
+            const unsigned tmem_s0 = tmem_base + g * 2 * kAtKeys;
+            const unsigned tmem_o = tmem_base + 2 * kAtGroups * kAtKeys + g * kAtD;
+            auto issue_s = [&](int t) {                                          // S(t) = Q K(t)^T
+                const int s = t % kAtStages;
+                // (a group past its last tile waits too: it may hand a stage back once per filling)
+                if (!mbar_wait(k_full + s, (t / kAtStages) & 1)) return false;
+                if (t >= my_tiles) { mbar_arrive(k_free + s); return true; }
                 asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory");
-                const unsigned char* q_tile = smem + kAtQ + g * 2 * kAtHalf;
-                const unsigned char* k_tile = smem + kAtK + s * 2 * kAtHalf;
+                const unsigned k_tile = k_lo + ((s * kAtStageBytes) >> 4);
+                const unsigned tmem_s = tmem_s0 + (t & 1) * kAtKeys;
+                // k-step j: 16 channels = 32 bytes inside a 64-channel block; blocks 16 KB (Q) and 8 KB (K) apart
+                umma_ss<false>(tmem_s, q_lo, k_tile, idesc_s);
 #pragma unroll
-                for (int j = 0; j < kAtD / 16; ++j)
-                    umma_bf16(tmem_base + g * kAtKeys, umma_desc(q_tile + (j >> 2) * kAtHalf, (j & 3) * 32),
-                              umma_desc(k_tile + (j >> 2) * kAtHalf, (j & 3) * 32), idesc_s, j > 0);
-                umma_commit(s_bar + g);
+                for (int j = 1; j < kAtD / 16; ++j)
+                    umma_ss<true>(tmem_s, q_lo + (((j >> 2) * kAtHalf + (j & 3) * 32) >> 4),
+                                  k_tile + (((j >> 2) * kAtStageHalf + (j & 3) * 32) >> 4), idesc_s);
+                umma_commit(s_bar + 2 * g + (t & 1));
                 umma_commit(k_free + s);
                 return true;
             };
-            auto issue_o = [&](int g, int t) {                                   // O_g += P_g V(t)
-                const int s = t & 1;
-                if (t >= group_tiles[g]) { mbar_arrive(v_free + s); return true; }
-                if (!mbar_wait(p_bar + g, t & 1) || !mbar_wait(v_full + s, (t >> 1) & 1)) return false;
+            auto issue_o = [&](int t) {                                          // O += P(t) V(t)
+                const int s = t % kAtStages;
+                if (!mbar_wait(v_full + s, (t / kAtStages) & 1)) return false;
+                if (t >= my_tiles) { mbar_arrive(v_free + s); return true; }
+                if (!mbar_wait(p_bar + 2 * g + (t & 1), (t >> 1) & 1)) return false;
                 asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory");
-                const unsigned char* v_tile = smem + kAtV + s * 2 * kAtHalf;
+                const unsigned v_tile = v_lo + ((s * kAtStageBytes) >> 4);
+                const unsigned tmem_p = tmem_s0 + (t & 1) * kAtKeys;
+                // k-step j: 16 keys = 8 columns of P, 16 rows of 128 bytes of V
 #pragma unroll
                 for (int j = 0; j < kAtKeys / 16; ++j)
-                    umma_bf16_a_tmem(tmem_base + 2 * kAtKeys + g * kAtD, tmem_base + g * kAtKeys + j * 8,
-                                     umma_desc_mn(v_tile, j * 16 * 128, kAtHalf), idesc_o, t > 0 || j > 0);
+                    umma_ts(tmem_o, tmem_p + j * 8, v_tile + ((j * 16 * 128) >> 4), idesc_o, t > 0 || j > 0);
                 umma_commit(v_free + s);
-                if (t == group_tiles[g] - 1) umma_commit(o_bar + g);
+                umma_commit(o_bar + 2 * g + (t & 1));
                 return true;
             };
             ok = mbar_wait(q_bar, 0);
-            for (int g = 0; g < kAtGroups && ok; ++g) ok = issue_s(g, 0);
-            for (int t = 0; t < tiles && ok; ++t)
-                for (int g = 0; g < kAtGroups && ok; ++g) {
-                    ok = issue_o(g, t);
-                    if (ok && t + 1 < tiles) ok = issue_s(g, t + 1);
-                }
+            for (int t = 0; t < 2 && t < tiles && ok; ++t) ok = issue_s(t);
+            for (int t = 0; t < tiles && ok; ++t) {
+                ok = issue_o(t);
+                if (ok && t + 2 < tiles) ok = issue_s(t + 2);
+            }
             if (!ok) atomicExch(error_flag, 23);
         }
     } else {
@@ -303,18 +346,19 @@ __global__ void __launch_bounds__(kAtThreads, 1) prefill_attention_tc_kernel(
         const int q_pos = first_pos + g * kAtRows + row;
         const int warp_first = first_pos + g * kAtRows + (warp & 3) * 32, warp_last = warp_first + 31;
         const unsigned lane_base = (unsigned)((warp & 3) * 32) << 16;
-        const unsigned tmem_s = tmem_base + g * kAtKeys + lane_base;
-        const unsigned tmem_o = tmem_base + 2 * kAtKeys + g * kAtD + lane_base;
+        const unsigned tmem_o = tmem_base + 2 * kAtGroups * kAtKeys + g * kAtD + lane_base;
         float row_ref = -INFINITY, row_sum = 0.0f;              // reference exponent, sum of exp2(s - reference)
         for (int t = 0; t < my_tiles; ++t) {
             const int k0 = k_first + t * kAtKeys;
-            if (ok && !mbar_wait(s_bar + g, t & 1)) { atomicExch(error_flag, 25); ok = false; }
+            const int buffer = t & 1;
+            const unsigned tmem_s = tmem_base + g * 2 * kAtKeys + buffer * kAtKeys + lane_base;
+            if (ok && !mbar_wait(s_bar + 2 * g + buffer, (t >> 1) & 1)) { atomicExch(error_flag, 25); ok = false; }
             ok = __all_sync(0xffffffffu, ok);
             asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory");
-            // The whole row of S (128 values) in registers: one round trip to tensor memory.
+            // The row of S (64 values) in registers: one round trip to tensor memory.
             float sv[kAtKeys];
-#pragma unroll
-            for (int c = 0; c < 4; ++c) tmem_ld32_issue(tmem_s + c * 32, sv + c * 32);
+            tmem_ld32_issue(tmem_s, sv);
+            tmem_ld32_issue(tmem_s + 32, sv + 32);
             tmem_ld_wait();
             // A tile wholly visible to every row of this warp (before its first query, inside
             // every window) needs no mask; only tiles on the diagonal or at a window's edge do.
@@ -328,49 +372,61 @@ __global__ void __launch_bounds__(kAtThreads, 1) prefill_attention_tc_kernel(
                     if (!visible) sv[e] = -INFINITY;
                 }
             }
-            float tile_max = sv[0];
+            // (four chains each for the maximum and the sum: a thread has little else to overlap)
+            float max4[4] = {sv[0], sv[1], sv[2], sv[3]};
 #pragma unroll
-            for (int e = 1; e < kAtKeys; ++e) tile_max = fmaxf(tile_max, sv[e]);
+            for (int e = 4; e < kAtKeys; ++e) max4[e & 3] = fmaxf(max4[e & 3], sv[e]);
+            float tile_max = fmaxf(fmaxf(max4[0], max4[1]), fmaxf(max4[2], max4[3]));
             tile_max *= scale_log2;                                           // scale_log2 > 0
             const bool moved = tile_max > row_ref + kAtRescaleStep;           // also the first finite maximum
             const float new_ref = moved ? tile_max : row_ref;
             const float ref = new_ref == -INFINITY ? 0.0f : new_ref;
             const float alpha = moved ? exp2_approx(row_ref - ref) : 1.0f;    // exp2(-inf) = 0
             row_ref = new_ref;
-            float tile_sum = 0.0f;
+            float sum4[4] = {0.0f, 0.0f, 0.0f, 0.0f};
+            // 64 keys as 32 columns of bfloat16 pairs (even key in the low half), written over S
+            unsigned packed[32];
 #pragma unroll
-            for (int c = 0; c < 2; ++c) {
-                // keys c * 64 .. c * 64 + 63 as 32 columns of bfloat16 pairs (even key in the low half)
-                unsigned packed[32];
-#pragma unroll
-                for (int e = 0; e < 32; ++e) {
-                    const float p0 = exp2_approx(fmaf(sv[c * 64 + 2 * e], scale_log2, -ref));
-                    const float p1 = exp2_approx(fmaf(sv[c * 64 + 2 * e + 1], scale_log2, -ref));
-                    tile_sum += p0 + p1;
-                    const __nv_bfloat162 pair = __floats2bfloat162_rn(p0, p1);
-                    packed[e] = *reinterpret_cast<const unsigned*>(&pair);
-                }
-                tmem_st32_bits(tmem_s + c * 32, packed);
+            for (int e = 0; e < 32; ++e) {
+                const float p0 = exp2_approx(fmaf(sv[2 * e], scale_log2, -ref));
+                const float p1 = exp2_approx(fmaf(sv[2 * e + 1], scale_log2, -ref));
+                sum4[e & 3] += p0 + p1;
+                const __nv_bfloat162 pair = __floats2bfloat162_rn(p0, p1);
+                packed[e] = *reinterpret_cast<const unsigned*>(&pair);
             }
-            row_sum = row_sum * alpha + tile_sum;
-            // rescale O where the reference moved (a whole warp at a time: the accesses are collective)
+            tmem_st32_bits(tmem_s, packed);
+            row_sum = row_sum * alpha + ((sum4[0] + sum4[1]) + (sum4[2] + sum4[3]));
+            // Rescale O where the reference moved (a whole warp at a time: the accesses are
+            // collective), after the P V before this tile has finished.  That P V has its
+            // barrier to itself until this thread's arrival below lets the next one be issued,
+            // and "S of this tile is ready" implies that the P V two tiles back, the one before
+            // on that barrier, is complete: the barrier is in the phase of the awaited P V or
+            // one past it, so the parity wait is exact.
             if (t > 0 && ok && __any_sync(0xffffffffu, moved)) {
+                if (!mbar_wait(o_bar + 2 * g + ((t - 1) & 1), ((t - 1) >> 1) & 1)) { atomicExch(error_flag, 27); ok = false; }
+                ok = __all_sync(0xffffffffu, ok);
+                asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory");
+                if (ok) {
 #pragma unroll
-                for (int c = 0; c < 4; ++c) {
-                    float v[32];
-                    tmem_ld32(tmem_o + c * 32, v);
+                    for (int c = 0; c < 4; ++c) {
+                        float v[32];
+                        tmem_ld32(tmem_o + c * 32, v);
 #pragma unroll
-                    for (int e = 0; e < 32; ++e) v[e] *= alpha;
-                    tmem_st32(tmem_o + c * 32, v);
+                        for (int e = 0; e < 32; ++e) v[e] *= alpha;
+                        tmem_st32(tmem_o + c * 32, v);
+                    }
                 }
             }
             asm volatile("tcgen05.wait::st.sync.aligned;\n" ::: "memory");
             asm volatile("tcgen05.fence::before_thread_sync;\n" ::: "memory");
-            mbar_arrive(p_bar + g);
+            mbar_arrive(p_bar + 2 * g + buffer);
         }
 
         // ---- O / sum to the output ----
-        if (my_tiles > 0 && ok && !mbar_wait(o_bar + g, 0)) { atomicExch(error_flag, 26); ok = false; }
+        if (my_tiles > 0 && ok && !mbar_wait(o_bar + 2 * g + ((my_tiles - 1) & 1), ((my_tiles - 1) >> 1) & 1)) {
+            atomicExch(error_flag, 26);
+            ok = false;
+        }
         ok = __all_sync(0xffffffffu, ok);
         asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory");
         const float inv = row_sum > 0.0f ? 1.0f / row_sum : 0.0f;
