@@ -102,3 +102,19 @@ def test_stop_token_and_min_tokens(folders):
     held = llm.generate([prompt], engine.SamplingParams(temperature=0.0, max_tokens=6, min_tokens=6,
                                                         stop_token_ids=[stopper]))[0]
     assert stopper not in held.token_ids[:5] and len(held.token_ids) == 6
+
+
+def test_a_kernel_error_flag_stops_the_engine(folders, monkeypatch):
+    """A kernel that gave up a bounded wait leaves a flag; the engine reads the flags when
+    its requests are done (and now and then) and refuses to hand such results on."""
+    import vllm_from_scratch_b200.kernels as kernels
+    llm = engine.LLM(folders["A"], dtype="float32", device="cpu", enforce_eager=True, max_model_len=64)
+    runner = llm.engine.runner
+    runner.check_device()                                   # nothing wrong
+    monkeypatch.setattr(kernels, "device_error", lambda: "attention kernel gave up waiting (code 25)")
+    with pytest.raises(RuntimeError, match="gave up waiting"):
+        runner.check_device()
+    with pytest.raises(RuntimeError, match="results since the last check are void"):
+        llm.generate([[1, 2, 3]], engine.SamplingParams(temperature=0.0, max_tokens=2))
+    with pytest.raises(engine.EngineDeadError):
+        llm.engine.step()

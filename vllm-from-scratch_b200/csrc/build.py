@@ -144,6 +144,11 @@ def load_library(name: str) -> ctypes.CDLL:
     return library
 
 
+def is_loaded(name: str) -> bool:
+    """Whether this process has loaded the library (and so may have launched its kernels)."""
+    return name in _loaded
+
+
 def compile_all(verbose: bool = True) -> list[Path]:
     """Build every kernel library that has a source file (several at a time)."""
     from concurrent.futures import ThreadPoolExecutor

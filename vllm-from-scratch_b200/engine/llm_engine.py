@@ -130,8 +130,11 @@ class LLMEngine:
                 self.num_steps_ahead += 1
                 self._pending = self._execute(ahead, previous=current)
         outputs = self.scheduler.update(current.plan, current.wait())
-        if self._pending is not None and not self.scheduler.has_unfinished_requests():
+        idle = not self.scheduler.has_unfinished_requests()
+        if self._pending is not None and idle:
             self._pending = None            # everyone stopped: what was queued ahead is of no use
+        if idle or self.num_steps % 256 == 0:
+            self.runner.check_device()      # error flags of the kernels, now and then and at the end
         return outputs
 
     def _overlaps(self) -> bool:

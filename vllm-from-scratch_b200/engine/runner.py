@@ -65,3 +65,12 @@ class ModelRunner:
 
     def step(self, entries: list[StepEntry]) -> torch.Tensor | None:
         return self.step_function.run(entries)
+
+    def check_device(self) -> None:
+        """Raise if a step since the last check fed a token id outside the vocabulary or
+        a kernel gave up a bounded wait (waits for the device; not for every step)."""
+        from .. import kernels
+        self.model.check_token_ids()
+        problem = kernels.device_error()        # None where no kernel library is loaded
+        if problem:
+            raise RuntimeError(f"a kernel reported an error, results since the last check are void: {problem}")

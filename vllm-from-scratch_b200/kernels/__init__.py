@@ -16,7 +16,7 @@ from typing import Sequence
 
 import torch
 
-from ..csrc.build import load_library
+from ..csrc.build import is_loaded, load_library
 
 _DTYPE_CODE = {torch.float32: 0, torch.bfloat16: 1}
 
@@ -97,6 +97,23 @@ def _run(library: str, symbol: str, *args) -> None:
     status = getattr(lib, symbol)(*args)
     if status != 0:
         raise KernelError(lib.b200_last_error().decode())
+
+
+def device_error() -> str | None:
+    """What a kernel whose bounded wait ran out has left behind, or ``None``.  Such a
+    kernel stops issuing work and returns, so its results are wrong: callers check this
+    between steps.  Reads a few bytes from the device (synchronises); the flags are
+    cleared by reading."""
+    found = []
+    if is_loaded("attention_bf16"):
+        code = int(load_library("attention_bf16").b200_attention_error())
+        if code:
+            found.append(f"attention kernel gave up waiting (code {code})")
+    if is_loaded("gemm_bf16"):
+        code = int(load_library("gemm_bf16").b200_stream_gemm_error())
+        if code:
+            found.append(f"matrix-product kernel gave up waiting (code {code})")
+    return "; ".join(found) or None
 
 
 _P = ctypes.c_void_p
