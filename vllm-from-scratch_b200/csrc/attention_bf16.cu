@@ -2,6 +2,7 @@
 // themselves are in attention_bf16_kernels.cuh.
 #include "attention_bf16_kernels.cuh"
 #include "attention_tc.cuh"
+#include "decode_attention_tma.cuh"
 #include "tensor_map.cuh"
 
 // Returns 1 if head_dim / head counts are ones these kernels are built for.
@@ -32,6 +33,41 @@ B200_EXPORT int b200_decode_attention_bf16(
     return fail("decode_attention", "head_dim not built");
 }
 
+// 1 if the decode kernel with tensor copies takes this shape (pages of 8, 16, 32, ... keys).
+B200_EXPORT int b200_decode_attention_tma_supports(int nq, int nkv, int d, int page_size) {
+    return b200_attention_bf16_supports(nq, nkv, d) && page_size >= 8 && (page_size & (page_size - 1)) == 0 ? 1 : 0;
+}
+
+static int* attention_error_flag();
+
+// The same contract as b200_decode_attention_bf16; num_pages: pages in k_pages / v_pages.
+B200_EXPORT int b200_decode_attention_tma_bf16(
+    const void* q, const void* k_pages, const void* v_pages, void* out, float* partial_o,
+    float* partial_ml, const int* seq_lens, const int* block_table, int num_requests, int max_pages,
+    int nq, int nkv, int d, int page_size, int num_pages, float scale, int window, int splits,
+    cudaStream_t stream) {
+    using namespace b200;
+    if (num_requests == 0) return 0;
+    if (!b200_decode_attention_tma_supports(nq, nkv, d, page_size)) return fail("decode_attention", "shape not built");
+    if (splits < 1 || nkv > 65535 || num_requests > 65535) return fail("decode_attention", "grid out of range");
+    if (splits > 1 && (partial_o == nullptr || partial_ml == nullptr))
+        return fail("decode_attention", "scratch for the splits is missing");
+    int* error_flag = attention_error_flag();
+    if (error_flag == nullptr) return fail("decode_attention", "no error flag");
+    const int copy_rows = page_size < kKeys ? page_size : kKeys;
+    const CUtensorMap* map_k = tensor_map_for(k_pages, num_pages * nkv * page_size, d, copy_rows);
+    const CUtensorMap* map_v = tensor_map_for(v_pages, num_pages * nkv * page_size, d, copy_rows);
+    if (map_k == nullptr || map_v == nullptr) return fail("decode_attention", "could not encode a tensor map");
+#define B200_CASE(D)                                                                                        \
+    if (d == D)                                                                                             \
+        return launch_decode_tma<D>(map_k, map_v, q, out, partial_o, partial_ml, seq_lens, block_table,     \
+                                    num_requests, max_pages, nq, nkv, page_size, scale, window, splits,    \
+                                    error_flag, stream);
+    B200_CASE(64) B200_CASE(128) B200_CASE(256)
+#undef B200_CASE
+    return fail("decode_attention", "head_dim not built");
+}
+
 B200_EXPORT int b200_prefill_attention_bf16(
     const void* q, const void* k_pages, const void* v_pages, void* out, const int* query_start,
     const int* seq_lens, const int* block_table, int num_requests, int num_tokens, int max_pages, int nq,
@@ -52,6 +88,19 @@ namespace b200 {
 // Set by a kernel whose bounded wait ran out (0 = never); read and cleared by b200_attention_error().
 __device__ int g_attention_error;
 }  // namespace b200
+
+// Device address of the error flag (per device of the calling thread), or null.
+static int* attention_error_flag() {
+    static int* address[64] = {};
+    int device = 0;
+    if (cudaGetDevice(&device) != cudaSuccess || device < 0 || device >= 64) return nullptr;
+    if (address[device] == nullptr) {
+        void* found = nullptr;
+        if (cudaGetSymbolAddress(&found, b200::g_attention_error) != cudaSuccess) return nullptr;
+        address[device] = static_cast<int*>(found);
+    }
+    return address[device];
+}
 
 B200_EXPORT int b200_attention_error() {
     int code = 0;
@@ -78,14 +127,8 @@ B200_EXPORT int b200_prefill_attention_tc_bf16(
     using namespace b200;
     if (num_requests == 0 || num_tokens == 0) return 0;
     if (!b200_prefill_attention_tc_supports(nq, nkv, d, page_size)) return fail("prefill_attention_tc", "shape not built");
-    static int* error_flag[64] = {};
-    int device = 0;
-    if (cudaGetDevice(&device) != cudaSuccess || device < 0 || device >= 64) return fail("prefill_attention_tc", "no device");
-    if (error_flag[device] == nullptr) {
-        void* found = nullptr;
-        if (cudaGetSymbolAddress(&found, g_attention_error) != cudaSuccess) return fail("prefill_attention_tc", "no error flag");
-        error_flag[device] = static_cast<int*>(found);
-    }
+    int* error_flag = attention_error_flag();
+    if (error_flag == nullptr) return fail("prefill_attention_tc", "no error flag");
     const CUtensorMap* map_q = tensor_map_for(q, num_tokens, nq * d, kAtRows);   // one group of rows per copy
     const int copy_rows = page_size < kAtKeys ? page_size : kAtKeys;            // a page, or the part of it in one tile
     const CUtensorMap* map_k = tensor_map_for(k_pages, num_pages * nkv * page_size, d, copy_rows);
@@ -97,6 +140,6 @@ B200_EXPORT int b200_prefill_attention_tc_bf16(
     dim3 grid(num_tokens / kAtBlockRows + num_requests, nq);
     prefill_attention_tc_kernel<<<grid, kAtThreads, kAtSmem, stream>>>(
         *map_q, *map_k, *map_v, (__nv_bfloat16*)out, query_start, seq_lens, block_table, num_requests, max_pages,
-        nq, nkv, page_size, scale * kLog2e, window, error_flag[device]);
+        nq, nkv, page_size, scale * kLog2e, window, error_flag);
     return check_launch("prefill_attention_tc");
 }

@@ -51,12 +51,17 @@ def paged_attention_bf16(q, k_pages, v_pages, out, query_start, seq_lens, block_
         if splits > 1:
             partial_o = torch.empty((tokens * num_q_heads * splits, head_dim), dtype=torch.float32, device=q.device)
             partial_ml = torch.empty((tokens * num_q_heads * splits, 2), dtype=torch.float32, device=q.device)
-        status = lib.b200_decode_attention_bf16(
-            _P(q.data_ptr()), _P(k_pages.data_ptr()), _P(v_pages.data_ptr()), _P(out.data_ptr()),
-            _P(partial_o.data_ptr() if splits > 1 else 0), _P(partial_ml.data_ptr() if splits > 1 else 0),
-            _P(seq_lens.data_ptr()), _P(block_table.data_ptr()), _I(requests), _I(block_table.shape[1]),
-            _I(num_q_heads), _I(num_kv_heads), _I(head_dim), _I(page_size), _F(scale), _I(window or 0),
-            _I(splits), _stream())
+        common = (_P(q.data_ptr()), _P(k_pages.data_ptr()), _P(v_pages.data_ptr()), _P(out.data_ptr()),
+                  _P(partial_o.data_ptr() if splits > 1 else 0), _P(partial_ml.data_ptr() if splits > 1 else 0),
+                  _P(seq_lens.data_ptr()), _P(block_table.data_ptr()), _I(requests), _I(block_table.shape[1]),
+                  _I(num_q_heads), _I(num_kv_heads), _I(head_dim), _I(page_size))
+        tail = (_F(scale), _I(window or 0), _I(splits), _stream())
+        if (os.environ.get("B200_NO_TMA_DECODE") is None
+                and lib.b200_decode_attention_tma_supports(num_q_heads, num_kv_heads, head_dim, page_size)):
+            # keys and values by tensor copies straight from the pages
+            status = lib.b200_decode_attention_tma_bf16(*common, _I(k_pages.shape[0]), *tail)
+        else:
+            status = lib.b200_decode_attention_bf16(*common, *tail)
     elif (max_query_len >= TC_MIN_QUERY_LEN and os.environ.get("B200_NO_TC_ATTENTION") is None
           and lib.b200_prefill_attention_tc_supports(num_q_heads, num_kv_heads, head_dim, page_size)):
         # long portions of prompts: the tcgen05 / tensor-memory kernel
