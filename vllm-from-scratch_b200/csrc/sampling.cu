@@ -82,7 +82,21 @@ __global__ void __launch_bounds__(kSampleThreads) sample_kernel(
 
     if (temp < greedy_eps) {
         ArgMax mine{-INFINITY, 0x7fffffff};
-        for (int i = tid; i < vocab; i += blockDim.x) mine = better(mine, ArgMax{x[i], i});
+        if ((vocab & 3) == 0 && ((uintptr_t)x & 15) == 0) {
+            // four 16-byte loads in flight per thread: one block has a whole row to itself
+            const float4* x4 = reinterpret_cast<const float4*>(x);
+            const int quads = vocab >> 2;
+#pragma unroll 4
+            for (int i = tid; i < quads; i += blockDim.x) {
+                const float4 v = x4[i];
+                mine = better(mine, ArgMax{v.x, 4 * i});
+                mine = better(mine, ArgMax{v.y, 4 * i + 1});
+                mine = better(mine, ArgMax{v.z, 4 * i + 2});
+                mine = better(mine, ArgMax{v.w, 4 * i + 3});
+            }
+        } else {
+            for (int i = tid; i < vocab; i += blockDim.x) mine = better(mine, ArgMax{x[i], i});
+        }
         mine = block_argmax(mine, arg_scratch);
         if (tid == 0) tokens[row] = mine.index;
         return;
