@@ -91,6 +91,40 @@ def test_same_key_same_token_and_large_vocabulary():
     assert bool(keep[a].all())
 
 
+def _large_rows():
+    g = torch.Generator().manual_seed(21)
+    vocab = 151936
+    spread = torch.randn(vocab, generator=g) * 3                 # thresholds fall into sparse coarse bins
+    crowd = torch.randn(vocab, generator=g) * 0.01               # every token within 0.05: one crowded bin
+    tail = torch.full((vocab,), -60.0)                           # all but a hundred tokens far below the maximum
+    tail[torch.randperm(vocab, generator=g)[:100]] = torch.randn(100, generator=g)
+    peaked = torch.randn(vocab, generator=g)
+    peaked[torch.randperm(vocab, generator=g)[:6]] += torch.tensor([9.0, 8.5, 8.0, 7.5, 7.0, 6.5])
+    return {"spread": spread, "crowd": crowd, "tail": tail, "peaked": peaked}
+
+
+@pytest.mark.parametrize("name,temperature,top_k,top_p,min_p", [
+    ("spread", 1.0, 5, 1.0, 0.0), ("spread", 0.8, 300, 0.9, 0.0), ("spread", 1.0, 0, 0.999, 0.0),
+    ("crowd", 1.0, 6, 1.0, 0.0), ("crowd", 1.0, 70000, 1.0, 0.0), ("crowd", 1.0, 0, 0.5, 0.0),
+    ("crowd", 1.0, 50000, 0.7, 0.0), ("tail", 1.0, 500, 1.0, 0.0), ("tail", 1.0, 40, 0.9, 0.0),
+    ("tail", 1.0, 0, 0.999999, 0.0), ("peaked", 1.0, 0, 0.6, 0.0), ("peaked", 1.3, 4, 0.95, 0.001),
+])
+def test_filters_on_a_large_vocabulary(name, temperature, top_k, top_p, min_p):
+    """The threshold search looks at the row coarsely first and then selects inside one
+    bin held in shared memory; thresholds in a crowded bin or in the far tail take the
+    path over the whole row.  All of them must keep the reference's set."""
+    row = _large_rows()[name]
+    keep = plain_keep_mask(row, temperature, top_k, top_p, min_p)
+    tokens = draw(row, 2048, temperature, top_k, top_p, min_p)
+    assert bool(keep[tokens].all()), "a token outside the reference's candidate set was drawn"
+    kept = int(keep.sum())
+    if kept <= 8:
+        assert set(tokens.tolist()) == set(keep.nonzero().flatten().tolist())
+    else:
+        # a kept set that large cannot be hit by so few distinct tokens if the cut were far too high
+        assert len(set(tokens.tolist())) >= min(kept, 64) // 2
+
+
 def test_penalties_and_masks_follow_the_formula():
     import vllm_from_scratch_b200.kernels as k
     vocab = 503

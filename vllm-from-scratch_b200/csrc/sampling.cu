@@ -7,7 +7,12 @@
 // logit found by radix selection over the order-preserving integer image of the
 // float (four passes of 256 bins): top-k by counts, top-p by probability mass in
 // 2^-40 fixed point, so that the sums do not depend on the order of the atomics
-// and a seed always reproduces its tokens.  Ties at a threshold are all kept (the
+// and a seed always reproduces its tokens.  The selection does not run over the
+// whole row: one pass sorts the kept tokens into coarse bins by their distance
+// below the maximum, the bin that holds the threshold is copied into shared memory
+// (a few thousand keys at most) and the radix selection runs there; only a
+// threshold in the far tail, or a bin too crowded for the list, falls back to
+// selecting over the row.  Ties at a threshold are all kept (the
 // reference keeps ties at the k-th value too, and breaks top-p ties by sort order).
 // The draw is Gumbel-max: argmax(x_i - log(E_i)), E_i exponential from Philox
 // keyed by (seed, index of the generated token, token id), equal in distribution
@@ -65,15 +70,139 @@ __device__ ArgMax block_argmax(ArgMax mine, ArgMax* scratch) {
 }
 
 // One block per row.
-__global__ void __launch_bounds__(kSampleThreads) sample_kernel(
+// Calls f(value, index) for every logit of a row, this thread's share.  A block has a whole
+// row to itself, so each thread keeps four 16-byte loads in flight where the row allows it.
+template <typename F>
+__device__ __forceinline__ void for_each_logit(const float* __restrict__ x, int vocab, F&& f) {
+    const int tid = threadIdx.x, step = blockDim.x;
+    if ((vocab & 3) == 0 && ((uintptr_t)x & 15) == 0) {
+        const float4* x4 = reinterpret_cast<const float4*>(x);
+        const int quads = vocab >> 2;
+#pragma unroll 4
+        for (int i = tid; i < quads; i += step) {
+            const float4 v = x4[i];
+            f(v.x, 4 * i);
+            f(v.y, 4 * i + 1);
+            f(v.z, 4 * i + 2);
+            f(v.w, 4 * i + 3);
+        }
+    } else {
+        for (int i = tid; i < vocab; i += step) f(x[i], i);
+    }
+}
+
+__device__ __forceinline__ float key_value(unsigned key) {
+    return __uint_as_float((key & 0x80000000u) ? (key & 0x7fffffffu) : ~key);
+}
+
+// Probability mass of a scaled logit in 2^-40 fixed point (0 from about 27.7 below the maximum).
+// The product with a power of two is exact in float, so this is the floor of exp() * 2^40.
+__device__ __forceinline__ unsigned long long fixed_mass(float y, float y_max) {
+    return __float2ull_rz(expf(y - y_max) * 1099511627776.0f);
+}
+
+// A first, coarse look at a row: kept tokens by how far they lie below the maximum, eight
+// bins per unit, the last bin for everything 31.875 and more below.  Bin indices fall as
+// the logit rises, so bins are ranges of the key order.  Random-looking logits spread
+// over many bins, which keeps the shared-memory atomics apart; the crowded far bin is
+// counted in registers.
+constexpr int kCoarseBins = 256;
+constexpr float kCoarsePerUnit = 8.0f;
+constexpr int kListCapacity = 6144;             // candidates of one coarse bin held in shared memory
+
+__device__ __forceinline__ int coarse_bin(float y, float y_max) {
+    const float d = (y_max - y) * kCoarsePerUnit;
+    return d >= (float)(kCoarseBins - 1) ? kCoarseBins - 1 : (int)d;
+}
+
+struct SampleShared {
+    ArgMax arg_scratch[33];
+    unsigned long long bins[256];               // one radix pass: counts or masses per byte value
+    unsigned coarse_mass_lo[kCoarseBins], coarse_mass_hi[kCoarseBins];     // 64-bit sums kept as two words
+    unsigned coarse_count[kCoarseBins];
+    unsigned list[kListCapacity];               // keys of the kept tokens of one coarse bin
+    unsigned list_size;
+    unsigned prefix_key;
+    unsigned long long carry;
+    int chosen_bin;
+    unsigned long long chosen_before;           // count above / mass below the chosen bin
+};
+
+// The k-th largest key among the keys >= cut that `each` visits (`each(f)` calls f(key) for
+// this thread's share).  Fewer than k such keys: the smallest possible prefix, which cuts nothing.
+template <typename Each>
+__device__ unsigned select_kth_largest(Each&& each, unsigned cut, int k, SampleShared& sh) {
+    const int tid = threadIdx.x;
+    unsigned prefix = 0;
+    int remaining = k;
+    for (int pass = 0; pass < 4; ++pass) {
+        const int shift = 24 - 8 * pass;
+        const unsigned mask = pass == 0 ? 0u : (0xffffffffu << (shift + 8));
+        for (int b = tid; b < 256; b += blockDim.x) sh.bins[b] = 0ull;
+        __syncthreads();
+        each([&](unsigned key) {
+            if (key >= cut && (key & mask) == prefix) atomicAdd(&sh.bins[(key >> shift) & 255u], 1ull);
+        });
+        __syncthreads();
+        if (tid == 0) {
+            int b = 255;
+            unsigned long long above = 0;
+            for (; b > 0; --b) {
+                if (above + sh.bins[b] >= (unsigned long long)remaining) break;
+                above += sh.bins[b];
+            }
+            sh.prefix_key = prefix | ((unsigned)b << shift);
+            sh.carry = above;
+        }
+        __syncthreads();
+        prefix = sh.prefix_key;
+        remaining -= (int)sh.carry;
+        __syncthreads();
+    }
+    return prefix;
+}
+
+// The smallest key at which the mass of the visited keys >= cut, summed from the smallest
+// key up and starting from `below`, first exceeds `target`.
+template <typename Each>
+__device__ unsigned select_mass_from_below(Each&& each, unsigned cut, unsigned long long target,
+                                           unsigned long long below, float y_max, SampleShared& sh) {
+    const int tid = threadIdx.x;
+    unsigned prefix = 0;
+    for (int pass = 0; pass < 4; ++pass) {
+        const int shift = 24 - 8 * pass;
+        const unsigned mask = pass == 0 ? 0u : (0xffffffffu << (shift + 8));
+        for (int b = tid; b < 256; b += blockDim.x) sh.bins[b] = 0ull;
+        __syncthreads();
+        each([&](unsigned key) {
+            if (key >= cut && (key & mask) == prefix)
+                atomicAdd(&sh.bins[(key >> shift) & 255u], fixed_mass(key_value(key), y_max));
+        });
+        __syncthreads();
+        if (tid == 0) {
+            int b = 0;
+            unsigned long long mass = below;
+            for (; b < 255; ++b) {
+                if (mass + sh.bins[b] > target) break;       // this bin holds the first kept token
+                mass += sh.bins[b];
+            }
+            sh.prefix_key = prefix | ((unsigned)b << shift);
+            sh.carry = mass;
+        }
+        __syncthreads();
+        prefix = sh.prefix_key;
+        below = sh.carry;
+        __syncthreads();
+    }
+    return prefix;
+}
+
+__global__ void __launch_bounds__(kSampleThreads, 1) sample_kernel(
     const float* __restrict__ logits, int vocab, const float* __restrict__ temperature,
     const int* __restrict__ top_k, const float* __restrict__ top_p, const float* __restrict__ min_p,
     const unsigned long long* __restrict__ seeds, const unsigned long long* __restrict__ draw_index,
     int* __restrict__ tokens, float greedy_eps) {
-    __shared__ ArgMax arg_scratch[33];
-    __shared__ unsigned long long bins[256];
-    __shared__ unsigned prefix_key;
-    __shared__ unsigned long long carry;
+    __shared__ SampleShared sh;
 
     const int row = blockIdx.x;
     const float* x = logits + (size_t)row * vocab;
@@ -82,117 +211,148 @@ __global__ void __launch_bounds__(kSampleThreads) sample_kernel(
 
     if (temp < greedy_eps) {
         ArgMax mine{-INFINITY, 0x7fffffff};
-        if ((vocab & 3) == 0 && ((uintptr_t)x & 15) == 0) {
-            // four 16-byte loads in flight per thread: one block has a whole row to itself
-            const float4* x4 = reinterpret_cast<const float4*>(x);
-            const int quads = vocab >> 2;
-#pragma unroll 4
-            for (int i = tid; i < quads; i += blockDim.x) {
-                const float4 v = x4[i];
-                mine = better(mine, ArgMax{v.x, 4 * i});
-                mine = better(mine, ArgMax{v.y, 4 * i + 1});
-                mine = better(mine, ArgMax{v.z, 4 * i + 2});
-                mine = better(mine, ArgMax{v.w, 4 * i + 3});
-            }
-        } else {
-            for (int i = tid; i < vocab; i += blockDim.x) mine = better(mine, ArgMax{x[i], i});
-        }
-        mine = block_argmax(mine, arg_scratch);
+        for_each_logit(x, vocab, [&](float v, int i) { mine = better(mine, ArgMax{v, i}); });
+        mine = block_argmax(mine, sh.arg_scratch);
         if (tid == 0) tokens[row] = mine.index;
         return;
     }
 
     // Scaled logits y = x / T; maximum and normaliser.
     ArgMax top{-INFINITY, 0x7fffffff};
-    for (int i = tid; i < vocab; i += blockDim.x) top = better(top, ArgMax{x[i] / temp, i});
-    top = block_argmax(top, arg_scratch);
+    for_each_logit(x, vocab, [&](float v, int i) { top = better(top, ArgMax{v / temp, i}); });
+    top = block_argmax(top, sh.arg_scratch);
     const float y_max = top.value;
 
     unsigned cut = 0;                       // keep tokens whose key >= cut
     const float mp = min_p[row];
     if (mp > 0.0f) cut = ordered_key(y_max + logf(mp));
 
+    auto each_in_row = [&](auto&& f) { for_each_logit(x, vocab, [&](float v, int) { f(ordered_key(v / temp)); }); };
+    auto each_in_list = [&](auto&& f) {
+        const int n = (int)sh.list_size;
+        for (int i = tid; i < n; i += blockDim.x) f(sh.list[i]);
+    };
+    // Counts (and, for top-p, masses) of the kept tokens per coarse bin.
+    // (A mass is added as two 32-bit words with the carry passed on by hand: nearly all
+    // masses fit the low word, and 32-bit shared-memory atomics are the fast ones.)
+    auto add_mass = [&](int b, unsigned long long m) {
+        const unsigned lo = (unsigned)m, hi = (unsigned)(m >> 32);
+        const unsigned before = atomicAdd(&sh.coarse_mass_lo[b], lo);
+        const unsigned carry = before + lo < before ? 1u : 0u;
+        if (hi + carry) atomicAdd(&sh.coarse_mass_hi[b], hi + carry);
+    };
+    auto mass_of_bin = [&](int b) { return ((unsigned long long)sh.coarse_mass_hi[b] << 32) + sh.coarse_mass_lo[b]; };
+    auto look = [&](bool with_mass) {
+        for (int b = tid; b < kCoarseBins; b += blockDim.x) sh.coarse_count[b] = sh.coarse_mass_lo[b] = sh.coarse_mass_hi[b] = 0u;
+        __syncthreads();
+        unsigned far_count = 0;
+        unsigned long long far_mass = 0;
+        each_in_row([&](unsigned key) {
+            if (key < cut) return;
+            const float y = key_value(key);
+            const int b = coarse_bin(y, y_max);
+            if (b == kCoarseBins - 1) {
+                ++far_count;
+                if (with_mass) far_mass += fixed_mass(y, y_max);
+            } else {
+                atomicAdd(&sh.coarse_count[b], 1u);
+                if (with_mass) add_mass(b, fixed_mass(y, y_max));
+            }
+        });
+#pragma unroll
+        for (int offset = 16; offset > 0; offset >>= 1) {
+            far_count += __shfl_xor_sync(0xffffffffu, far_count, offset);
+            far_mass += __shfl_xor_sync(0xffffffffu, far_mass, offset);
+        }
+        if ((tid & 31) == 0 && far_count) {
+            atomicAdd(&sh.coarse_count[kCoarseBins - 1], far_count);
+            add_mass(kCoarseBins - 1, far_mass);
+        }
+        __syncthreads();
+    };
+    // The kept tokens of coarse bin `bin` into the list (a warp appends together).
+    auto gather = [&](int bin) {
+        if (tid == 0) sh.list_size = 0u;
+        __syncthreads();
+        each_in_row([&](unsigned key) {
+            const bool mine = key >= cut && coarse_bin(key_value(key), y_max) == bin;
+            const unsigned active = __activemask();
+            const unsigned who = __ballot_sync(active, mine);
+            if (who == 0u) return;
+            const int lane = tid & 31, leader = __ffs(who) - 1;
+            unsigned base = 0;
+            if (lane == leader) base = atomicAdd(&sh.list_size, (unsigned)__popc(who));
+            base = __shfl_sync(active, base, leader);
+            if (mine) {
+                const unsigned at = base + __popc(who & ((1u << lane) - 1u));
+                if (at < (unsigned)kListCapacity) sh.list[at] = key;
+            }
+        });
+        __syncthreads();
+    };
+
     // ---- top-k: the k-th largest key among the kept ones -------------------
     const int k = top_k[row];
+    const float p = top_p[row];
+    bool looked = false;                    // the coarse bins hold counts and masses under the current cut
     if (k > 0 && k < vocab) {
-        unsigned prefix = 0;
-        int remaining = k;
-        for (int pass = 0; pass < 4; ++pass) {
-            const int shift = 24 - 8 * pass;
-            const unsigned mask = pass == 0 ? 0u : (0xffffffffu << (shift + 8));
-            for (int b = tid; b < 256; b += blockDim.x) bins[b] = 0ull;
-            __syncthreads();
-            for (int i = tid; i < vocab; i += blockDim.x) {
-                const unsigned key = ordered_key(x[i] / temp);
-                if (key >= cut && (key & mask) == prefix)
-                    atomicAdd(&bins[(key >> shift) & 255u], 1ull);
+        look(p < 1.0f);
+        looked = true;
+        if (tid == 0) {
+            unsigned long long above = 0;
+            int b = 0;
+            for (; b < kCoarseBins; ++b) {
+                if (above + sh.coarse_count[b] >= (unsigned long long)k) break;
+                above += sh.coarse_count[b];
             }
-            __syncthreads();
-            if (tid == 0) {
-                int b = 255;
-                unsigned long long above = 0;
-                for (; b > 0; --b) {
-                    if (above + bins[b] >= (unsigned long long)remaining) break;
-                    above += bins[b];
-                }
-                prefix_key = prefix | ((unsigned)b << shift);
-                carry = above;
-            }
-            __syncthreads();
-            prefix = prefix_key;
-            remaining -= (int)carry;
-            __syncthreads();
+            sh.chosen_bin = b;                  // kCoarseBins: fewer than k tokens are kept
+            sh.chosen_before = above;
         }
-        if (prefix > cut) cut = prefix;
+        __syncthreads();
+        const int bin = sh.chosen_bin;
+        const unsigned long long above = sh.chosen_before;
+        __syncthreads();
+        if (bin < kCoarseBins) {
+            unsigned kth;
+            if (bin < kCoarseBins - 1 && sh.coarse_count[bin] <= (unsigned)kListCapacity) {
+                gather(bin);
+                kth = select_kth_largest(each_in_list, cut, k - (int)above, sh);
+            } else {
+                kth = select_kth_largest(each_in_row, cut, k, sh);         // the far bin, or a crowd: the whole row
+            }
+            if (kth > cut) { cut = kth; looked = false; }
+        }
     }
 
     // ---- top-p: drop the smallest tokens while their mass stays <= 1 - p ----
-    const float p = top_p[row];
     if (p < 1.0f) {
-        const double kFixed = 1099511627776.0;     // 2^40
-        unsigned long long local = 0;
-        for (int i = tid; i < vocab; i += blockDim.x) {
-            const float y = x[i] / temp;
-            if (ordered_key(y) >= cut) local += (unsigned long long)((double)expf(y - y_max) * kFixed);
-        }
-        for (int b = tid; b < 256; b += blockDim.x) bins[b] = 0ull;
-        __syncthreads();
-        atomicAdd(&bins[0], local);
-        __syncthreads();
-        const unsigned long long total = bins[0];
-        const unsigned long long target = (unsigned long long)((double)total * (double)(1.0f - p));
-        unsigned prefix = 0;
-        unsigned long long below = 0;              // mass of kept tokens with a smaller key
-        __syncthreads();
-        for (int pass = 0; pass < 4; ++pass) {
-            const int shift = 24 - 8 * pass;
-            const unsigned mask = pass == 0 ? 0u : (0xffffffffu << (shift + 8));
-            for (int b = tid; b < 256; b += blockDim.x) bins[b] = 0ull;
-            __syncthreads();
-            for (int i = tid; i < vocab; i += blockDim.x) {
-                const float y = x[i] / temp;
-                const unsigned key = ordered_key(y);
-                if (key >= cut && (key & mask) == prefix)
-                    atomicAdd(&bins[(key >> shift) & 255u],
-                              (unsigned long long)((double)expf(y - y_max) * kFixed));
+        if (!looked) look(true);
+        if (tid == 0) {
+            unsigned long long total = 0;
+            for (int b = 0; b < kCoarseBins; ++b) total += mass_of_bin(b);
+            const unsigned long long target = (unsigned long long)((double)total * (double)(1.0f - p));
+            unsigned long long below = 0;
+            int b = kCoarseBins - 1;
+            for (; b > 0; --b) {
+                if (below + mass_of_bin(b) > target) break;
+                below += mass_of_bin(b);
             }
-            __syncthreads();
-            if (tid == 0) {
-                int b = 0;
-                unsigned long long mass = below;
-                for (; b < 255; ++b) {
-                    if (mass + bins[b] > target) break;   // this bin holds the first kept token
-                    mass += bins[b];
-                }
-                prefix_key = prefix | ((unsigned)b << shift);
-                carry = mass;
-            }
-            __syncthreads();
-            prefix = prefix_key;
-            below = carry;
-            __syncthreads();
+            sh.chosen_bin = b;
+            sh.chosen_before = below;
+            sh.carry = target;
         }
-        if (prefix > cut) cut = prefix;
+        __syncthreads();
+        const int bin = sh.chosen_bin;
+        const unsigned long long below = sh.chosen_before, target = sh.carry;
+        __syncthreads();
+        unsigned edge;
+        if (bin < kCoarseBins - 1 && sh.coarse_count[bin] <= (unsigned)kListCapacity) {
+            gather(bin);
+            edge = select_mass_from_below(each_in_list, cut, target, below, y_max, sh);
+        } else {
+            edge = select_mass_from_below(each_in_row, cut, target, 0ull, y_max, sh);
+        }
+        if (edge > cut) cut = edge;
         const unsigned top_key = ordered_key(y_max);
         if (cut > top_key) cut = top_key;          // the largest token always stays
     }
@@ -201,7 +361,20 @@ __global__ void __launch_bounds__(kSampleThreads) sample_kernel(
     const unsigned long long seed = seeds[row], draw = draw_index[row];
     ArgMax best{-INFINITY, 0x7fffffff};
     const int chunks = (vocab + 3) >> 2;
+    const bool vec = (vocab & 3) == 0 && ((uintptr_t)x & 15) == 0;
     for (int c = tid; c < chunks; c += blockDim.x) {
+        float xs[4];
+        if (vec) {
+            const float4 v = reinterpret_cast<const float4*>(x)[c];
+            xs[0] = v.x; xs[1] = v.y; xs[2] = v.z; xs[3] = v.w;
+        } else {
+#pragma unroll
+            for (int j = 0; j < 4; ++j) xs[j] = 4 * c + j < vocab ? x[4 * c + j] : -INFINITY;
+        }
+        bool any = false;
+#pragma unroll
+        for (int j = 0; j < 4; ++j) any = any || (4 * c + j < vocab && ordered_key(xs[j] / temp) >= cut);
+        if (!any) continue;                        // no kept token here: its random numbers are not needed
         curandStatePhilox4_32_10_t state;
         curand_init(seed, draw, 4ull * (unsigned long long)c, &state);
         const float4 u = curand_uniform4(&state);
@@ -210,13 +383,13 @@ __global__ void __launch_bounds__(kSampleThreads) sample_kernel(
         for (int j = 0; j < 4; ++j) {
             const int i = 4 * c + j;
             if (i >= vocab) break;
-            const float y = x[i] / temp;
+            const float y = xs[j] / temp;
             if (ordered_key(y) < cut) continue;
             const float e = fmaxf(-logf(us[j]), 1e-30f);
             best = better(best, ArgMax{y - logf(e), i});
         }
     }
-    best = block_argmax(best, arg_scratch);
+    best = block_argmax(best, sh.arg_scratch);
     if (tid == 0) tokens[row] = best.index == 0x7fffffff ? top.index : best.index;
 }
 
