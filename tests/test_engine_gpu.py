@@ -214,3 +214,24 @@ def test_steps_queued_ahead_give_the_same_tokens(folders, dtype):
         assert ahead.token_ids == sync.token_ids, f"request {index}"
         assert ahead.finish_reason == sync.finish_reason and ahead.stop_reason == sync.stop_reason
     assert results[True][1].finish_reason.name == "STOP" and len(results[True][1].token_ids) <= 11
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_repeated_mixed_steps_replay_graphs_with_the_same_tokens(folders, dtype):
+    """Prompts cut under a small token budget give steps of the same shape again and again
+    (a portion that fills the budget beside the decoding requests); from the second time on
+    such a step is a graph replay.  Tokens must equal those of the engine without graphs."""
+    import vllm_from_scratch_b200 as engine
+    raw = tiny_configs.TINY_B
+    prompts = [helpers.random_tokens(raw["vocab_size"], n, seed=400 + i) for i, n in enumerate([150, 97, 140, 33, 120])]
+    params = engine.SamplingParams(temperature=0.0, max_tokens=12)
+    results = {}
+    for eager in (True, False):
+        llm = engine.LLM(folders["B"], dtype=dtype, max_model_len=192, block_size=8, max_num_seqs=3,
+                         max_num_batched_tokens=24, enforce_eager=eager)
+        results[eager] = [o.token_ids for o in llm.generate(prompts, params)]
+        llm.engine.runner.manager.check_invariants()
+        if not eager:
+            assert llm.engine.mixed_graphs.replays >= 8, "steps of a repeated shape must be replayed"
+            assert llm.engine.decode_graphs.replays > 0
+    assert results[False] == results[True]

@@ -11,6 +11,15 @@ batches (minivllm/worker/gpu_model_runner.py:1108-1165, 1215-1276, 1415-1477).
 Block tables are captured at their full width (``max_model_len`` positions) and
 kernel launch shapes are chosen for that length, so a replay is valid for any
 context length.
+
+Steps that also bring portions of prompts repeat their shapes too (a prompt cut
+under a token budget fills the budget step after step): ``MixedGraphs`` keeps a
+graph per (tokens, requests rounded up to a power of two, wanted rows likewise,
+kind of longest portion) once a shape has come twice, and runs other shapes through
+the ordinary step function.  The requests added by the rounding have no tokens, the
+wanted rows added repeat row 0 and are dropped from the result.  Everything that
+differs between steps of one shape (which tokens belong to which request, positions,
+lengths, pages) is data in the packed buffer.
 """
 
 from __future__ import annotations
@@ -111,3 +120,73 @@ class DecodeGraphs:
         if len(wanted) == len(entries):
             return captured.logits[:len(entries)]
         return captured.logits[torch.tensor(wanted, device=captured.logits.device)]
+
+
+class MixedGraphs:
+    """Graph replay for steps of any composition whose shape has been seen before."""
+
+    def __init__(self, runner: ModelRunner, max_model_len: int, max_graphs: int = 24) -> None:
+        self.runner = runner
+        self.step_function = runner.step_function
+        self.table_width = -(-max_model_len // runner.storage.page_size)
+        self.max_model_len = max_model_len
+        self.max_graphs = max_graphs
+        self._seen: dict[tuple, int] = {}
+        self._graphs: dict[tuple, _Captured] = {}
+        self._pool = None
+        self.replays = 0
+        self.last_h2d_bytes = 0
+
+    @staticmethod
+    def _portion_kind(longest: int) -> int:
+        """What the kernels' dispatch distinguishes about the longest portion."""
+        from ..kernels.attention_bf16 import TC_MIN_QUERY_LEN
+        return 0 if longest == 1 else (2 if longest >= TC_MIN_QUERY_LEN else 1)
+
+    def run(self, entries: list[StepEntry]) -> torch.Tensor | None:
+        """The same result as ``StepFunction.run``."""
+        entries = [entry for entry in entries if entry.tokens]
+        if not entries or any(e.start + len(e.tokens) > self.max_model_len for e in entries):
+            return self.step_function.run(entries)
+        tokens = sum(len(e.tokens) for e in entries)
+        wanted = sum(len(e.want) for e in entries)
+        requests_up = 1 << (len(entries) - 1).bit_length()
+        wanted_up = 0 if wanted == 0 else max(requests_up, 1 << (wanted - 1).bit_length())
+        key = (tokens, requests_up, wanted_up, self._portion_kind(max(len(e.tokens) for e in entries)))
+        captured = self._graphs.get(key)
+        if captured is None:
+            self._seen[key] = self._seen.get(key, 0) + 1
+            if self._seen[key] < 2 or len(self._graphs) >= self.max_graphs:
+                return self.step_function.run(entries)
+        self.runner.storage.zero_slots(self.runner.manager.take_fresh_slots())
+        host, meta = self.step_function.pack_host(entries, pad_requests=requests_up, table_width=self.table_width,
+                                                  pad_tokens=0, pad_wanted=wanted_up)
+        if captured is None:
+            captured = self._graphs[key] = self._capture(host, meta)
+        captured.packed.copy_(host, non_blocking=True)
+        self.last_h2d_bytes = host.numel() * host.element_size()
+        captured.graph.replay()
+        self.replays += 1
+        return None if wanted == 0 else captured.logits[:wanted]
+
+    def _capture(self, host: torch.Tensor, meta: dict) -> _Captured:
+        device = self.runner.device
+        packed = torch.empty(host.numel(), dtype=torch.int32, device=device)
+        packed.copy_(host, non_blocking=True)
+        meta = {**meta, "max_seq_len": self.max_model_len}
+        ctx, token_ids, want_rows = self.step_function.context_from(packed, meta)
+        model, views = self.runner.model, self.runner.storage.views
+
+        def body() -> torch.Tensor | None:
+            x, residual = model.forward(token_ids, ctx, views)
+            return None if meta["num_wanted"] == 0 else model.logits(x, residual, want_rows)
+
+        # No warm-up run: a step of this very shape has gone through the ordinary step
+        # function before (that is why it is captured now), so every kernel it launches is
+        # compiled, loaded and configured.
+        graph = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(graph, pool=self._pool):
+            logits = body()
+        if self._pool is None:
+            self._pool = graph.pool()
+        return _Captured(graph, packed, meta, logits, (ctx, token_ids, want_rows))

@@ -73,9 +73,13 @@ class LLMEngine:
         self._pending: _InFlight | None = None
         self._host_tokens: list[torch.Tensor] = []
         self.decode_graphs = None
+        self.mixed_graphs = None
         if not model.enforce_eager and self.runner.device.type == "cuda":
-            from .decode_graph import DecodeGraphs
+            from .decode_graph import DecodeGraphs, MixedGraphs
             self.decode_graphs = DecodeGraphs(self.runner, sched.max_num_seqs, model.max_model_len)
+            if not self.runner.storage.has_state:
+                # (parts with state of their own may look at the step from the host)
+                self.mixed_graphs = MixedGraphs(self.runner, model.max_model_len)
 
     # ----------------------------------------------------------------- requests
     def add_request(self, request_id: str, prompt_token_ids: Sequence[int],
@@ -173,6 +177,8 @@ class LLMEngine:
             logits = self.decode_graphs.run(entries, device_tokens=(previous.tokens, rows))
         elif self.decode_graphs is not None and self.decode_graphs.accepts(entries):
             logits = self.decode_graphs.run(entries)
+        elif self.mixed_graphs is not None:
+            logits = self.mixed_graphs.run(entries)
         else:
             logits = self.runner.step(entries)
         if self._first_inputs is None:
@@ -206,6 +212,7 @@ class LLMEngine:
 
     def shutdown(self) -> None:
         self.decode_graphs = None
+        self.mixed_graphs = None
 
 
 class LLM:

@@ -49,15 +49,17 @@ class StepFunction:
 
     # ------------------------------------------------------------------ packing
     def pack_host(self, entries: list[StepEntry], pad_requests: int | None = None,
-                  table_width: int | None = None) -> tuple[torch.Tensor, dict]:
-        """Describe the batch in one pinned int32 buffer.  ``pad_requests`` adds
-        requests of one token that read and write nothing (for shapes fixed in
-        advance); ``table_width`` fixes the width of the block tables."""
+                  table_width: int | None = None, pad_tokens: int = 1, pad_wanted: int = 0
+                  ) -> tuple[torch.Tensor, dict]:
+        """Describe the batch in one pinned int32 buffer.  For shapes fixed in advance:
+        ``pad_requests`` adds requests of ``pad_tokens`` tokens (one or none) that read and
+        write nothing, ``pad_wanted`` repeats the first token's row up to that many wanted
+        rows, ``table_width`` fixes the width of the block tables."""
         page_size = self.page_size
         real = len(entries)
         num_requests = max(real, pad_requests or 0)
         padding = num_requests - real
-        lengths = [len(entry.tokens) for entry in entries] + [1] * padding
+        lengths = [len(entry.tokens) for entry in entries] + [pad_tokens] * padding
         num_tokens = sum(lengths)
         query_start = np.zeros(num_requests + 1, dtype=np.int32)
         np.cumsum(lengths, out=query_start[1:])
@@ -66,7 +68,7 @@ class StepFunction:
         # Padded requests use the spare state slot past the last real one.
         slots = np.array([self.manager.slot(entry.request_id) for entry in entries]
                          + [self.storage.max_requests] * padding, dtype=np.int32)
-        zeros = np.zeros(padding, dtype=np.int32)
+        zeros = np.zeros(padding * pad_tokens, dtype=np.int32)
         token_ids = np.concatenate([np.asarray(entry.tokens, dtype=np.int32) for entry in entries] + [zeros])
         positions = np.concatenate([np.arange(entry.start, entry.start + len(entry.tokens), dtype=np.int32)
                                     for entry in entries] + [zeros])
@@ -78,6 +80,7 @@ class StepFunction:
                     raise ValueError(f"request {entry.request_id!r}: wanted place {place} is outside "
                                      f"its {lengths[row]} tokens of this step")
                 want_rows.append(int(query_start[row]) + place)
+        want_rows += [0] * max(0, pad_wanted - len(want_rows))
         want = np.asarray(want_rows, dtype=np.int32)
 
         pieces = [token_ids, positions, token_request, query_start, seq_lens, slots, want]
