@@ -118,3 +118,29 @@ def test_a_kernel_error_flag_stops_the_engine(folders, monkeypatch):
         llm.generate([[1, 2, 3]], engine.SamplingParams(temperature=0.0, max_tokens=2))
     with pytest.raises(engine.EngineDeadError):
         llm.engine.step()
+
+
+def test_packing_with_empty_requests_and_repeated_wanted_rows(folders):
+    """Shapes fixed in advance: requests without tokens after the real ones, wanted rows
+    filled up with row 0; nothing about the real requests changes."""
+    runner = engine.ModelRunner.from_folder(folders["A"], "float32", 16, 8, 4, device="cpu")
+    for rid, n in (("a", 5), ("b", 1)):
+        runner.manager.admit(rid)
+        assert runner.manager.allocate(rid, 20 + n)
+    entries = [engine.StepEntry("a", [1, 2, 3, 4, 5], 20, [4]), engine.StepEntry("b", [9], 20, [])]
+    step = runner.step_function
+    plain, plain_meta = step.pack_host(entries, table_width=4)
+    host, meta = step.pack_host(entries, pad_requests=4, table_width=4, pad_tokens=0, pad_wanted=4)
+    assert meta["num_tokens"] == plain_meta["num_tokens"] == 6 and meta["num_requests"] == 4
+    assert meta["query_start"] == [0, 5, 6, 6, 6] and meta["seq_lens"] == [25, 21, 0, 0]
+    assert meta["num_wanted"] == 4 and meta["max_query_len"] == 5
+    ctx, ids, want = step.context_from(host, meta)
+    plain_ctx, plain_ids, plain_want = step.context_from(plain, plain_meta)
+    assert ids.tolist() == plain_ids.tolist() == [1, 2, 3, 4, 5, 9]
+    assert want.tolist() == [4, 0, 0, 0] and plain_want.tolist() == [4]
+    assert ctx.groups[0].block_table[:2].tolist() == plain_ctx.groups[0].block_table.tolist()
+    assert ctx.groups[0].block_table[2:].eq(-1).all()
+    assert ctx.groups[0].slot_mapping.tolist() == plain_ctx.groups[0].slot_mapping.tolist()
+    # the old form: padding requests of one token each
+    host, meta = step.pack_host([entries[1]], pad_requests=2, table_width=4)
+    assert meta["num_tokens"] == 2 and meta["query_start"] == [0, 1, 2] and meta["seq_lens"] == [21, 0]
