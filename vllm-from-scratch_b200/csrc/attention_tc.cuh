@@ -81,6 +81,27 @@ __device__ __forceinline__ float exp2_approx(float x) {
     return y;
 }
 
+// Two float32 operations in one instruction (the packed forms of this architecture).
+__device__ __forceinline__ float2 fma_pair(float2 a, float2 b, float2 c) {
+    unsigned long long ra, rb, rc, rd;
+    asm("mov.b64 %0, {%1, %2};" : "=l"(ra) : "f"(a.x), "f"(a.y));
+    asm("mov.b64 %0, {%1, %2};" : "=l"(rb) : "f"(b.x), "f"(b.y));
+    asm("mov.b64 %0, {%1, %2};" : "=l"(rc) : "f"(c.x), "f"(c.y));
+    asm("fma.rn.f32x2 %0, %1, %2, %3;" : "=l"(rd) : "l"(ra), "l"(rb), "l"(rc));
+    float2 d;
+    asm("mov.b64 {%0, %1}, %2;" : "=f"(d.x), "=f"(d.y) : "l"(rd));
+    return d;
+}
+__device__ __forceinline__ float2 add_pair(float2 a, float2 b) {
+    unsigned long long ra, rb, rd;
+    asm("mov.b64 %0, {%1, %2};" : "=l"(ra) : "f"(a.x), "f"(a.y));
+    asm("mov.b64 %0, {%1, %2};" : "=l"(rb) : "f"(b.x), "f"(b.y));
+    asm("add.rn.f32x2 %0, %1, %2;" : "=l"(rd) : "l"(ra), "l"(rb));
+    float2 d;
+    asm("mov.b64 {%0, %1}, %2;" : "=f"(d.x), "=f"(d.y) : "l"(rd));
+    return d;
+}
+
 // Issue the read of 32 columns into v[0..31]; the values are valid after tmem_ld_wait().
 __device__ __forceinline__ void tmem_ld32_issue(unsigned taddr, float* v) {
     asm volatile(
@@ -372,30 +393,39 @@ __global__ void __launch_bounds__(kAtThreads, 1) prefill_attention_tc_kernel(
                     if (!visible) sv[e] = -INFINITY;
                 }
             }
-            // (four chains each for the maximum and the sum: a thread has little else to overlap)
+            // The exponentials are taken against the reference the row already has, which does
+            // not wait for this tile's maximum; the maximum is found beside them (four chains),
+            // and only a row whose maximum has outgrown the reference by more than 2^8, which
+            // is rare after the first tiles, takes them again against the new one.
+            // 64 keys become 32 columns of bfloat16 pairs (even key in the low half), written over S.
+            unsigned packed[32];
+            auto exponentials = [&](float ref) {
+                const float2 scale2 = make_float2(scale_log2, scale_log2), shift2 = make_float2(-ref, -ref);
+                float2 sum_a = make_float2(0.0f, 0.0f), sum_b = make_float2(0.0f, 0.0f);
+#pragma unroll
+                for (int e = 0; e < 32; ++e) {
+                    const float2 x = fma_pair(make_float2(sv[2 * e], sv[2 * e + 1]), scale2, shift2);
+                    const float2 pr = make_float2(exp2_approx(x.x), exp2_approx(x.y));      // exp2(-inf) = 0
+                    if (e & 1) sum_b = add_pair(sum_b, pr); else sum_a = add_pair(sum_a, pr);
+                    const __nv_bfloat162 pair = __floats2bfloat162_rn(pr.x, pr.y);
+                    packed[e] = *reinterpret_cast<const unsigned*>(&pair);
+                }
+                return (sum_a.x + sum_a.y) + (sum_b.x + sum_b.y);
+            };
+            float tile_sum = exponentials(row_ref == -INFINITY ? 0.0f : row_ref);
             float max4[4] = {sv[0], sv[1], sv[2], sv[3]};
 #pragma unroll
             for (int e = 4; e < kAtKeys; ++e) max4[e & 3] = fmaxf(max4[e & 3], sv[e]);
-            float tile_max = fmaxf(fmaxf(max4[0], max4[1]), fmaxf(max4[2], max4[3]));
-            tile_max *= scale_log2;                                           // scale_log2 > 0
-            const bool moved = tile_max > row_ref + kAtRescaleStep;           // also the first finite maximum
-            const float new_ref = moved ? tile_max : row_ref;
-            const float ref = new_ref == -INFINITY ? 0.0f : new_ref;
-            const float alpha = moved ? exp2_approx(row_ref - ref) : 1.0f;    // exp2(-inf) = 0
-            row_ref = new_ref;
-            float sum4[4] = {0.0f, 0.0f, 0.0f, 0.0f};
-            // 64 keys as 32 columns of bfloat16 pairs (even key in the low half), written over S
-            unsigned packed[32];
-#pragma unroll
-            for (int e = 0; e < 32; ++e) {
-                const float p0 = exp2_approx(fmaf(sv[2 * e], scale_log2, -ref));
-                const float p1 = exp2_approx(fmaf(sv[2 * e + 1], scale_log2, -ref));
-                sum4[e & 3] += p0 + p1;
-                const __nv_bfloat162 pair = __floats2bfloat162_rn(p0, p1);
-                packed[e] = *reinterpret_cast<const unsigned*>(&pair);
+            const float tile_max = fmaxf(fmaxf(max4[0], max4[1]), fmaxf(max4[2], max4[3])) * scale_log2;   // scale_log2 > 0
+            const bool moved = tile_max > row_ref + kAtRescaleStep;          // also the first finite maximum
+            float alpha = 1.0f;
+            if (moved) {
+                alpha = exp2_approx(row_ref - tile_max);                     // exp2(-inf) = 0
+                row_ref = tile_max;
+                tile_sum = exponentials(tile_max);
             }
             tmem_st32_bits(tmem_s, packed);
-            row_sum = row_sum * alpha + ((sum4[0] + sum4[1]) + (sum4[2] + sum4[3]));
+            row_sum = row_sum * alpha + tile_sum;
             // Rescale O where the reference moved (a whole warp at a time: the accesses are
             // collective), after the P V before this tile has finished.  That P V has its
             // barrier to itself until this thread's arrival below lets the next one be issued,
