@@ -56,6 +56,10 @@ template <> __device__ __forceinline__ void store_pair<float>(float* p, float a,
 }
 template <typename T> __device__ __forceinline__ void store_one(T* p, float a) { *p = from_float<T>(a); }
 
+}  // namespace b200
+#include "slab_gemm.cuh"
+namespace b200 {
+
 constexpr int kSkinnyMaxWarps = 16;
 
 // TILES: weight-row blocks of 8 per CTA.  GATED: TILES must be 2; block 0 = gate rows, block 1 = up rows.
@@ -200,6 +204,29 @@ int launch_skinny(const bf16* x, const bf16* w, OutT* y, int M, int N, int K, in
 // Set by a kernel whose bounded wait ran out (0 = never).  Read and cleared by
 // b200_stream_gemm_error().
 __device__ int g_stream_error;
+
+// 1 = launched, 0 = not a shape for the kernel with resident weight rows, < 0 = error.
+template <typename OutT>
+int launch_slab(const bf16* x, const bf16* w, OutT* y, int M, int N, int K, cudaStream_t stream) {
+    const bool disabled = getenv("B200_NO_SLAB_GEMM") != nullptr;
+    if (disabled || M > 8 || K % 128 != 0 || slab_smem_bytes(K) > 200 * 1024) return 0;
+    static int* error_flag = nullptr;
+    if (error_flag == nullptr) {
+        void* found = nullptr;
+        if (cudaGetSymbolAddress(&found, g_stream_error) != cudaSuccess) return fail("slab_gemm", "no error flag");
+        error_flag = static_cast<int*>(found);
+    }
+    auto kernel = slab_gemm_kernel<OutT>;
+    static size_t configured = 0;
+    const size_t smem = slab_smem_bytes(K);
+    if (smem > configured) {
+        cudaError_t status = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024);
+        if (status != cudaSuccess) return fail("slab_gemm", cudaGetErrorString(status));
+        configured = 200 * 1024;
+    }
+    launch_overlapped(kernel, (N + kSlabRows - 1) / kSlabRows, kSlabWarps * 32, smem, stream, x, w, y, M, N, K, error_flag);
+    return check_launch("slab_gemm") == 0 ? 1 : -1;
+}
 
 // Returns 1 when the shape was launched, 0 when its token rows do not fit in shared
 // memory beside at least three weight stages (the caller then uses the other kernel).
@@ -373,6 +400,11 @@ B200_EXPORT int b200_skinny_gemm_bf16(const void* x, const void* w, void* y, int
             ? launch_stream<bf16>((const bf16*)x, (const bf16*)w, (bf16*)y, M, N, K, gated_inter, stream)
             : launch_stream<float>((const bf16*)x, (const bf16*)w, (float*)y, M, N, K, gated_inter, stream);
         if (rc != 0) return rc < 0 ? rc : 0;       // launched (1) or failed (< 0); 0 = shape too large for it
+    }
+    if (gated_inter == 0 && (out_dtype == 0 || out_dtype == 1) && ((uintptr_t)y & (out_dtype == 1 ? 3 : 7)) == 0) {
+        const int rc = out_dtype == 1 ? launch_slab<bf16>((const bf16*)x, (const bf16*)w, (bf16*)y, M, N, K, stream)
+                                      : launch_slab<float>((const bf16*)x, (const bf16*)w, (float*)y, M, N, K, stream);
+        if (rc != 0) return rc < 0 ? rc : 0;
     }
     if (out_dtype == 1) {
         if ((uintptr_t)y & 3) return fail("skinny_gemm", "output must be 4-byte aligned");

@@ -1,0 +1,129 @@
+// y[M, N] = x[M, K] w[N, K]^T for up to 8 token rows, with a block's whole share of the
+// weight matrix resident in shared memory.
+//
+// A decode step multiplies a handful of token rows by matrices of 8 to 50 MB, one after
+// the other, and each such product is short: most of its time is the wait for the first
+// bytes.  Weights are written by no kernel, so a block of this kernel asks for all of its
+// eight weight rows (K up to 12288: at most 192 KB) with bulk asynchronous copies before
+// it waits for the kernel ahead of it on the stream (overlapped launch, common.cuh): the
+// matrix is on its way while the short kernel that produces the token rows still runs,
+// and everything a block will ever read is in flight at once, with no ring to refill.
+// Copies are one per weight row and quarter of K, each quarter with its own mbarrier, so
+// the products start when the first quarter has landed.  Rows have a pitch of K * 2 + 16
+// bytes, which spreads the warps' 16-byte reads over all banks.
+// The arithmetic is that of skinny_gemm_kernel (gemm_bf16.cu): m16n8k16 products with the
+// token rows as the 16-row operand, the warps splitting K, their sums added in a fixed
+// order.  Waits are bounded; a block that gives up sets `error_flag` and stores nothing.
+#pragma once
+
+#include "stream_gemm.cuh"
+
+namespace b200 {
+
+constexpr int kSlabWarps = 8;
+constexpr int kSlabQuarters = 4;
+constexpr int kSlabRows = 8;                        // weight rows per block
+
+inline size_t slab_smem_bytes(int K) {
+    return (size_t)kSlabRows * ((size_t)K * 2 + 16) + 64 + 128;
+}
+
+template <typename OutT>
+__global__ void __launch_bounds__(kSlabWarps * 32, 2) slab_gemm_kernel(
+    const __nv_bfloat16* __restrict__ x, const __nv_bfloat16* __restrict__ w, OutT* __restrict__ y, int M, int N,
+    int K, int* __restrict__ error_flag) {
+    extern __shared__ __align__(128) unsigned char slab_smem[];
+    __shared__ float partial[kSlabWarps][32][4];
+    overlap_trigger();
+    const int pitch = K * 2 + 16;
+    unsigned char* rows = slab_smem;
+    unsigned long long* bars = reinterpret_cast<unsigned long long*>(slab_smem + (((size_t)kSlabRows * pitch + 63) & ~(size_t)63));
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    const int g = lane >> 2, t = lane & 3;
+    const int n0 = blockIdx.x * kSlabRows;
+    const int rows_here = min(kSlabRows, N - n0);
+    const int quarter_bytes = K / 2;                // K * 2 bytes / 4; K is a multiple of 32
+
+    if (threadIdx.x == 0) {
+        for (int q = 0; q < kSlabQuarters; ++q) mbar_init(bars + q, 1);
+        asm volatile("fence.mbarrier_init.release.cluster;\n" ::: "memory");
+    }
+    // weight rows past the end of the matrix read as zeros
+    for (int i = threadIdx.x; i < (kSlabRows - rows_here) * (pitch / 16); i += blockDim.x)
+        reinterpret_cast<uint4*>(rows + (size_t)rows_here * pitch)[i] = make_uint4(0, 0, 0, 0);
+    __syncthreads();
+    if (warp == 0) {
+        if (lane == 0)
+            for (int q = 0; q < kSlabQuarters; ++q) mbar_expect_tx(bars + q, (unsigned)(rows_here * quarter_bytes));
+        __syncwarp();
+        if (lane < rows_here) {
+            const unsigned char* src = reinterpret_cast<const unsigned char*>(w + (size_t)(n0 + lane) * K);
+            for (int q = 0; q < kSlabQuarters; ++q)
+                bulk_copy_g2s(rows + (size_t)lane * pitch + q * quarter_bytes, src + q * quarter_bytes,
+                              (unsigned)quarter_bytes, bars + q);
+        }
+    }
+    overlap_wait();                                 // the token rows come from the kernel before this one
+
+    const bool x_ok = g < M;
+    const __nv_bfloat16* x_row = x + (size_t)(x_ok ? g : 0) * K + 8 * t;
+    const unsigned char* w_row = rows + (size_t)g * pitch + 16 * t;
+    float acc[4] = {0.0f, 0.0f, 0.0f, 0.0f};
+    const int blocks = K >> 5;                      // blocks of 32 elements of K
+    const int blocks_per_quarter = blocks / kSlabQuarters;        // K a multiple of 128 (checked by the caller)
+    const uint4 zero = make_uint4(0, 0, 0, 0);
+    bool ok = true;
+    constexpr int kUnroll = 4;
+    for (int q = 0; q < kSlabQuarters; ++q) {
+        const int first = q * blocks_per_quarter, last = first + blocks_per_quarter;
+        bool waited = false;
+        for (int j = first + warp; j < last; j += kUnroll * kSlabWarps) {
+            uint4 xv[kUnroll];
+#pragma unroll
+            for (int u = 0; u < kUnroll; ++u) {
+                const int block = j + u * kSlabWarps;
+                xv[u] = (block < last && x_ok) ? *reinterpret_cast<const uint4*>(x_row + (block << 5)) : zero;
+            }
+            if (!waited) {
+                if (ok && !mbar_wait(bars + q, 0)) { atomicExch(error_flag, 41); ok = false; }
+                ok = __all_sync(0xffffffffu, ok);
+                waited = true;
+            }
+#pragma unroll
+            for (int u = 0; u < kUnroll; ++u) {
+                const int block = j + u * kSlabWarps;
+                if (block >= last) break;
+                const uint4 wv = *reinterpret_cast<const uint4*>(w_row + (size_t)block * 64);
+                mma_bf16_16816(acc, xv[u].x, 0u, xv[u].y, 0u, wv.x, wv.y);
+                mma_bf16_16816(acc, xv[u].z, 0u, xv[u].w, 0u, wv.z, wv.w);
+            }
+        }
+    }
+    // Every copy must have landed before the block may leave (its shared memory is theirs).
+    for (int q = 0; q < kSlabQuarters; ++q)
+        if (ok && !mbar_wait(bars + q, 0)) { atomicExch(error_flag, 42); ok = false; }
+    ok = __all_sync(0xffffffffu, ok);
+
+#pragma unroll
+    for (int e = 0; e < 4; ++e) partial[warp][lane][e] = acc[e];
+    __syncthreads();
+    if (warp != 0 || !ok) return;
+    float total[2];
+#pragma unroll
+    for (int e = 0; e < 2; ++e) {                   // c0, c1 = (token g, weight rows 2t, 2t + 1)
+        float sum = partial[0][lane][e];
+#pragma unroll
+        for (int wi = 1; wi < kSlabWarps; ++wi) sum += partial[wi][lane][e];
+        total[e] = sum;
+    }
+    if (g >= M) return;
+    const int n = n0 + 2 * t;
+    OutT* dst = y + (size_t)g * N + n;
+    if (n + 1 < N && (N & 1) == 0) store_pair<OutT>(dst, total[0], total[1]);
+    else {
+        if (n < N) store_one<OutT>(dst, total[0]);
+        if (n + 1 < N) store_one<OutT>(dst + 1, total[1]);
+    }
+}
+
+}  // namespace b200
