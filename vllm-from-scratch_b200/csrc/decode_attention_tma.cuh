@@ -79,7 +79,8 @@ __global__ void __launch_bounds__(kDtThreads, D <= 128 ? 3 : 1) decode_attention
     }
     asm volatile("fence.proxy.async.shared::cta;\n" ::: "memory");
     __syncthreads();
-    overlap_wait();                 // the newest key and value come from the kernel before this one
+    // Only the newest key and value (and the queries) come from the kernel before this one:
+    // tiles that end before the newest position are requested before waiting for it.
     bool ok = true;
 
     float o[D / 8][4];
@@ -91,8 +92,13 @@ __global__ void __launch_bounds__(kDtThreads, D <= 128 ? 3 : 1) decode_attention
         const int copy_rows = min(page_size, kKeys);
         const int copies_per_tile = kKeys / copy_rows;
         const int table_len = (seq_len + page_size - 1) / page_size;
+        bool waited = false;
         for (int t = 0; t < tiles; ++t) {
             const int s = t % kDtStages;
+            if (!waited && (t >= kDtStages || my_begin + (t + 1) * kKeys >= seq_len)) {
+                overlap_wait();
+                waited = true;
+            }
             const int key = my_begin + t * kKeys + lane * copy_rows;
             const int index = key / page_size;
             int row = -1;
@@ -117,6 +123,7 @@ __global__ void __launch_bounds__(kDtThreads, D <= 128 ? 3 : 1) decode_attention
         }
     } else {
         // -------- four warps, 16 keys of every tile each --------
+        overlap_wait();
         const bf16* q_base = q + ((size_t)request * nq + (size_t)kv_head * group) * D;
         unsigned qa[D / 16][4];
         load_q_fragments<D>(qa, row_a < group ? q_base + (size_t)row_a * D : nullptr,
