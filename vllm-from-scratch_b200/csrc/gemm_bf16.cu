@@ -206,25 +206,35 @@ int launch_skinny(const bf16* x, const bf16* w, OutT* y, int M, int N, int K, in
 __device__ int g_stream_error;
 
 // 1 = launched, 0 = not a shape for the kernel with resident weight rows, < 0 = error.
+// gated_inter > 0: w is [2 * gated_inter, K], the result [M, gated_inter].
 template <typename OutT>
-int launch_slab(const bf16* x, const bf16* w, OutT* y, int M, int N, int K, cudaStream_t stream) {
+int launch_slab(const bf16* x, const bf16* w, OutT* y, int M, int N, int K, int gated_inter, cudaStream_t stream) {
     const bool disabled = getenv("B200_NO_SLAB_GEMM") != nullptr;
-    if (disabled || M > 8 || K % 128 != 0 || slab_smem_bytes(K) > 200 * 1024) return 0;
+    const bool gated = gated_inter > 0;
+    if (gated && getenv("B200_NO_SLAB_GATED") != nullptr) return 0;
+    if (disabled || M > 8 || K % 128 != 0 || slab_smem_bytes(K, gated) > 200 * 1024) return 0;
     static int* error_flag = nullptr;
     if (error_flag == nullptr) {
         void* found = nullptr;
         if (cudaGetSymbolAddress(&found, g_stream_error) != cudaSuccess) return fail("slab_gemm", "no error flag");
         error_flag = static_cast<int*>(found);
     }
-    auto kernel = slab_gemm_kernel<OutT>;
-    static size_t configured = 0;
-    const size_t smem = slab_smem_bytes(K);
-    if (smem > configured) {
-        cudaError_t status = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024);
+    static bool configured = false;
+    if (!configured) {
+        cudaError_t status = cudaFuncSetAttribute(slab_gemm_kernel<OutT, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024);
+        if (status == cudaSuccess)
+            status = cudaFuncSetAttribute(slab_gemm_kernel<OutT, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024);
         if (status != cudaSuccess) return fail("slab_gemm", cudaGetErrorString(status));
-        configured = 200 * 1024;
+        configured = true;
     }
-    launch_overlapped(kernel, (N + kSlabRows - 1) / kSlabRows, kSlabWarps * 32, smem, stream, x, w, y, M, N, K, error_flag);
+    const size_t smem = slab_smem_bytes(K, gated);
+    const int rows = gated ? gated_inter : N;
+    if (gated)
+        launch_overlapped(slab_gemm_kernel<OutT, true>, (rows + kSlabRows - 1) / kSlabRows, kSlabWarps * 32, smem, stream,
+                          x, w, y, M, rows, K, error_flag);
+    else
+        launch_overlapped(slab_gemm_kernel<OutT, false>, (rows + kSlabRows - 1) / kSlabRows, kSlabWarps * 32, smem, stream,
+                          x, w, y, M, rows, K, error_flag);
     return check_launch("slab_gemm") == 0 ? 1 : -1;
 }
 
@@ -401,9 +411,10 @@ B200_EXPORT int b200_skinny_gemm_bf16(const void* x, const void* w, void* y, int
             : launch_stream<float>((const bf16*)x, (const bf16*)w, (float*)y, M, N, K, gated_inter, stream);
         if (rc != 0) return rc < 0 ? rc : 0;       // launched (1) or failed (< 0); 0 = shape too large for it
     }
-    if (gated_inter == 0 && (out_dtype == 0 || out_dtype == 1) && ((uintptr_t)y & (out_dtype == 1 ? 3 : 7)) == 0) {
-        const int rc = out_dtype == 1 ? launch_slab<bf16>((const bf16*)x, (const bf16*)w, (bf16*)y, M, N, K, stream)
-                                      : launch_slab<float>((const bf16*)x, (const bf16*)w, (float*)y, M, N, K, stream);
+    if ((out_dtype == 0 || out_dtype == 1) && ((uintptr_t)y & (out_dtype == 1 ? 3 : 7)) == 0) {
+        const int rc = out_dtype == 1
+            ? launch_slab<bf16>((const bf16*)x, (const bf16*)w, (bf16*)y, M, N, K, gated_inter, stream)
+            : launch_slab<float>((const bf16*)x, (const bf16*)w, (float*)y, M, N, K, gated_inter, stream);
         if (rc != 0) return rc < 0 ? rc : 0;
     }
     if (out_dtype == 1) {

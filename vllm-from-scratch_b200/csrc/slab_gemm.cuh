@@ -13,7 +13,9 @@
 // bytes, which spreads the warps' 16-byte reads over all banks.
 // The arithmetic is that of skinny_gemm_kernel (gemm_bf16.cu): m16n8k16 products with the
 // token rows as the 16-row operand, the warps splitting K, their sums added in a fixed
-// order.  Waits are bounded; a block that gives up sets `error_flag` and stores nothing.
+// order.  GATED: w is [2 N, K] with N gate rows followed by N up rows; a block holds eight
+// of each and stores silu(gate) * up, the feed-forward's first product and activation in one.
+// Waits are bounded; a block that gives up sets `error_flag` and stores nothing.
 #pragma once
 
 #include "stream_gemm.cuh"
@@ -24,20 +26,21 @@ constexpr int kSlabWarps = 8;
 constexpr int kSlabQuarters = 4;
 constexpr int kSlabRows = 8;                        // weight rows per block
 
-inline size_t slab_smem_bytes(int K) {
-    return (size_t)kSlabRows * ((size_t)K * 2 + 16) + 64 + 128;
+inline size_t slab_smem_bytes(int K, bool gated) {
+    return (size_t)(gated ? 2 : 1) * kSlabRows * ((size_t)K * 2 + 16) + 64 + 128;
 }
 
-template <typename OutT>
+template <typename OutT, bool GATED>
 __global__ void __launch_bounds__(kSlabWarps * 32, 2) slab_gemm_kernel(
     const __nv_bfloat16* __restrict__ x, const __nv_bfloat16* __restrict__ w, OutT* __restrict__ y, int M, int N,
     int K, int* __restrict__ error_flag) {
     extern __shared__ __align__(128) unsigned char slab_smem[];
-    __shared__ float partial[kSlabWarps][32][4];
+    constexpr int kSets = GATED ? 2 : 1;            // sets of eight rows: gate and up, or one
+    __shared__ float partial[kSlabWarps][kSets][32][4];
     overlap_trigger();
     const int pitch = K * 2 + 16;
     unsigned char* rows = slab_smem;
-    unsigned long long* bars = reinterpret_cast<unsigned long long*>(slab_smem + (((size_t)kSlabRows * pitch + 63) & ~(size_t)63));
+    unsigned long long* bars = reinterpret_cast<unsigned long long*>(slab_smem + (((size_t)kSets * kSlabRows * pitch + 63) & ~(size_t)63));
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
     const int g = lane >> 2, t = lane & 3;
     const int n0 = blockIdx.x * kSlabRows;
@@ -49,15 +52,17 @@ __global__ void __launch_bounds__(kSlabWarps * 32, 2) slab_gemm_kernel(
         asm volatile("fence.mbarrier_init.release.cluster;\n" ::: "memory");
     }
     // weight rows past the end of the matrix read as zeros
-    for (int i = threadIdx.x; i < (kSlabRows - rows_here) * (pitch / 16); i += blockDim.x)
-        reinterpret_cast<uint4*>(rows + (size_t)rows_here * pitch)[i] = make_uint4(0, 0, 0, 0);
+    for (int set = 0; set < kSets; ++set)
+        for (int i = threadIdx.x; i < (kSlabRows - rows_here) * (pitch / 16); i += blockDim.x)
+            reinterpret_cast<uint4*>(rows + (size_t)(set * kSlabRows + rows_here) * pitch)[i] = make_uint4(0, 0, 0, 0);
     __syncthreads();
     if (warp == 0) {
         if (lane == 0)
-            for (int q = 0; q < kSlabQuarters; ++q) mbar_expect_tx(bars + q, (unsigned)(rows_here * quarter_bytes));
+            for (int q = 0; q < kSlabQuarters; ++q) mbar_expect_tx(bars + q, (unsigned)(kSets * rows_here * quarter_bytes));
         __syncwarp();
-        if (lane < rows_here) {
-            const unsigned char* src = reinterpret_cast<const unsigned char*>(w + (size_t)(n0 + lane) * K);
+        const int set = lane / kSlabRows, r = lane % kSlabRows;       // lanes 8..15: the up rows, N rows further on
+        if (set < kSets && r < rows_here) {
+            const unsigned char* src = reinterpret_cast<const unsigned char*>(w + ((size_t)set * N + n0 + r) * K);
             for (int q = 0; q < kSlabQuarters; ++q)
                 bulk_copy_g2s(rows + (size_t)lane * pitch + q * quarter_bytes, src + q * quarter_bytes,
                               (unsigned)quarter_bytes, bars + q);
@@ -68,7 +73,9 @@ __global__ void __launch_bounds__(kSlabWarps * 32, 2) slab_gemm_kernel(
     const bool x_ok = g < M;
     const __nv_bfloat16* x_row = x + (size_t)(x_ok ? g : 0) * K + 8 * t;
     const unsigned char* w_row = rows + (size_t)g * pitch + 16 * t;
-    float acc[4] = {0.0f, 0.0f, 0.0f, 0.0f};
+    float acc[kSets][4];
+#pragma unroll
+    for (int set = 0; set < kSets; ++set) acc[set][0] = acc[set][1] = acc[set][2] = acc[set][3] = 0.0f;
     const int blocks = K >> 5;                      // blocks of 32 elements of K
     const int blocks_per_quarter = blocks / kSlabQuarters;        // K a multiple of 128 (checked by the caller)
     const uint4 zero = make_uint4(0, 0, 0, 0);
@@ -93,9 +100,12 @@ __global__ void __launch_bounds__(kSlabWarps * 32, 2) slab_gemm_kernel(
             for (int u = 0; u < kUnroll; ++u) {
                 const int block = j + u * kSlabWarps;
                 if (block >= last) break;
-                const uint4 wv = *reinterpret_cast<const uint4*>(w_row + (size_t)block * 64);
-                mma_bf16_16816(acc, xv[u].x, 0u, xv[u].y, 0u, wv.x, wv.y);
-                mma_bf16_16816(acc, xv[u].z, 0u, xv[u].w, 0u, wv.z, wv.w);
+#pragma unroll
+                for (int set = 0; set < kSets; ++set) {
+                    const uint4 wv = *reinterpret_cast<const uint4*>(w_row + (size_t)set * kSlabRows * pitch + (size_t)block * 64);
+                    mma_bf16_16816(acc[set], xv[u].x, 0u, xv[u].y, 0u, wv.x, wv.y);
+                    mma_bf16_16816(acc[set], xv[u].z, 0u, xv[u].w, 0u, wv.z, wv.w);
+                }
             }
         }
     }
@@ -105,16 +115,30 @@ __global__ void __launch_bounds__(kSlabWarps * 32, 2) slab_gemm_kernel(
     ok = __all_sync(0xffffffffu, ok);
 
 #pragma unroll
-    for (int e = 0; e < 4; ++e) partial[warp][lane][e] = acc[e];
+    for (int set = 0; set < kSets; ++set)
+#pragma unroll
+        for (int e = 0; e < 4; ++e) partial[warp][set][lane][e] = acc[set][e];
     __syncthreads();
     if (warp != 0 || !ok) return;
+    float sums[kSets][2];
+#pragma unroll
+    for (int set = 0; set < kSets; ++set)
+#pragma unroll
+        for (int e = 0; e < 2; ++e) {               // c0, c1 = (token g, weight rows 2t, 2t + 1)
+            float sum = partial[0][set][lane][e];
+#pragma unroll
+            for (int wi = 1; wi < kSlabWarps; ++wi) sum += partial[wi][set][lane][e];
+            sums[set][e] = sum;
+        }
     float total[2];
 #pragma unroll
-    for (int e = 0; e < 2; ++e) {                   // c0, c1 = (token g, weight rows 2t, 2t + 1)
-        float sum = partial[0][lane][e];
-#pragma unroll
-        for (int wi = 1; wi < kSlabWarps; ++wi) sum += partial[wi][lane][e];
-        total[e] = sum;
+    for (int e = 0; e < 2; ++e) {
+        if (GATED) {
+            const float gate = sums[0][e], up = sums[kSets - 1][e];
+            total[e] = gate / (1.0f + expf(-gate)) * up;
+        } else {
+            total[e] = sums[0][e];
+        }
     }
     if (g >= M) return;
     const int n = n0 + 2 * t;

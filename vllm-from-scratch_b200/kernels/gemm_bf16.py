@@ -11,6 +11,7 @@ by default: its 128-row tiles leave too few blocks for matrices of this size.
 from __future__ import annotations
 
 import ctypes
+import os
 
 import torch
 
@@ -32,6 +33,17 @@ _P, _I = ctypes.c_void_p, ctypes.c_int
 
 def _skinny_ok(m: int, n: int, k: int, *tensors: torch.Tensor) -> bool:
     return (1 <= m <= SKINNY_MAX_ROWS and n <= SKINNY_MAX_WEIGHT_ROWS and k >= 32 and k % 32 == 0
+            and all(t.data_ptr() % 16 == 0 for t in tensors))
+
+
+def _resident_ok(m: int, k: int, gated: bool, *tensors: torch.Tensor) -> bool:
+    """Whether the kernel that keeps a block's weight rows in shared memory takes the
+    shape (any number of weight rows): at most 8 tokens, K a multiple of 128, and 8 (gated:
+    16) rows of K within 200 KB."""
+    if os.environ.get("B200_NO_SLAB_GEMM") is not None or (gated and os.environ.get("B200_NO_SLAB_GATED") is not None):
+        return False
+    rows = 16 if gated else 8
+    return (1 <= m <= 8 and k % 128 == 0 and rows * (2 * k + 16) + 192 <= 200 * 1024
             and all(t.data_ptr() % 16 == 0 for t in tensors))
 
 
@@ -59,7 +71,8 @@ def gemm_bf16(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor) -> None:
 def gated_silu_gemm_bf16(x: torch.Tensor, w_gate_up: torch.Tensor, out: torch.Tensor) -> bool:
     """``out = silu(x w[:I]^T) * (x w[I:]^T)`` in one kernel; False if the shape is
     not one the fused kernel takes (the caller then does it in two steps)."""
-    if not _skinny_ok(x.shape[0], w_gate_up.shape[0], x.shape[1], x, w_gate_up, out):
+    if not (_skinny_ok(x.shape[0], w_gate_up.shape[0], x.shape[1], x, w_gate_up, out)
+            or _resident_ok(x.shape[0], x.shape[1], True, x, w_gate_up, out)):
         return False
     _skinny(x, w_gate_up, out, out.shape[1])
     return True
