@@ -24,6 +24,7 @@ namespace b200 {
 
 constexpr int kSlabWarps = 8;
 constexpr int kSlabQuarters = 4;
+static_assert(kSlabQuarters == 4, "the caller's check K % 128 == 0 makes a quarter of a row a multiple of 64 bytes");
 constexpr int kSlabRows = 8;                        // weight rows per block
 
 inline size_t slab_smem_bytes(int K, bool gated) {
@@ -45,7 +46,7 @@ __global__ void __launch_bounds__(kSlabWarps * 32, 2) slab_gemm_kernel(
     const int g = lane >> 2, t = lane & 3;
     const int n0 = blockIdx.x * kSlabRows;
     const int rows_here = min(kSlabRows, N - n0);
-    const int quarter_bytes = K / 2;                // K * 2 bytes / 4; K is a multiple of 32
+    const int quarter_bytes = K * 2 / kSlabQuarters;        // K is a multiple of 128: a multiple of 16 bytes
 
     if (threadIdx.x == 0) {
         for (int q = 0; q < kSlabQuarters; ++q) mbar_init(bars + q, 1);
