@@ -8,9 +8,9 @@
 // it waits for the kernel ahead of it on the stream (overlapped launch, common.cuh): the
 // matrix is on its way while the short kernel that produces the token rows still runs,
 // and everything a block will ever read is in flight at once, with no ring to refill.
-// Copies are one per weight row and quarter of K, each quarter with its own mbarrier, so
-// the products start when the first quarter has landed.  Rows have a pitch of K * 2 + 16
-// bytes, which spreads the warps' 16-byte reads over all banks.
+// Copies are one per weight row (kSlabQuarters parts of a row, each part with its own
+// mbarrier; one part measured best).  Rows have a pitch of K * 2 + 16 bytes, which spreads
+// the warps' 16-byte reads over all banks.
 // The arithmetic is that of skinny_gemm_kernel (gemm_bf16.cu): m16n8k16 products with the
 // token rows as the 16-row operand, the warps splitting K, their sums added in a fixed
 // order.  GATED: w is [2 N, K] with N gate rows followed by N up rows; a block holds eight
@@ -23,8 +23,11 @@
 namespace b200 {
 
 constexpr int kSlabWarps = 8;
-constexpr int kSlabQuarters = 4;
-static_assert(kSlabQuarters == 4, "the caller's check K % 128 == 0 makes a quarter of a row a multiple of 64 bytes");
+// Copies per weight row.  One is best: measured 4.9 / 4.0 / 7.7 us for the 4096 x 2048, 2048 x 2048 and
+// 2048 x 6144 products against 5.7 / 4.7 / 8.3 us with four and 11.9 / 9.1 / 12.7 us with sixteen: few
+// large copies load faster than many small ones, and that outweighs starting on a first part early.
+constexpr int kSlabQuarters = 1;
+static_assert(128 % (32 * kSlabQuarters) == 0, "the caller checks K % 128 == 0: every part must be whole blocks of 32");
 constexpr int kSlabRows = 8;                        // weight rows per block
 
 inline size_t slab_smem_bytes(int K, bool gated) {
