@@ -273,3 +273,94 @@ def test_toy_mixer_with_state_registers_builds_and_steps():
             assert float((results[rid] - expected[rid]).abs().max()) < 5e-5, rid
     finally:
         MIXERS.unregister("toy_running_sum")
+
+
+# ------------------------------------- a toy feed-forward with routing, a toy position encoding
+def test_toy_routed_feed_forward_and_toy_frequencies_register_build_and_step():
+    """Two more parts defined here and registered from the test: a feed-forward that sends
+    each token to one of three small experts (router logits and the choice in float32), and
+    a position encoding of the rotary family with frequencies of its own over half of the
+    head.  Layer 0 keeps the model's parts, layer 1 takes both toys; the model is stepped
+    whole, in portions and mixed with another request."""
+    from vllm_from_scratch_b200 import ModelRunner, PartSpec
+    from vllm_from_scratch_b200.parts import (FEED_FORWARDS, POSITION_ENCODINGS, DecoderModel, FeedForward,
+                                              PositionEncoding, WeightInfo)
+    import dataclasses
+
+    class TopOneExperts(FeedForward):
+        def __init__(self, params, env):
+            super().__init__(params, env)
+            self.experts = int(params["experts"])
+            self.router = self.w = None
+
+        def expected_weights(self):
+            h = self.env.hidden_size
+            return {"router.weight": WeightInfo((self.experts, h)), "experts.weight": WeightInfo((self.experts * h, h))}
+
+        def load_weights(self, tensors):
+            self.router, self.w = tensors["router.weight"], tensors["experts.weight"]
+
+        def forward(self, x, ctx):
+            h = self.env.hidden_size
+            logits = x.float() @ self.router.float().T                  # float32 router
+            choice = logits.argmax(dim=-1)
+            gate = torch.softmax(logits, dim=-1).gather(1, choice[:, None])
+            w = self.w.float().view(self.experts, h, h)[choice]         # [T, h, h]
+            return (gate * torch.einsum("tk,tnk->tn", x.float(), w)).to(x.dtype)
+
+    class BandFrequencies(PositionEncoding):
+        def __init__(self, params, env):
+            super().__init__(params, env)
+            self.rotary_dim = int(params["rotary_dim"])
+            self._inv = torch.tensor(params["inverse_frequencies"], dtype=torch.float32, device=env.device)
+            assert self._inv.numel() == self.rotary_dim // 2
+
+        def inverse_frequencies(self):
+            return self._inv
+
+    band = [1.0, 0.5, 0.03, 0.002]                                      # 8 of the 16 channels of a head rotate
+    FEED_FORWARDS.register("toy_top_one_experts")(TopOneExperts)
+    POSITION_ENCODINGS.register("toy_band_frequencies")(BandFrequencies)
+    try:
+        base = small_spec([(0, None), (1, None)])
+        toy = dataclasses.replace(
+            base.layers[1], feed_forward=PartSpec("toy_top_one_experts", {"experts": 3}, name="moe"),
+            position=PartSpec("toy_band_frequencies", {"rotary_dim": 8, "inverse_frequencies": band}))
+        spec = dataclasses.replace(base, layers=(base.layers[0], toy))
+        weights = random_weights_for(DecoderModel(spec, torch.float32, "cpu"), seed=8)
+        assert "model.layers.1.moe.router.weight" in weights and "model.layers.1.mlp.down_proj.weight" not in weights
+        runner = ModelRunner(spec, weights, "float32", 8, 32, 2, device="cuda")
+
+        def plain(tokens):
+            cfg = {"heads": 4, "kv_heads": 2, "head_dim": 16, "eps": 1e-6, "theta": 1e4}
+            h = weights["model.embed_tokens.weight"][torch.tensor(tokens)]
+            p = "model.layers.0."
+            w = {"a." + k[len(p + "self_attn."):]: v for k, v in weights.items() if k.startswith(p + "self_attn.")}
+            h = h + plain_attention(plain_qwen3.rms_norm(h, weights[p + "input_layernorm.weight"], 1e-6), w, cfg, None)
+            h = h + plain_qwen3.feed_forward(plain_qwen3.rms_norm(h, weights[p + "post_attention_layernorm.weight"], 1e-6), weights, p + "mlp.")
+            p = "model.layers.1."
+            x = plain_qwen3.rms_norm(h, weights[p + "input_layernorm.weight"], 1e-6)
+            seq = len(tokens)
+            q = plain_qwen3.rms_norm((x @ weights[p + "self_attn.q_proj.weight"].T).view(seq, 4, 16), weights[p + "self_attn.q_norm.weight"], 1e-6)
+            k = plain_qwen3.rms_norm((x @ weights[p + "self_attn.k_proj.weight"].T).view(seq, 2, 16), weights[p + "self_attn.k_norm.weight"], 1e-6)
+            v = (x @ weights[p + "self_attn.v_proj.weight"].T).view(seq, 2, 16)
+            angles = torch.arange(seq, dtype=torch.float32)[:, None] * torch.tensor(band)[None, :]
+            q, k = plain_qwen3.apply_rope(q, angles.cos(), angles.sin()), plain_qwen3.apply_rope(k, angles.cos(), angles.sin())
+            h = h + plain_qwen3.causal_attention(q, k, v, 0.25, None) @ weights[p + "self_attn.o_proj.weight"].T
+            x = plain_qwen3.rms_norm(h, weights[p + "post_attention_layernorm.weight"], 1e-6)
+            logits = x @ weights[p + "moe.router.weight"].T
+            choice = logits.argmax(dim=-1)
+            gate = torch.softmax(logits, dim=-1).gather(1, choice[:, None])
+            experts = weights[p + "moe.experts.weight"].view(3, 64, 64)[choice]
+            h = h + gate * torch.einsum("tk,tnk->tn", x, experts)
+            return plain_qwen3.rms_norm(h, weights["model.norm.weight"], 1e-6) @ weights["model.embed_tokens.weight"].T
+
+        sequences = {rid: helpers.random_tokens(97, n, seed=3 * n) for rid, n in {"a": 45, "b": 19}.items()}
+        expected = {rid: plain(toks) for rid, toks in sequences.items()}
+        for steps in ([[("a", 45), ("b", 19)]], [[("a", 7)], [("a", 2), ("b", 11)], [("b", 8), ("a", 30)], [("a", 6)]]):
+            results = helpers.run_schedule(runner, sequences, steps)
+            for rid in sequences:
+                assert float((results[rid] - expected[rid]).abs().max()) < 5e-5, rid
+    finally:
+        FEED_FORWARDS.unregister("toy_top_one_experts")
+        POSITION_ENCODINGS.unregister("toy_band_frequencies")
