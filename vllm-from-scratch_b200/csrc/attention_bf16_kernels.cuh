@@ -279,13 +279,43 @@ __global__ void __launch_bounds__(kThreads) decode_attention_kernel(
     }
 }
 
-// One block per (token, query head): merge the splits' partial results.
+// One block per (token, query head): merge the splits' partial results.  Up to 16 splits
+// are fetched in one go (every load issued before any is used); more run through a loop.
 template <int D>
 __global__ void merge_splits_kernel(const float* __restrict__ partial_o, const float* __restrict__ partial_ml,
                                     bf16* __restrict__ out, int splits) {
     overlap_trigger();
     overlap_wait();
     const size_t head = blockIdx.x;
+    constexpr int kHeld = 16;
+    if (splits <= kHeld) {
+        for (int j = threadIdx.x; j < D; j += blockDim.x) {
+            float m[kHeld], l[kHeld], o[kHeld];
+#pragma unroll
+            for (int s = 0; s < kHeld; ++s) {
+                const bool in = s < splits;
+                m[s] = in ? partial_ml[(head * splits + s) * 2] : -INFINITY;
+                l[s] = in ? partial_ml[(head * splits + s) * 2 + 1] : 0.0f;
+                o[s] = in ? partial_o[(head * splits + s) * D + j] : 0.0f;
+            }
+            float m_star = -INFINITY;
+#pragma unroll
+            for (int s = 0; s < kHeld; ++s) m_star = fmaxf(m_star, m[s]);
+            float acc = 0.0f, l_sum = 0.0f;
+            if (m_star != -INFINITY) {
+#pragma unroll
+                for (int s = 0; s < kHeld; ++s) {
+                    if (s < splits) {
+                        const float weight = exp2f(m[s] - m_star);
+                        acc += weight * o[s];
+                        l_sum += weight * l[s];
+                    }
+                }
+            }
+            out[head * D + j] = __float2bfloat16_rn(l_sum > 0.0f ? acc / l_sum : 0.0f);
+        }
+        return;
+    }
     float m_star = -INFINITY;
     for (int s = 0; s < splits; ++s) m_star = fmaxf(m_star, partial_ml[(head * splits + s) * 2]);
     for (int j = threadIdx.x; j < D; j += blockDim.x) {

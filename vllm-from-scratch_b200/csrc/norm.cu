@@ -67,8 +67,16 @@ __global__ void add_rmsnorm_vec_kernel(const T* __restrict__ x, float* __restric
     __shared__ float scratch[33];
     constexpr int kSteps = 4;
     overlap_trigger();
-    overlap_wait();
     const int out_row = blockIdx.x;
+    // The norm's weights are written by no kernel: they are fetched before the wait for the
+    // kernel ahead, not after the reduction, where they would cost a round trip of their own.
+    float4 scale[kSteps];
+#pragma unroll
+    for (int step = 0; step < kSteps; ++step) {
+        const int i = (step * blockDim.x + threadIdx.x) * 4;
+        scale[step] = i < hidden ? *reinterpret_cast<const float4*>(weight + i) : make_float4(0.f, 0.f, 0.f, 0.f);
+    }
+    overlap_wait();
     const int row = rows ? rows[out_row] : out_row;
     const size_t base = (size_t)row * hidden;
     const bool store_sum = (rows == nullptr) && (x != nullptr);
@@ -95,7 +103,7 @@ __global__ void add_rmsnorm_vec_kernel(const T* __restrict__ x, float* __restric
     for (int step = 0; step < kSteps; ++step) {
         const int i = (step * blockDim.x + threadIdx.x) * 4;
         if (i < hidden) {
-            const float4 w = *reinterpret_cast<const float4*>(weight + i);
+            const float4 w = scale[step];
             const float4 v = kept[step];
             Vec4<T>::store(out + out_base + i, make_float4(v.x * inv * w.x, v.y * inv * w.y, v.z * inv * w.z, v.w * inv * w.w));
         }

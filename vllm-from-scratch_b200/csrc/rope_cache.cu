@@ -23,7 +23,6 @@ __global__ void head_norm_rope_cache_kernel(
     const float* __restrict__ inv_freq, T* __restrict__ q_out, T* __restrict__ k_pages,
     T* __restrict__ v_pages, int nq, int nkv, int d, int rotary_dim, int page_size, float eps) {
     overlap_trigger();
-    overlap_wait();
     const int token = blockIdx.x;
     const int warps = blockDim.x >> 5;
     const int head_slot = blockIdx.y * warps + (threadIdx.x >> 5);
@@ -35,23 +34,47 @@ __global__ void head_norm_rope_cache_kernel(
     const bool is_v = !is_q && !is_k;
     if (!is_q && k_pages == nullptr) return;  // this execution owns no cache: keys/values unused
 
+    // Everything that does not come from the kernel before this one is fetched and worked out
+    // before waiting for it: position and slot (inputs of the step), the angles' sines and
+    // cosines, the norm weights.  After the wait only the head itself is read.
+    constexpr int kMaxPairs = 8;                    // pairs of channels per lane held in registers
+    const int half = rotary_dim >> 1;
+    const bool held = half <= 32 * kMaxPairs;
+    const float* weight = is_q ? q_weight : k_weight;
+    const float pos = (float)positions[token];
+    int slot = 0;
+    if (!is_q) {
+        slot = slots[token];
+        if (slot < 0) return;
+    }
+    float sin_r[kMaxPairs], cos_r[kMaxPairs], w1_r[kMaxPairs], w2_r[kMaxPairs];
+    if (!is_v && held) {
+#pragma unroll
+        for (int i = 0; i < kMaxPairs; ++i) {
+            const int j = lane + 32 * i;
+            sin_r[i] = 0.0f; cos_r[i] = 1.0f; w1_r[i] = w2_r[i] = 1.0f;
+            if (j < half) {
+                sincosf(pos * inv_freq[j], &sin_r[i], &cos_r[i]);
+                if (weight) { w1_r[i] = weight[j]; w2_r[i] = weight[j + half]; }
+            }
+        }
+    }
     const T* src = qkv + (size_t)token * total_heads * d + (size_t)head_slot * d;
     T* dst;
     if (is_q) {
         dst = q_out + (size_t)token * nq * d + (size_t)head_slot * d;
     } else {
-        const int slot = slots[token];
-        if (slot < 0) return;
         const int page = slot / page_size, offset = slot - page * page_size;
         const int kv_head = is_k ? head_slot - nq : head_slot - nq - nkv;
         T* pages = is_k ? k_pages : v_pages;
         dst = pages + (((size_t)page * nkv + kv_head) * page_size + offset) * d;
     }
+    overlap_wait();
+
     if (is_v) {
         for (int j = lane; j < d; j += 32) dst[j] = src[j];
         return;
     }
-    const float* weight = is_q ? q_weight : k_weight;
     float inv = 1.0f;
     if (weight) {
         float sum_sq = 0.0f;
@@ -62,15 +85,25 @@ __global__ void head_norm_rope_cache_kernel(
         sum_sq = warp_sum(sum_sq);
         inv = rsqrtf(sum_sq / (float)d + eps);
     }
-    const int half = rotary_dim >> 1;
-    const float pos = (float)positions[token];
-    for (int j = lane; j < half; j += 32) {
-        float x1 = to_float(src[j]) * inv, x2 = to_float(src[j + half]) * inv;
-        if (weight) { x1 *= weight[j]; x2 *= weight[j + half]; }
-        float s, c;
-        sincosf(pos * inv_freq[j], &s, &c);
-        dst[j] = from_float<T>(x1 * c - x2 * s);
-        dst[j + half] = from_float<T>(x2 * c + x1 * s);
+    if (held) {
+#pragma unroll
+        for (int i = 0; i < kMaxPairs; ++i) {
+            const int j = lane + 32 * i;
+            if (j < half) {
+                const float x1 = to_float(src[j]) * inv * w1_r[i], x2 = to_float(src[j + half]) * inv * w2_r[i];
+                dst[j] = from_float<T>(x1 * cos_r[i] - x2 * sin_r[i]);
+                dst[j + half] = from_float<T>(x2 * cos_r[i] + x1 * sin_r[i]);
+            }
+        }
+    } else {
+        for (int j = lane; j < half; j += 32) {
+            float x1 = to_float(src[j]) * inv, x2 = to_float(src[j + half]) * inv;
+            if (weight) { x1 *= weight[j]; x2 *= weight[j + half]; }
+            float s, c;
+            sincosf(pos * inv_freq[j], &s, &c);
+            dst[j] = from_float<T>(x1 * c - x2 * s);
+            dst[j + half] = from_float<T>(x2 * c + x1 * s);
+        }
     }
     for (int j = rotary_dim + lane; j < d; j += 32) {
         float v = to_float(src[j]) * inv;
