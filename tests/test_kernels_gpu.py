@@ -280,7 +280,8 @@ def test_decode_attention_same_for_any_split():
 
 
 @pytest.mark.parametrize("m,n,k_", [(1, 512, 128), (8, 4096, 2048), (3, 2048, 6144), (16, 503, 96), (9, 264, 160),
-                                    (16, 12288, 2048), (5, 151936, 256), (3, 1003, 256), (7, 5, 12288), (8, 77, 384)])
+                                    (16, 12288, 2048), (5, 151936, 256), (3, 1003, 256), (7, 5, 12288), (8, 77, 384),
+                                    (12, 2048, 2048), (9, 1003, 6144)])
 @pytest.mark.parametrize("out_dtype", [torch.bfloat16, torch.float32])
 def test_few_rows_gemm(m, n, k_, out_dtype):
     """The weight-streaming kernel (M <= 16): exact float64 reference, and a token's
@@ -303,7 +304,7 @@ def test_few_rows_gemm(m, n, k_, out_dtype):
 
 
 @pytest.mark.parametrize("m,inter,k_", [(1, 160, 96), (8, 6144, 2048), (16, 1111, 64), (40, 256, 128), (5, 1003, 256),
-                                        (2, 8, 6144)])
+                                        (2, 8, 6144), (12, 1003, 256), (16, 6144, 2048)])
 @pytest.mark.parametrize("dtype", DTYPES)
 def test_gated_silu_gemm(m, inter, k_, dtype):
     k = kernels()

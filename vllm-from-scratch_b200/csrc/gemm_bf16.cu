@@ -212,7 +212,7 @@ int launch_slab(const bf16* x, const bf16* w, OutT* y, int M, int N, int K, int 
     const bool disabled = getenv("B200_NO_SLAB_GEMM") != nullptr;
     const bool gated = gated_inter > 0;
     if (gated && getenv("B200_NO_SLAB_GATED") != nullptr) return 0;
-    if (disabled || M > 8 || K % 128 != 0 || slab_smem_bytes(K, gated) > 200 * 1024) return 0;
+    if (disabled || M > 16 || K % 128 != 0 || slab_smem_bytes(K, gated) > 200 * 1024) return 0;
     static int* error_flag = nullptr;
     if (error_flag == nullptr) {
         void* found = nullptr;
@@ -221,20 +221,28 @@ int launch_slab(const bf16* x, const bf16* w, OutT* y, int M, int N, int K, int 
     }
     static bool configured = false;
     if (!configured) {
-        cudaError_t status = cudaFuncSetAttribute(slab_gemm_kernel<OutT, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024);
+        cudaError_t status = cudaFuncSetAttribute(slab_gemm_kernel<OutT, false, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024);
         if (status == cudaSuccess)
-            status = cudaFuncSetAttribute(slab_gemm_kernel<OutT, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024);
+            status = cudaFuncSetAttribute(slab_gemm_kernel<OutT, true, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024);
+        if (status == cudaSuccess)
+            status = cudaFuncSetAttribute(slab_gemm_kernel<OutT, false, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024);
+        if (status == cudaSuccess)
+            status = cudaFuncSetAttribute(slab_gemm_kernel<OutT, true, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024);
         if (status != cudaSuccess) return fail("slab_gemm", cudaGetErrorString(status));
         configured = true;
     }
     const size_t smem = slab_smem_bytes(K, gated);
     const int rows = gated ? gated_inter : N;
-    if (gated)
-        launch_overlapped(slab_gemm_kernel<OutT, true>, (rows + kSlabRows - 1) / kSlabRows, kSlabWarps * 32, smem, stream,
-                          x, w, y, M, rows, K, error_flag);
+    const int blocks = (rows + kSlabRows - 1) / kSlabRows, threads = kSlabWarps * 32;
+    const bool wide = M > 8;
+    if (gated && wide)
+        launch_overlapped(slab_gemm_kernel<OutT, true, true>, blocks, threads, smem, stream, x, w, y, M, rows, K, error_flag);
+    else if (gated)
+        launch_overlapped(slab_gemm_kernel<OutT, true, false>, blocks, threads, smem, stream, x, w, y, M, rows, K, error_flag);
+    else if (wide)
+        launch_overlapped(slab_gemm_kernel<OutT, false, true>, blocks, threads, smem, stream, x, w, y, M, rows, K, error_flag);
     else
-        launch_overlapped(slab_gemm_kernel<OutT, false>, (rows + kSlabRows - 1) / kSlabRows, kSlabWarps * 32, smem, stream,
-                          x, w, y, M, rows, K, error_flag);
+        launch_overlapped(slab_gemm_kernel<OutT, false, false>, blocks, threads, smem, stream, x, w, y, M, rows, K, error_flag);
     return check_launch("slab_gemm") == 0 ? 1 : -1;
 }
 

@@ -1,4 +1,4 @@
-// y[M, N] = x[M, K] w[N, K]^T for up to 8 token rows, with a block's whole share of the
+// y[M, N] = x[M, K] w[N, K]^T for up to 16 token rows, with a block's whole share of the
 // weight matrix resident in shared memory.
 //
 // A decode step multiplies a handful of token rows by matrices of 8 to 50 MB, one after
@@ -34,8 +34,9 @@ inline size_t slab_smem_bytes(int K, bool gated) {
     return (size_t)(gated ? 2 : 1) * kSlabRows * ((size_t)K * 2 + 16) + 64 + 128;
 }
 
-template <typename OutT, bool GATED>
-__global__ void __launch_bounds__(kSlabWarps * 32, 2) slab_gemm_kernel(
+// WIDE: 9 to 16 token rows (both halves of the 16-row operand are read).
+template <typename OutT, bool GATED, bool WIDE>
+__global__ void __launch_bounds__(kSlabWarps * 32, GATED ? 3 : 4) slab_gemm_kernel(
     const __nv_bfloat16* __restrict__ x, const __nv_bfloat16* __restrict__ w, OutT* __restrict__ y, int M, int N,
     int K, int* __restrict__ error_flag) {
     extern __shared__ __align__(128) unsigned char slab_smem[];
@@ -74,8 +75,9 @@ __global__ void __launch_bounds__(kSlabWarps * 32, 2) slab_gemm_kernel(
     }
     overlap_wait();                                 // the token rows come from the kernel before this one
 
-    const bool x_ok = g < M;
+    const bool x_ok = g < M, x_hi_ok = WIDE && g + 8 < M;   // rows g and g + 8 of the 16-row operand
     const __nv_bfloat16* x_row = x + (size_t)(x_ok ? g : 0) * K + 8 * t;
+    const __nv_bfloat16* x_row_hi = x + (size_t)(x_hi_ok ? g + 8 : 0) * K + 8 * t;
     const unsigned char* w_row = rows + (size_t)g * pitch + 16 * t;
     float acc[kSets][4];
 #pragma unroll
@@ -84,16 +86,17 @@ __global__ void __launch_bounds__(kSlabWarps * 32, 2) slab_gemm_kernel(
     const int blocks_per_quarter = blocks / kSlabQuarters;        // K a multiple of 128 (checked by the caller)
     const uint4 zero = make_uint4(0, 0, 0, 0);
     bool ok = true;
-    constexpr int kUnroll = 4;
+    constexpr int kUnroll = WIDE ? 2 : 4;
     for (int q = 0; q < kSlabQuarters; ++q) {
         const int first = q * blocks_per_quarter, last = first + blocks_per_quarter;
         bool waited = false;
         for (int j = first + warp; j < last; j += kUnroll * kSlabWarps) {
-            uint4 xv[kUnroll];
+            uint4 xv[kUnroll], xh[kUnroll];
 #pragma unroll
             for (int u = 0; u < kUnroll; ++u) {
                 const int block = j + u * kSlabWarps;
                 xv[u] = (block < last && x_ok) ? *reinterpret_cast<const uint4*>(x_row + (block << 5)) : zero;
+                xh[u] = (WIDE && block < last && x_hi_ok) ? *reinterpret_cast<const uint4*>(x_row_hi + (block << 5)) : zero;
             }
             if (!waited) {
                 if (ok && !mbar_wait(bars + q, 0)) { atomicExch(error_flag, 41); ok = false; }
@@ -107,8 +110,8 @@ __global__ void __launch_bounds__(kSlabWarps * 32, 2) slab_gemm_kernel(
 #pragma unroll
                 for (int set = 0; set < kSets; ++set) {
                     const uint4 wv = *reinterpret_cast<const uint4*>(w_row + (size_t)set * kSlabRows * pitch + (size_t)block * 64);
-                    mma_bf16_16816(acc[set], xv[u].x, 0u, xv[u].y, 0u, wv.x, wv.y);
-                    mma_bf16_16816(acc[set], xv[u].z, 0u, xv[u].w, 0u, wv.z, wv.w);
+                    mma_bf16_16816(acc[set], xv[u].x, xh[u].x, xv[u].y, xh[u].y, wv.x, wv.y);
+                    mma_bf16_16816(acc[set], xv[u].z, xh[u].z, xv[u].w, xh[u].w, wv.z, wv.w);
                 }
             }
         }
@@ -124,33 +127,32 @@ __global__ void __launch_bounds__(kSlabWarps * 32, 2) slab_gemm_kernel(
         for (int e = 0; e < 4; ++e) partial[warp][set][lane][e] = acc[set][e];
     __syncthreads();
     if (warp != 0 || !ok) return;
-    float sums[kSets][2];
-#pragma unroll
-    for (int set = 0; set < kSets; ++set)
-#pragma unroll
-        for (int e = 0; e < 2; ++e) {               // c0, c1 = (token g, weight rows 2t, 2t + 1)
-            float sum = partial[0][set][lane][e];
-#pragma unroll
-            for (int wi = 1; wi < kSlabWarps; ++wi) sum += partial[wi][set][lane][e];
-            sums[set][e] = sum;
-        }
-    float total[2];
-#pragma unroll
-    for (int e = 0; e < 2; ++e) {
-        if (GATED) {
-            const float gate = sums[0][e], up = sums[kSets - 1][e];
-            total[e] = gate / (1.0f + expf(-gate)) * up;
-        } else {
-            total[e] = sums[0][e];
-        }
-    }
-    if (g >= M) return;
+    // accumulator layout: c0, c1 = (token g, weight rows 2t, 2t + 1), c2, c3 = (token g + 8, same rows)
+    constexpr int kHalves = WIDE ? 2 : 1;
     const int n = n0 + 2 * t;
-    OutT* dst = y + (size_t)g * N + n;
-    if (n + 1 < N && (N & 1) == 0) store_pair<OutT>(dst, total[0], total[1]);
-    else {
-        if (n < N) store_one<OutT>(dst, total[0]);
-        if (n + 1 < N) store_one<OutT>(dst + 1, total[1]);
+#pragma unroll
+    for (int half = 0; half < kHalves; ++half) {
+        float total[2];
+#pragma unroll
+        for (int e = 0; e < 2; ++e) {
+            float sums[kSets];
+#pragma unroll
+            for (int set = 0; set < kSets; ++set) {
+                float sum = partial[0][set][lane][half * 2 + e];
+#pragma unroll
+                for (int wi = 1; wi < kSlabWarps; ++wi) sum += partial[wi][set][lane][half * 2 + e];
+                sums[set] = sum;
+            }
+            total[e] = GATED ? sums[0] / (1.0f + expf(-sums[0])) * sums[kSets - 1] : sums[0];
+        }
+        const int token = g + half * 8;
+        if (token >= M) continue;
+        OutT* dst = y + (size_t)token * N + n;
+        if (n + 1 < N && (N & 1) == 0) store_pair<OutT>(dst, total[0], total[1]);
+        else {
+            if (n < N) store_one<OutT>(dst, total[0]);
+            if (n + 1 < N) store_one<OutT>(dst + 1, total[1]);
+        }
     }
 }
 
