@@ -235,3 +235,53 @@ def test_repeated_mixed_steps_replay_graphs_with_the_same_tokens(folders, dtype)
             assert llm.engine.mixed_graphs.replays >= 8, "steps of a repeated shape must be replayed"
             assert llm.engine.decode_graphs.replays > 0
     assert results[False] == results[True]
+
+
+@pytest.mark.parametrize("name", ["A", "B", "C"])
+def test_every_engine_setting_gives_the_same_tokens(folders, name):
+    """Ten requests of mixed lengths (some sharing a prefix), greedy and seeded, joining at
+    random steps: without graphs, with graphs, with steps queued ahead, with prefix caching,
+    and with a pool so small that requests are preempted.  In float32 every setting must
+    give every request the very same tokens."""
+    import random
+    import vllm_from_scratch_b200 as engine
+    raw = getattr(tiny_configs, f"TINY_{name}")
+
+    def run(eager, ahead, prefix, blocks, seed):
+        rng = random.Random(seed)
+        shared = helpers.random_tokens(raw["vocab_size"], 40, seed=seed)
+        prompts = []
+        for i in range(10):
+            prompt = helpers.random_tokens(raw["vocab_size"], rng.choice([1, 3, 9, 17, 33, 50, 70]), seed=seed * 100 + i)
+            prompts.append(shared[:rng.choice([16, 24, 40])] + prompt if i % 3 == 0 else prompt)
+        params = [engine.SamplingParams(temperature=0.0 if i % 2 == 0 else 0.8, seed=i, top_k=0 if i % 4 else 20,
+                                        max_tokens=rng.choice([1, 5, 20, 40])) for i in range(10)]
+        arrivals = sorted(rng.randrange(0, 30) for _ in prompts)
+        llm = engine.LLM(folders[name], dtype="float32", max_model_len=160, block_size=8, max_num_seqs=4,
+                         max_num_batched_tokens=32, enforce_eager=eager, async_scheduling=ahead,
+                         enable_prefix_caching=prefix, num_gpu_blocks=blocks)
+        core, latest, step, added = llm.engine, {}, 0, 0
+        while added < len(prompts) or core.has_unfinished_requests():
+            while added < len(prompts) and arrivals[added] <= step:
+                core.add_request(f"r{added}", prompts[added], params[added])
+                added += 1
+            for output in core.step():
+                latest[output.request_id] = output
+            step += 1
+            assert step < 5000
+        core.runner.manager.check_invariants()
+        assert core.runner.manager.stats()["requests"] == 0
+        return [latest[f"r{i}"].token_ids for i in range(len(prompts))], core
+
+    for seed in (1, 2):
+        expected, _ = run(True, False, False, None, seed)
+        settings = [(False, False, False, None), (False, True, False, None), (False, True, False, 30)]
+        if name != "C":                                     # a windowed group has no prefix caching
+            settings += [(False, True, True, None), (True, False, True, None), (False, False, True, 30)]
+        for eager, ahead, prefix, blocks in settings:
+            got, core = run(eager, ahead, prefix, blocks, seed)
+            assert got == expected, (seed, eager, ahead, prefix, blocks)
+            if blocks is not None:
+                assert core.scheduler.num_preemptions > 0, "the small pool was meant to force preemption"
+            if ahead:
+                assert core.num_steps_ahead > 0
