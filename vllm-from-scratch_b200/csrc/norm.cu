@@ -60,7 +60,10 @@ template <> struct Vec4<__nv_bfloat16> {
     }
 };
 
-template <typename T>
+// EARLY (launches of a few rows, where the kernel is one round trip long): the norm's weights,
+// which no kernel writes, are fetched before the wait for the kernel ahead instead of after the
+// reduction.  Launches of many rows keep the registers for more blocks per SM.
+template <typename T, bool EARLY>
 __global__ void add_rmsnorm_vec_kernel(const T* __restrict__ x, float* __restrict__ residual,
                                        const float* __restrict__ weight, T* __restrict__ out,
                                        const int* __restrict__ rows, int hidden, float eps) {
@@ -68,13 +71,13 @@ __global__ void add_rmsnorm_vec_kernel(const T* __restrict__ x, float* __restric
     constexpr int kSteps = 4;
     overlap_trigger();
     const int out_row = blockIdx.x;
-    // The norm's weights are written by no kernel: they are fetched before the wait for the
-    // kernel ahead, not after the reduction, where they would cost a round trip of their own.
-    float4 scale[kSteps];
+    float4 scale[EARLY ? kSteps : 1];
+    if (EARLY) {
 #pragma unroll
-    for (int step = 0; step < kSteps; ++step) {
-        const int i = (step * blockDim.x + threadIdx.x) * 4;
-        scale[step] = i < hidden ? *reinterpret_cast<const float4*>(weight + i) : make_float4(0.f, 0.f, 0.f, 0.f);
+        for (int step = 0; step < kSteps; ++step) {
+            const int i = (step * blockDim.x + threadIdx.x) * 4;
+            scale[step] = i < hidden ? *reinterpret_cast<const float4*>(weight + i) : make_float4(0.f, 0.f, 0.f, 0.f);
+        }
     }
     overlap_wait();
     const int row = rows ? rows[out_row] : out_row;
@@ -103,7 +106,7 @@ __global__ void add_rmsnorm_vec_kernel(const T* __restrict__ x, float* __restric
     for (int step = 0; step < kSteps; ++step) {
         const int i = (step * blockDim.x + threadIdx.x) * 4;
         if (i < hidden) {
-            const float4 w = scale[step];
+            const float4 w = EARLY ? scale[EARLY ? step : 0] : *reinterpret_cast<const float4*>(weight + i);
             const float4 v = kept[step];
             Vec4<T>::store(out + out_base + i, make_float4(v.x * inv * w.x, v.y * inv * w.y, v.z * inv * w.z, v.w * inv * w.w));
         }
@@ -184,11 +187,18 @@ B200_EXPORT int b200_add_rmsnorm(const void* x, float* residual, const float* we
         int threads = 64;
         while (threads < 1024 && threads * 16 < hidden) threads *= 2;      // at most four steps a thread
         while (threads < 256 && threads * 4 < hidden) threads *= 2;        // short rows: one step a thread
-        if (dtype == 0)
-            launch_overlapped(add_rmsnorm_vec_kernel<float>, num_rows, threads, 0, stream,
+        const bool early = num_rows <= 64;
+        if (dtype == 0 && early)
+            launch_overlapped(add_rmsnorm_vec_kernel<float, true>, num_rows, threads, 0, stream,
                               (const float*)x, residual, weight, (float*)out, rows, hidden, eps);
+        else if (dtype == 0)
+            launch_overlapped(add_rmsnorm_vec_kernel<float, false>, num_rows, threads, 0, stream,
+                              (const float*)x, residual, weight, (float*)out, rows, hidden, eps);
+        else if (early)
+            launch_overlapped(add_rmsnorm_vec_kernel<__nv_bfloat16, true>, num_rows, threads, 0, stream,
+                              (const __nv_bfloat16*)x, residual, weight, (__nv_bfloat16*)out, rows, hidden, eps);
         else
-            launch_overlapped(add_rmsnorm_vec_kernel<__nv_bfloat16>, num_rows, threads, 0, stream,
+            launch_overlapped(add_rmsnorm_vec_kernel<__nv_bfloat16, false>, num_rows, threads, 0, stream,
                               (const __nv_bfloat16*)x, residual, weight, (__nv_bfloat16*)out, rows, hidden, eps);
         return check_launch("add_rmsnorm");
     }
