@@ -110,9 +110,13 @@ def random_prompt(vocab: int, length: int, seed: int) -> list[int]:
 
 def prefill_all(runner, ids: list[str], prompts: list[list[int]], chunk: int):
     """Every prompt into the cache, ``chunk`` tokens a step.  Returns the CUDA-event
-    time in ms of the last full-size step (a 2,048-token prefill when chunk = 2048)."""
+    time in ms of the last full-size step (a 2,048-token prefill when chunk = 2048).
+    Steps go the way the engine sends them: through the step function the first time a
+    shape is seen, as a graph replay of the same step from the second time on."""
     import torch
     from vllm_from_scratch_b200 import StepEntry
+    from vllm_from_scratch_b200.engine.decode_graph import MixedGraphs
+    steps = MixedGraphs(runner, max(len(p) for p in prompts))
     last_ms = None
     for request_id, prompt in zip(ids, prompts):
         runner.manager.admit(request_id)
@@ -123,7 +127,7 @@ def prefill_all(runner, ids: list[str], prompts: list[list[int]], chunk: int):
             begin, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
             torch.cuda.synchronize()
             begin.record()
-            runner.step([StepEntry(request_id, prompt[done:done + count], done, [count - 1])])
+            steps.run([StepEntry(request_id, prompt[done:done + count], done, [count - 1])])
             end.record()
             torch.cuda.synchronize()
             if count == chunk:
