@@ -24,11 +24,15 @@ def decode_splits(num_requests: int, num_kv_heads: int, max_seq_len: int) -> int
     """Over how many blocks the keys of one (request, key/value head) are split.
     Three blocks fit on an SM at a time; the split is chosen so that the blocks fill
     whole rounds of the GPU (a last round with few blocks would leave it idle), with
-    at least 512 keys per block at the planned length."""
+    at least 512 keys per block at the planned length (256 for one or two requests)."""
     pairs = max(1, num_requests * num_kv_heads)
     slots = 3 * NUM_SMS
     best, best_fill = 1, 0.0
-    for splits in range(1, max(1, min(16, max_seq_len // 512)) + 1):
+    # One or two requests cannot fill half of the GPU with 512 keys a block: they get 256
+    # (a step at batch 1 takes 1.21 against 1.29 ms, at batch 2 1.27 against 1.31; from batch 4
+    # on the finer split loses to its own merge and set-up).
+    min_keys = 256 if pairs * max(1, max_seq_len // 512) < slots // 2 else 512
+    for splits in range(1, max(1, min(16, max_seq_len // min_keys)) + 1):
         blocks = pairs * splits
         fill = blocks / (-(-blocks // slots) * slots) - 0.002 * splits     # a split more costs a little
         if fill > best_fill:
