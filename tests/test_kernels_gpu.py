@@ -326,7 +326,8 @@ def test_gated_silu_gemm(m, inter, k_, dtype):
 
 
 @pytest.mark.parametrize("m,n,k_", [(1, 256, 128), (8, 4096, 2048), (16, 2048, 6144), (17, 1000, 264), (64, 12288, 2048),
-                                    (100, 503, 96), (256, 384, 512), (5, 151936, 256)])
+                                    (100, 503, 96), (256, 384, 512), (5, 151936, 256), (24, 2048, 2048),
+                                    (128, 4096, 2048), (33, 2050, 6144)])
 @pytest.mark.parametrize("out_dtype", [torch.bfloat16, torch.float32])
 def test_tensor_memory_gemm(m, n, k_, out_dtype):
     """The tcgen05 / TMA kernel against a float64 product; no bounded wait may run out."""
@@ -335,7 +336,7 @@ def test_tensor_memory_gemm(m, n, k_, out_dtype):
     x = torch.randn(m, k_, device="cuda", generator=g).bfloat16()
     w = torch.randn(n, k_, device="cuda", generator=g).bfloat16()
     out = torch.full((m, n), 7.0, device="cuda", dtype=out_dtype)
-    for _ in range(2):                               # twice: the tile counters must reset themselves
+    for _ in range(2):                               # twice: nothing may be left over from a launch
         gemm_bf16.tc_gemm_bf16(x, w, out)
     assert gemm_bf16.device_error_code() == 0
     exact = x.double() @ w.double().T
@@ -344,7 +345,8 @@ def test_tensor_memory_gemm(m, n, k_, out_dtype):
     assert float((out.double() - exact).abs().max()) <= bound
 
 
-@pytest.mark.parametrize("m,inter,k_", [(1, 256, 128), (8, 6144, 2048), (33, 1000, 320), (64, 1536, 1024)])
+@pytest.mark.parametrize("m,inter,k_", [(1, 256, 128), (8, 6144, 2048), (33, 1000, 320), (64, 1536, 1024),
+                                        (64, 6144, 2048), (128, 3001, 512)])
 def test_tensor_memory_gated_gemm(m, inter, k_):
     from vllm_from_scratch_b200.kernels import gemm_bf16
     g = torch.Generator(device="cuda").manual_seed(m + inter)
@@ -357,6 +359,26 @@ def test_tensor_memory_gated_gemm(m, inter, k_):
     plain_ops.gated_silu_gemm(x, w, expected)
     bound = float(expected.float().abs().max()) * 2 ** -7
     assert float((out.float() - expected.float()).abs().max()) <= bound
+
+
+def test_tensor_memory_gemm_by_switch(monkeypatch):
+    """With B200_TC_GEMM_ROWS the engine's products of 17 rows and more go to the tcgen05 kernel."""
+    from vllm_from_scratch_b200.kernels import gemm_bf16
+    g = torch.Generator(device="cuda").manual_seed(5)
+    x = torch.randn(40, 512, device="cuda", generator=g).bfloat16()
+    w = (torch.randn(2 * 384, 512, device="cuda", generator=g) * 0.1).bfloat16()
+    plain, gated = torch.empty(40, 768, device="cuda", dtype=torch.bfloat16), torch.empty(40, 384, device="cuda", dtype=torch.bfloat16)
+    expected_plain, expected_gated = torch.empty_like(plain), torch.empty_like(gated)
+    plain_ops.gemm(x, w, expected_plain)
+    plain_ops.gated_silu_gemm(x, w, expected_gated)
+    monkeypatch.setenv("B200_TC_GEMM_ROWS", "128")
+    before = k.launch_count
+    k.gemm(x, w, plain)
+    k.gated_silu_gemm(x, w, gated)
+    assert k.launch_count == before + 2              # one kernel each: no separate activation
+    assert gemm_bf16.device_error_code() == 0
+    for got, want in ((plain, expected_plain), (gated, expected_gated)):
+        assert float((got.float() - want.float()).abs().max()) <= float(want.float().abs().max()) * 2 ** -7
 
 
 TENSOR_MEMORY_ATTENTION_SHAPES = [

@@ -32,7 +32,7 @@
 // Masking and arguments are those of attention_generic.cu.  Waits are bounded.
 #pragma once
 
-#include "tc_gemm.cuh"
+#include "tcgen05.cuh"
 
 namespace b200 {
 

@@ -19,7 +19,7 @@
 #pragma once
 
 #include "attention_bf16_kernels.cuh"
-#include "tc_gemm.cuh"
+#include "tcgen05.cuh"
 
 namespace b200 {
 

@@ -18,7 +18,6 @@
 
 #include "common.cuh"
 #include "stream_gemm.cuh"
-#include "tc_gemm.cuh"
 #include "tensor_map.cuh"
 
 #include <map>
@@ -58,6 +57,7 @@ template <typename T> __device__ __forceinline__ void store_one(T* p, float a) {
 
 }  // namespace b200
 #include "slab_gemm.cuh"
+#include "tc_gemm.cuh"
 namespace b200 {
 
 constexpr int kSkinnyMaxWarps = 16;
@@ -315,63 +315,101 @@ struct TcPlan {
     int ntok, stages, splits, steps_per_split, row_tiles, smem;
 };
 
+inline int env_int(const char* name, int fallback) {
+    const char* text = getenv(name);
+    return text != nullptr ? atoi(text) : fallback;
+}
+
 inline TcPlan tc_plan(int M, int N, int K, bool gated) {
     TcPlan plan;
     plan.ntok = ((M + 15) / 16) * 16;
-    const int stage = kTcATile + plan.ntok * kTcK * 2;
-    plan.stages = 8;
-    while (plan.stages > 2 && TcLayout(plan.stages, plan.ntok).total(gated) > 112 * 1024) --plan.stages;
-    plan.smem = TcLayout(plan.stages, plan.ntok).total(gated);
     const int rows_per_tile = gated ? 64 : kTcRows;
     plan.row_tiles = (N + rows_per_tile - 1) / rows_per_tile;
     const int total_steps = (K + kTcK - 1) / kTcK;
-    // Enough blocks for two per SM; the split depends on the matrix only, never on the
-    // number of tokens, so a token's sums are formed the same way in every batch.
-    int splits = (2 * 148 + plan.row_tiles - 1) / plan.row_tiles;
-    if (splits > 16) splits = 16;
-    if (const char* forced = getenv("B200_TC_SPLITS")) splits = atoi(forced);
+    // Matrices with few rows are split along K, over a cluster: as many splits as still leave
+    // every block one of the two places of an SM (so that all of them stream at once, and the
+    // kernel after this one finds room to start its own copies), the steps divided evenly if
+    // that is possible.  The split depends on the matrix only, never on the number of tokens,
+    // so a token's sums are formed in the same order in every batch.
+    const int places = env_int("B200_TC_BLOCKS", 2 * 148);
+    int splits = 1;
+    for (int s = kTcMaxSplits; s > 1; --s)
+        if (plan.row_tiles * s <= places && s * 2 <= total_steps && total_steps % s == 0) {
+            splits = s;
+            break;
+        }
+    if (splits == 1)
+        for (int s = kTcMaxSplits; s > 1; --s)
+            if (plan.row_tiles * s <= places && s * 2 <= total_steps) {
+                splits = s;
+                break;
+            }
+    splits = env_int("B200_TC_SPLITS", splits);
+    if (splits > kTcMaxSplits) splits = kTcMaxSplits;
     if (splits > total_steps / 2) splits = total_steps / 2;
     if (splits < 1) splits = 1;
     plan.steps_per_split = (total_steps + splits - 1) / splits;
     plan.splits = (total_steps + plan.steps_per_split - 1) / plan.steps_per_split;
-    (void)stage;
+    // As many stages as a split has steps (its whole share of the matrix is then requested at
+    // once, before the kernel ahead has ended), within half of an SM's shared memory.
+    const int budget = env_int("B200_TC_SMEM_KB", 100) * 1024;
+    plan.stages = plan.steps_per_split < 12 ? plan.steps_per_split : 12;
+    while (plan.stages > 2 && TcLayout(plan.stages, plan.ntok).total() > budget) --plan.stages;
+    plan.smem = TcLayout(plan.stages, plan.ntok).total();
+    // A block's share of an SM's shared memory is never below its share of the SM's 512 columns of
+    // tensor memory, so the blocks that fit on an SM never ask for more columns than it has: a
+    // block that spun in tcgen05.alloc while the holders of the columns waited for it (at the
+    // cluster barrier, or for its whole kernel to end) would be a deadlock.
+    int columns = 32;
+    while (columns < plan.ntok) columns *= 2;
+    const int least = (228 * 1024 / 512) * columns;
+    if (plan.smem < least) plan.smem = least;
     return plan;
 }
 
 template <bool GATED, typename OutT>
-int launch_tc(const bf16* x, const bf16* w, OutT* y, float* scratch, int* counters, int M, int N, int K,
-              int w_rows, int* error_flag, cudaStream_t stream) {
+int launch_tc(const bf16* x, const bf16* w, OutT* y, int M, int N, int K, int w_rows, int* error_flag,
+              cudaStream_t stream) {
     const TcPlan plan = tc_plan(M, N, K, GATED);
+    if (plan.smem > 227 * 1024) return fail("tc_gemm", "the tiles of this shape do not fit in shared memory");
     const CUtensorMap* map_w = tensor_map_for(w, w_rows, K, GATED ? 64 : kTcRows);
     const CUtensorMap* map_x = tensor_map_for(x, M, K, plan.ntok);
     if (map_w == nullptr || map_x == nullptr) return fail("tc_gemm", "could not encode a tensor map");
     auto kernel = tc_gemm_kernel<GATED, OutT>;
     cudaError_t status = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, plan.smem);
     if (status != cudaSuccess) return fail("tc_gemm", cudaGetErrorString(status));
-    dim3 grid(plan.row_tiles, plan.splits);
-    kernel<<<grid, 128, plan.smem, stream>>>(*map_w, *map_x, scratch, counters, y, M, N, K, plan.ntok, plan.stages,
-                                             plan.steps_per_split, GATED ? N : 0, error_flag);
+    cudaLaunchConfig_t config = {};
+    config.gridDim = dim3(plan.row_tiles, plan.splits);
+    config.blockDim = dim3(128);
+    config.dynamicSmemBytes = plan.smem;
+    config.stream = stream;
+    cudaLaunchAttribute attributes[2];
+    attributes[0].id = cudaLaunchAttributeClusterDimension;
+    attributes[0].val.clusterDim.x = 1;
+    attributes[0].val.clusterDim.y = plan.splits;
+    attributes[0].val.clusterDim.z = 1;
+    attributes[1].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attributes[1].val.programmaticStreamSerializationAllowed = overlap_enabled() ? 1 : 0;
+    config.attrs = attributes;
+    config.numAttrs = 2;
+    status = cudaLaunchKernelEx(&config, kernel, *map_w, *map_x, y, M, N, K, plan.ntok, plan.stages,
+                                plan.steps_per_split, GATED ? N : 0, error_flag);
+    if (status != cudaSuccess) return fail("tc_gemm", cudaGetErrorString(status));
     return check_launch("tc_gemm");
 }
 
 }  // namespace b200
 
-// What the tcgen05 product needs of its caller for a shape: number of K splits (scratch
-// must hold splits * M * width floats when splits > 1, width = N, or 2 N for the gated
-// product) and of row tiles (one zeroed int counter each).  Returns 0 if the shape is not
-// one this kernel takes.
-B200_EXPORT int b200_tc_gemm_plan(int M, int N, int K, int gated, int* splits, int* row_tiles) {
+// Whether the tcgen05 product takes a shape (token rows M, weight rows N, width K).
+B200_EXPORT int b200_tc_gemm_supports(int M, int N, int K) {
     if (M < 1 || M > 256 || K < 64 || K % 8 != 0 || N < 1) return 0;
-    const b200::TcPlan plan = b200::tc_plan(M, N, K, gated != 0);
-    *splits = plan.splits;
-    *row_tiles = plan.row_tiles;
-    return 1;
+    return b200::tc_plan(M, N, K, false).smem <= 227 * 1024 ? 1 : 0;
 }
 
 // y[M, N] = x[M, K] . w[N, K]^T (gated_inter = 0), or y[M, I] = silu(x w[:I]^T) * (x w[I:]^T)
 // with w of 2 I rows (gated_inter = I, N = 2 I).  out_dtype: 0 float32, 1 bfloat16.
-B200_EXPORT int b200_tc_gemm_bf16(const void* x, const void* w, void* y, float* scratch, int* counters, int M,
-                                  int N, int K, int gated_inter, int out_dtype, cudaStream_t stream) {
+B200_EXPORT int b200_tc_gemm_bf16(const void* x, const void* w, void* y, int M, int N, int K, int gated_inter,
+                                  int out_dtype, cudaStream_t stream) {
     using namespace b200;
     if (M == 0 || N == 0) return 0;
     if (M < 1 || M > 256 || K < 64 || K % 8 != 0) return fail("tc_gemm", "needs 1 <= M <= 256 and K >= 64, a multiple of 8");
@@ -390,12 +428,11 @@ B200_EXPORT int b200_tc_gemm_bf16(const void* x, const void* w, void* y, float* 
     const bf16* wb = (const bf16*)w;
     if (gated_inter > 0) {
         if (out_dtype == 1)
-            return launch_tc<true, bf16>(xb, wb, (bf16*)y, scratch, counters, M, gated_inter, K, N, error_flag[device], stream);
-        return launch_tc<true, float>(xb, wb, (float*)y, scratch, counters, M, gated_inter, K, N, error_flag[device], stream);
+            return launch_tc<true, bf16>(xb, wb, (bf16*)y, M, gated_inter, K, N, error_flag[device], stream);
+        return launch_tc<true, float>(xb, wb, (float*)y, M, gated_inter, K, N, error_flag[device], stream);
     }
-    if (out_dtype == 1)
-        return launch_tc<false, bf16>(xb, wb, (bf16*)y, scratch, counters, M, N, K, N, error_flag[device], stream);
-    return launch_tc<false, float>(xb, wb, (float*)y, scratch, counters, M, N, K, N, error_flag[device], stream);
+    if (out_dtype == 1) return launch_tc<false, bf16>(xb, wb, (bf16*)y, M, N, K, N, error_flag[device], stream);
+    return launch_tc<false, float>(xb, wb, (float*)y, M, N, K, N, error_flag[device], stream);
 }
 
 // Largest M and the divisibility of K the few-rows kernel takes.
