@@ -364,6 +364,7 @@ def test_tensor_memory_gated_gemm(m, inter, k_):
 def test_tensor_memory_gemm_by_switch(monkeypatch):
     """With B200_TC_GEMM_ROWS the engine's products of 17 rows and more go to the tcgen05 kernel."""
     from vllm_from_scratch_b200.kernels import gemm_bf16
+    k = kernels()
     g = torch.Generator(device="cuda").manual_seed(5)
     x = torch.randn(40, 512, device="cuda", generator=g).bfloat16()
     w = (torch.randn(2 * 384, 512, device="cuda", generator=g) * 0.1).bfloat16()
