@@ -390,6 +390,8 @@ TENSOR_MEMORY_ATTENTION_SHAPES = [
     (8, 2, 128, 32, [130, 70], [130, 1000], None),
     (6, 3, 128, 8, [333], [1500], 256),
     (4, 4, 128, 128, [257, 64], [257, 640], None),
+    (2, 2, 128, 16, [1, 2, 63, 65, 129], [1, 2, 63, 65, 129], None),
+    (2, 1, 128, 16, [384, 100], [2500, 1100], 700),
 ]
 
 

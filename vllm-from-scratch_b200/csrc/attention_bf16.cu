@@ -137,7 +137,9 @@ B200_EXPORT int b200_prefill_attention_tc_bf16(
         return fail("prefill_attention_tc", "could not encode a tensor map");
     cudaError_t status = cudaFuncSetAttribute(prefill_attention_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kAtSmem);
     if (status != cudaSuccess) return fail("prefill_attention_tc", cudaGetErrorString(status));
-    dim3 grid(num_tokens / kAtBlockRows + num_requests, nq);
+    const int blocks = num_tokens / kAtBlockRows + num_requests;
+    if (blocks > 65535) return fail("prefill_attention_tc", "too many tokens for one launch");
+    dim3 grid(nq, blocks);
     prefill_attention_tc_kernel<<<grid, kAtThreads, kAtSmem, stream>>>(
         *map_q, *map_k, *map_v, (__nv_bfloat16*)out, query_start, seq_lens, block_table, num_requests, max_pages,
         nq, nkv, page_size, scale * kLog2e, window, error_flag);

@@ -188,8 +188,10 @@ __global__ void __launch_bounds__(kAtThreads, 1) prefill_attention_tc_kernel(
     unsigned long long* o_bar = p_bar + 2 * kAtGroups;      // [group][tile & 1] P V of the tile has been added to O
     unsigned* tmem_slot = reinterpret_cast<unsigned*>(o_bar + 2 * kAtGroups);
 
-    // Which request and which 256-row tile of it (heaviest tiles first).
-    const int block = gridDim.x - 1 - blockIdx.x;
+    // Which request and which 256-row tile of it.  grid (query heads, tiles): blocks start in the
+    // order of their index, x first, so the heaviest tiles of all heads start first, and the
+    // heads that share keys and values run side by side.
+    const int block = gridDim.y - 1 - blockIdx.y;
     int lo = 0, hi = num_requests - 1;
     while (lo < hi) {
         const int mid = (lo + hi + 1) >> 1;
@@ -203,7 +205,7 @@ __global__ void __launch_bounds__(kAtThreads, 1) prefill_attention_tc_kernel(
     const int rows_here = min(kAtBlockRows, q_len - tile_first);
     const int seq_len = seq_lens[request];
     const int past = seq_len - q_len;
-    const int head = blockIdx.y;
+    const int head = blockIdx.x;
     const int kv_head = head / (nq / nkv);
     const int* table = block_table + (size_t)request * max_pages;
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;

@@ -82,6 +82,9 @@ def main(argv=None) -> int:
     parser.add_argument("--warmup", type=int, default=3)
     parser.add_argument("--iters", type=int, default=10)
     parser.add_argument("--keep-l2", action="store_true")
+    parser.add_argument("--repeat", type=int, default=1,
+                        help="attention: launches per timed graph replay (the time printed is per launch); "
+                             "short kernels need several, CUDA events resolve no better than some microseconds")
     parser.add_argument("--gated", action="store_true", help="gemm: fused silu(gate) * up, N = 2 * inter")
     parser.add_argument("--kernel", default="default", choices=("default", "tc", "library"),
                         help="gemm: the engine's choice, the tcgen05 kernel, or the vendor library")
@@ -99,9 +102,13 @@ def main(argv=None) -> int:
         q, kp, vp, start, seq, table = _paged_case(batch, q_len, context, nq, nkv, d, args.page, dtype)
         out = torch.empty_like(q)
         planned = args.planned_context or context
-        fn = lambda: kernels.paged_attention(q, kp, vp, out, start, seq, table, nq, nkv, d, args.page,
-                                             d ** -0.5, None, q_len, planned)
-        ms = _time(fn, args.warmup, args.iters, not args.keep_l2)
+        one = lambda: kernels.paged_attention(q, kp, vp, out, start, seq, table, nq, nkv, d, args.page,
+                                              d ** -0.5, None, q_len, planned)
+
+        def fn():
+            for _ in range(args.repeat):
+                one()
+        ms = _time(fn, args.warmup, args.iters, not args.keep_l2) / args.repeat
         record.update(batch=batch, context=context, heads=nq, kv_heads=nkv, head_dim=d, page=args.page)
         if decode:
             moved = batch * context * nkv * d * 2 * size
