@@ -17,7 +17,8 @@ def folders(tmp_path_factory):
     base = tmp_path_factory.mktemp("engine_models")
     return {"A": helpers.make_model_folder(base, tiny_configs.TINY_A, seed=11),
             "B": helpers.make_model_folder(base, tiny_configs.TINY_B, seed=12),
-            "C": helpers.make_model_folder(base, tiny_configs.TINY_C, seed=13)}
+            "C": helpers.make_model_folder(base, tiny_configs.TINY_C, seed=13),
+            "E": helpers.make_model_folder(base, tiny_configs.TINY_E, seed=15)}
 
 
 def plain_greedy(folder, prompt, new_tokens):
@@ -285,3 +286,33 @@ def test_every_engine_setting_gives_the_same_tokens(folders, name):
                 assert core.scheduler.num_preemptions > 0, "the small pool was meant to force preemption"
             if ahead:
                 assert core.num_steps_ahead > 0
+
+
+@pytest.mark.parametrize("eager", [True, False])
+def test_decode_attention_in_one_kernel_gives_the_same_tokens(folders, eager, monkeypatch):
+    """bfloat16, head size 128, one layer with a window: decode steps whose attention kernel also
+    normalises and rotates the heads and stores the new key and value give the tokens of the steps
+    that run the two kernels one after the other (their arithmetic is the same), while pages of
+    the windowed layer come back and are used again."""
+    import vllm_from_scratch_b200 as engine
+    from vllm_from_scratch_b200 import kernels
+    raw = tiny_configs.TINY_E
+    prompts = [helpers.random_tokens(raw["vocab_size"], n, seed=70 + i) for i, n in enumerate([3, 60, 17, 130, 64])]
+    params = engine.SamplingParams(temperature=0.0, max_tokens=70)
+    results, launches = {}, {}
+    for fused in (True, False):
+        if fused:
+            monkeypatch.delenv("B200_NO_FUSED_DECODE", raising=False)
+        else:
+            monkeypatch.setenv("B200_NO_FUSED_DECODE", "1")
+        llm = engine.LLM(folders["E"], dtype="bfloat16", max_model_len=256, block_size=16, max_num_seqs=4,
+                         max_num_batched_tokens=64, enforce_eager=eager)
+        before = kernels.launch_count
+        results[fused] = [output.token_ids for output in llm.generate(prompts, params)]
+        launches[fused] = kernels.launch_count - before
+        llm.engine.runner.manager.check_invariants()
+        assert llm.engine.runner.manager.stats()["requests"] == 0
+        assert kernels.device_error() is None
+    assert results[True] == results[False]
+    if eager:
+        assert launches[True] < launches[False], "the decode steps must have run the one-kernel form"

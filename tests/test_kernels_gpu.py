@@ -382,6 +382,70 @@ def test_tensor_memory_gemm_by_switch(monkeypatch):
         assert float((got.float() - want.float()).abs().max()) <= float(want.float().abs().max()) * 2 ** -7
 
 
+FUSED_DECODE_SHAPES = [
+    # nq, nkv, page, seq_lens, window, head norms
+    (16, 8, 16, [1, 63, 64, 65, 129, 1000, 2100, 17], None, True),
+    (4, 4, 8, [2, 300, 128, 513], None, True),
+    (16, 1, 64, [700, 64, 1, 1025], None, False),
+    (6, 2, 16, [40, 600, 257, 1024], 256, True),
+    (8, 2, 128, [128, 129, 3000], None, True),
+]
+
+
+@pytest.mark.parametrize("shape", FUSED_DECODE_SHAPES)
+def test_fused_decode_attention(shape):
+    """Head norms, rotation, the store of the new key and value and the attention of a decode step
+    in one kernel give what the two kernels give one after the other: the same output, the same
+    pages, bit for bit (the arithmetic is the same), and nothing stored for a negative slot."""
+    k = kernels()
+    from vllm_from_scratch_b200.kernels import attention_bf16
+    nq, nkv, page, seq_lens, window, normed = shape
+    d = 128
+    requests = len(seq_lens)
+    _, kp, vp, _, seq, table = _attention_case(torch.bfloat16, nq, nkv, d, page, [1] * requests, seq_lens, window,
+                                               seed=nq + page)
+    g = torch.Generator(device="cuda").manual_seed(3)
+    qkv = torch.randn(requests, (nq + 2 * nkv) * d, device="cuda", generator=g).bfloat16()
+    positions = (seq - 1).to(torch.int32)
+    page_of = table[torch.arange(requests, device="cuda"), ((seq - 1) // page).long()]
+    slots = (page_of * page + (seq - 1) % page).to(torch.int32)
+    slots[-1] = -1                                       # the last request stores nothing
+    q_w = (1 + 0.1 * torch.randn(d, device="cuda", generator=g)) if normed else None
+    k_w = (1 + 0.1 * torch.randn(d, device="cuda", generator=g)) if normed else None
+    inv_freq = (1e4 ** (-torch.arange(0, d, 2, device="cuda").float() / d)).contiguous()
+    start = torch.arange(requests + 1, dtype=torch.int32, device="cuda")
+    # one after the other
+    kp_a, vp_a = kp.clone(), vp.clone()
+    q = torch.empty(requests, nq * d, device="cuda", dtype=torch.bfloat16)
+    k.head_norm_rope_cache(qkv, positions, slots, q_w, k_w, inv_freq, d, 1e-6, q, kp_a, vp_a, nq, nkv, d, page)
+    out_a = torch.zeros_like(q)
+    k.paged_attention(q, kp_a, vp_a, out_a, start, seq, table, nq, nkv, d, page, d ** -0.5, window, 1, max(seq_lens))
+    # in one
+    kp_b, vp_b = kp.clone(), vp.clone()
+    out_b = torch.zeros_like(q)
+    assert k.fused_decode_attention(qkv, positions, slots, q_w, k_w, inv_freq, d, 1e-6, kp_b, vp_b, out_b, seq, table,
+                                    nq, nkv, d, page, d ** -0.5, window, max(seq_lens))
+    assert attention_bf16.attention_error_code() == 0
+    assert torch.equal(kp_a, kp_b) and torch.equal(vp_a, vp_b)
+    assert not torch.equal(kp_a, kp)                     # something was stored
+    stored = slots[:-1].long()
+    assert torch.equal(kp_b.view(-1, nkv, page, d)[stored // page, :, stored % page],
+                       kp_a.view(-1, nkv, page, d)[stored // page, :, stored % page])
+    # The request that stores nothing reads what its slot held before in the first path and its
+    # own new key in the second: compare the others exactly, and all of them with the plain
+    # reference given the pages after the store.
+    assert torch.equal(out_a[:-1], out_b[:-1])
+    kp_c, vp_c = kp_a.clone(), vp_a.clone()
+    last_page, last_offset = int(page_of[-1]), int((seq[-1] - 1) % page)
+    q_c = torch.empty_like(q)
+    all_slots = (page_of * page + (seq - 1) % page).to(torch.int32)
+    k.head_norm_rope_cache(qkv, positions, all_slots, q_w, k_w, inv_freq, d, 1e-6, q_c, kp_c, vp_c, nq, nkv, d, page)
+    expected = torch.zeros_like(q)
+    plain_ops.paged_attention(q_c, kp_c, vp_c, expected, start, seq, table, nq, nkv, d, page, d ** -0.5, window, 1,
+                              max(seq_lens))
+    close(out_b, expected, torch.bfloat16, scale=2, what="fused decode attention")
+
+
 TENSOR_MEMORY_ATTENTION_SHAPES = [
     # nq, nkv, d, page, q_lens, seq_lens, window
     (2, 1, 128, 16, [128], [128], None),

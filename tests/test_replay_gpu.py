@@ -20,12 +20,13 @@ pytestmark = pytest.mark.gpu
 
 ROOT = Path(__file__).resolve().parent.parent
 CONFIGS = {"A": (tiny_configs.TINY_A, 16), "B": (tiny_configs.TINY_B, 8), "C": (tiny_configs.TINY_C, 16),
-           "D": (tiny_configs.TINY_D, 16)}
+           "D": (tiny_configs.TINY_D, 16), "E": (tiny_configs.TINY_E, 16)}
 LENGTHS = {
     "A": {"a": 70, "b": 45, "c": 100, "d": 37, "e": 64, "f": 3, "g": 128},
     "B": {"a": 70, "b": 145, "c": 100, "d": 37, "e": 64, "f": 2, "g": 200},
     "C": {"a": 70, "b": 145, "c": 100, "d": 37, "e": 64, "f": 5, "g": 300},
     "D": {"a": 70, "b": 145, "c": 100, "d": 37, "e": 64, "f": 2, "g": 410},
+    "E": {"a": 70, "b": 145, "c": 100, "d": 37, "e": 64, "f": 2, "g": 330},
 }
 # float32: rounding of sums taken in another order.  bfloat16: activations carry
 # 8 bits; the bound is a fraction of the largest logit of the sequence.

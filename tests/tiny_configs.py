@@ -40,6 +40,19 @@ TINY_D = {
     "hidden_act": "silu", "attention_bias": False, "initializer_range": 0.02,
 }
 
+# Head size 128, the checkpoint's own: in bfloat16 a decode step of this one runs the kernel that
+# normalises and rotates the heads, stores the new key and value and attends in one, a portion of a
+# prompt the tcgen05 kernel; one layer sees a window only.
+TINY_E = {
+    "architectures": ["Qwen3ForCausalLM"], "model_type": "qwen3",
+    "num_hidden_layers": 3, "hidden_size": 160, "num_attention_heads": 4, "num_key_value_heads": 2,
+    "head_dim": 128, "intermediate_size": 224, "vocab_size": 389, "rope_theta": 1000000.0,
+    "rms_norm_eps": 1e-6, "tie_word_embeddings": False, "max_position_embeddings": 512,
+    "hidden_act": "silu", "attention_bias": False, "initializer_range": 0.02,
+    "use_sliding_window": True, "sliding_window": 48,
+    "layer_types": ["full_attention", "sliding_attention", "full_attention"],
+}
+
 # Larger standard deviations than a checkpoint's, so that attention scores and
 # logits are far from uniform and a wrong key or a wrong page shows in the result.
 INIT = {"std": 0.08, "norm_std": 0.1}

@@ -60,12 +60,50 @@ B200_EXPORT int b200_decode_attention_tma_bf16(
     if (map_k == nullptr || map_v == nullptr) return fail("decode_attention", "could not encode a tensor map");
 #define B200_CASE(D)                                                                                        \
     if (d == D)                                                                                             \
-        return launch_decode_tma<D>(map_k, map_v, q, out, partial_o, partial_ml, seq_lens, block_table,     \
-                                    num_requests, max_pages, nq, nkv, page_size, scale, window, splits,    \
-                                    error_flag, stream);
+        return launch_decode_tma<D, false>(map_k, map_v, q, out, partial_o, partial_ml, seq_lens,          \
+                                           block_table, num_requests, max_pages, nq, nkv, page_size, scale, \
+                                           window, splits, error_flag, stream);
     B200_CASE(64) B200_CASE(128) B200_CASE(256)
 #undef B200_CASE
     return fail("decode_attention", "head_dim not built");
+}
+
+// 1 if the decode kernel that also normalises and rotates the heads and stores the new key and value takes the shape.
+B200_EXPORT int b200_decode_attention_fused_supports(int nq, int nkv, int d, int rotary_dim, int page_size) {
+    return d == 128 && rotary_dim == d && b200_decode_attention_tma_supports(nq, nkv, d, page_size) ? 1 : 0;
+}
+
+// One decode step's attention from the packed projection qkv [T, (nq + 2 nkv) d], one token per request:
+// what b200_head_norm_rope_cache (rope_cache.cu) followed by b200_decode_attention_tma_bf16 does.
+B200_EXPORT int b200_decode_attention_fused_bf16(
+    const void* qkv, const int* positions, const int* slots, const float* q_weight, const float* k_weight,
+    const float* inv_freq, float eps, void* k_pages, void* v_pages, void* out, float* partial_o,
+    float* partial_ml, const int* seq_lens, const int* block_table, int num_requests, int max_pages, int nq,
+    int nkv, int d, int page_size, int num_pages, float scale, int window, int splits, cudaStream_t stream) {
+    using namespace b200;
+    if (num_requests == 0) return 0;
+    if (!b200_decode_attention_fused_supports(nq, nkv, d, d, page_size)) return fail("decode_attention", "shape not built");
+    if (splits < 1 || nkv > 65535 || num_requests > 65535) return fail("decode_attention", "grid out of range");
+    if (splits > 1 && (partial_o == nullptr || partial_ml == nullptr))
+        return fail("decode_attention", "scratch for the splits is missing");
+    int* error_flag = attention_error_flag();
+    if (error_flag == nullptr) return fail("decode_attention", "no error flag");
+    const int copy_rows = page_size < kKeys ? page_size : kKeys;
+    const CUtensorMap* map_k = tensor_map_for(k_pages, num_pages * nkv * page_size, d, copy_rows);
+    const CUtensorMap* map_v = tensor_map_for(v_pages, num_pages * nkv * page_size, d, copy_rows);
+    if (map_k == nullptr || map_v == nullptr) return fail("decode_attention", "could not encode a tensor map");
+    DecodeRope rope;
+    rope.positions = positions;
+    rope.slots = slots;
+    rope.q_weight = q_weight;
+    rope.k_weight = k_weight;
+    rope.inv_freq = inv_freq;
+    rope.k_pages = (bf16*)k_pages;
+    rope.v_pages = (bf16*)v_pages;
+    rope.eps = eps;
+    return launch_decode_tma<128, true>(map_k, map_v, qkv, out, partial_o, partial_ml, seq_lens, block_table,
+                                        num_requests, max_pages, nq, nkv, page_size, scale, window, splits,
+                                        error_flag, stream, rope);
 }
 
 B200_EXPORT int b200_prefill_attention_bf16(

@@ -51,6 +51,15 @@ __device__ __forceinline__ float warp_max(float v) {
     return v;
 }
 
+// Rotation of a pair of channels by an angle (rotate-half position encoding).  Written out
+// with the product that is rounded on its own named, because a compiler may contract
+// a * b - c * d either way: every kernel that rotates (for a portion of a prompt, for a decode
+// step, inside the decode attention) must round a key or a query alike.
+__device__ __forceinline__ void rotate_pair(float x1, float x2, float c, float s, float& o1, float& o2) {
+    o1 = fmaf(x1, c, -__fmul_rn(x2, s));
+    o2 = fmaf(x2, c, __fmul_rn(x1, s));
+}
+
 // Sum over the whole block; every thread gets the result.  `scratch` holds 33 floats.
 __device__ __forceinline__ float block_sum(float v, float* scratch) {
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;

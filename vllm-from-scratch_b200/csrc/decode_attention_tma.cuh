@@ -16,6 +16,15 @@
 // Rows that no copy fills (past the end, pages given back) keep what the stage held;
 // the value stages are zeroed once so that this is never a NaN pattern.
 // grid (splits, kv heads, requests), 160 threads.  Waits are bounded.
+//
+// FUSED: the kernel takes the packed projection [T, (nq + 2 nkv) d] itself and does what
+// head_norm_rope_cache_kernel (rope_cache.cu) does for a decode step, with its arithmetic:
+// every block normalises and rotates the query heads of its group into shared memory; the
+// block whose keys end at the newest position also normalises and rotates the new key,
+// writes it and the new value into their page, and puts both into the row of its last tile
+// that the copy of the page filled with what the slot held before.  A step then has one
+// kernel less in its chain, and no tile has to wait for the kernel ahead: all of them come
+// from earlier steps.
 #pragma once
 
 #include "attention_bf16_kernels.cuh"
@@ -26,13 +35,27 @@ namespace b200 {
 constexpr int kDtStages = 2;
 constexpr int kDtThreads = 160;                 // four compute warps and the copying warp
 
-template <int D>
+// What the fused form needs beside the attention's own arguments (see rope_cache.cu).
+struct DecodeRope {
+    const int* positions;       // [T]
+    const int* slots;           // [T] page * page_size + offset of the new key, negative: do not store
+    const float* q_weight;      // [d] or null: no norm
+    const float* k_weight;
+    const float* inv_freq;      // [d / 2]
+    bf16* k_pages;
+    bf16* v_pages;
+    float eps;
+};
+template <int D> constexpr int decode_rope_smem() { return D * 4 + 16 * D * 2 + 2 * D * 2; }   // sin, cos; q; new key, value
+
+template <int D, bool FUSED>
 __global__ void __launch_bounds__(kDtThreads, D <= 128 ? 3 : 1) decode_attention_tma_kernel(
     const __grid_constant__ CUtensorMap map_k, const __grid_constant__ CUtensorMap map_v,
     const bf16* __restrict__ q, bf16* __restrict__ out, float* __restrict__ partial_o,
     float* __restrict__ partial_ml, const int* __restrict__ seq_lens, const int* __restrict__ block_table,
     int max_pages, int nq, int nkv, int page_size, float scale_log2, int window, int splits,
-    int* __restrict__ error_flag) {
+    int* __restrict__ error_flag, DecodeRope rope) {
+    static_assert(!FUSED || D == 128, "the fused form holds two pairs of channels per lane");
     constexpr int kBlocks = D / 64;                         // channel blocks of 64 (128 bytes a row)
     constexpr int kBlockBytes = kKeys * 128;                // one [64 keys x 64 channels] block
     constexpr int kTileBytes = kBlocks * kBlockBytes;       // K or V of a tile
@@ -40,6 +63,10 @@ __global__ void __launch_bounds__(kDtThreads, D <= 128 ? 3 : 1) decode_attention
     unsigned char* smem = reinterpret_cast<unsigned char*>(((uintptr_t)smem_dt + 1023) & ~(uintptr_t)1023);
     unsigned long long* full_bar = reinterpret_cast<unsigned long long*>(smem + kDtStages * 2 * kTileBytes);
     unsigned long long* empty_bar = full_bar + kDtStages;
+    float* sin_s = reinterpret_cast<float*>(smem + kDtStages * 2 * kTileBytes + 64);     // FUSED only, [D / 2] each
+    float* cos_s = sin_s + D / 2;
+    bf16* q_s = reinterpret_cast<bf16*>(cos_s + D / 2);                                 // [16][D]
+    bf16* new_s = q_s + 16 * D;                                                         // [2][D]: new key, new value
     overlap_trigger();
     const int split = blockIdx.x, kv_head = blockIdx.y, request = blockIdx.z;
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
@@ -54,6 +81,7 @@ __global__ void __launch_bounds__(kDtThreads, D <= 128 ? 3 : 1) decode_attention
     const int my_end = min(seq_len, my_begin + chunk);
     const int tiles = my_end > my_begin ? (my_end - my_begin + kKeys - 1) / kKeys : 0;
     const int* table = block_table + (size_t)request * max_pages;
+    const bool owner = FUSED && tiles > 0 && my_end == seq_len;         // this block's keys end at the newest one
 
     if (tid == 0) {
         for (int s = 0; s < kDtStages; ++s) {
@@ -95,7 +123,7 @@ __global__ void __launch_bounds__(kDtThreads, D <= 128 ? 3 : 1) decode_attention
         bool waited = false;
         for (int t = 0; t < tiles; ++t) {
             const int s = t % kDtStages;
-            if (!waited && (t >= kDtStages || my_begin + (t + 1) * kKeys >= seq_len)) {
+            if (!FUSED && !waited && (t >= kDtStages || my_begin + (t + 1) * kKeys >= seq_len)) {
                 overlap_wait();
                 waited = true;
             }
@@ -123,11 +151,84 @@ __global__ void __launch_bounds__(kDtThreads, D <= 128 ? 3 : 1) decode_attention
         }
     } else {
         // -------- four warps, 16 keys of every tile each --------
-        overlap_wait();
-        const bf16* q_base = q + ((size_t)request * nq + (size_t)kv_head * group) * D;
         unsigned qa[D / 16][4];
-        load_q_fragments<D>(qa, row_a < group ? q_base + (size_t)row_a * D : nullptr,
-                            row_b < group ? q_base + (size_t)row_b * D : nullptr, lane);
+        if (FUSED) {
+            // Before the wait: what does not come from the kernel ahead (position, angles, weights, slot).
+            const float pos = (float)rope.positions[request];
+            if (tid < D / 2) sincosf(pos * rope.inv_freq[tid], &sin_s[tid], &cos_s[tid]);
+            const int slot = rope.slots[request];
+            float qw1[2], qw2[2], kw1[2], kw2[2];
+#pragma unroll
+            for (int i = 0; i < 2; ++i) {
+                const int j = lane + 32 * i;
+                qw1[i] = rope.q_weight ? rope.q_weight[j] : 1.0f;
+                qw2[i] = rope.q_weight ? rope.q_weight[j + D / 2] : 1.0f;
+                kw1[i] = rope.k_weight ? rope.k_weight[j] : 1.0f;
+                kw2[i] = rope.k_weight ? rope.k_weight[j + D / 2] : 1.0f;
+            }
+            asm volatile("bar.sync 2, 128;\n" ::: "memory");          // the angles are in shared memory
+            overlap_wait();
+            const int total_heads = nq + 2 * nkv;
+            const bf16* row = q + (size_t)request * total_heads * D;            // q is the packed projection here
+            const int items = group + (owner ? 2 : 0);                          // query heads, new key, new value
+            for (int item = warp; item < items; item += 4) {
+                const bool is_q = item < group, is_k = item == group;
+                const int head = is_q ? kv_head * group + item : (is_k ? nq + kv_head : nq + nkv + kv_head);
+                const bf16* src = row + (size_t)head * D;
+                bf16* stored = nullptr;                                         // the new key's or value's place in its page
+                if (!is_q && slot >= 0) {
+                    const int page = slot / page_size, offset = slot - page * page_size;
+                    stored = (is_k ? rope.k_pages : rope.v_pages) + (((size_t)page * nkv + kv_head) * page_size + offset) * D;
+                }
+                bf16 held[4];                                                   // channels lane, lane + 32, + 64, + 96
+#pragma unroll
+                for (int i = 0; i < 4; ++i) held[i] = src[lane + 32 * i];
+                if (!is_q && !is_k) {
+#pragma unroll
+                    for (int i = 0; i < 4; ++i) {
+                        new_s[D + lane + 32 * i] = held[i];
+                        if (stored) stored[lane + 32 * i] = held[i];
+                    }
+                    continue;
+                }
+                const float* weight = is_q ? rope.q_weight : rope.k_weight;
+                float inv = 1.0f;
+                if (weight) {
+                    float sum_sq = 0.0f;
+#pragma unroll
+                    for (int i = 0; i < 4; ++i) {                               // the order of rope_cache.cu's loop
+                        const float v = to_float(held[i]);
+                        sum_sq = fmaf(v, v, sum_sq);
+                    }
+                    sum_sq = warp_sum(sum_sq);
+                    inv = rsqrtf(sum_sq / (float)D + rope.eps);
+                }
+                bf16* dst = is_q ? q_s + item * D : new_s;
+#pragma unroll
+                for (int i = 0; i < 2; ++i) {
+                    const int j = lane + 32 * i;
+                    const float x1 = to_float(held[i]) * inv * (is_q ? qw1[i] : kw1[i]);
+                    const float x2 = to_float(held[i + 2]) * inv * (is_q ? qw2[i] : kw2[i]);
+                    float r1, r2;
+                    rotate_pair(x1, x2, cos_s[j], sin_s[j], r1, r2);
+                    const bf16 o1 = from_float<bf16>(r1), o2 = from_float<bf16>(r2);
+                    dst[j] = o1;
+                    dst[j + D / 2] = o2;
+                    if (stored) {
+                        stored[j] = o1;
+                        stored[j + D / 2] = o2;
+                    }
+                }
+            }
+            asm volatile("bar.sync 2, 128;\n" ::: "memory");          // queries and the new key and value are in shared memory
+            load_q_fragments<D>(qa, row_a < group ? q_s + row_a * D : nullptr, row_b < group ? q_s + row_b * D : nullptr,
+                                lane);
+        } else {
+            overlap_wait();
+            const bf16* q_base = q + ((size_t)request * nq + (size_t)kv_head * group) * D;
+            load_q_fragments<D>(qa, row_a < group ? q_base + (size_t)row_a * D : nullptr,
+                                row_b < group ? q_base + (size_t)row_b * D : nullptr, lane);
+        }
 #pragma unroll
         for (int i = 0; i < D / 8; ++i) o[i][0] = o[i][1] = o[i][2] = o[i][3] = 0.0f;
         const int mi = lane >> 3, ri = lane & 7;
@@ -138,6 +239,18 @@ __global__ void __launch_bounds__(kDtThreads, D <= 128 ? 3 : 1) decode_attention
             ok = __all_sync(0xffffffffu, ok);
             const unsigned char* k_s = smem + (s * 2) * kTileBytes;
             const unsigned char* v_s = k_s + kTileBytes;
+            if (FUSED && owner && t == tiles - 1) {
+                // The newest key's row holds what its slot held before this step: the warp whose
+                // 16 keys include it (no other warp reads the row) puts the new key and value there.
+                const int r = seq_len - 1 - k0;
+                if ((r >> 4) == warp) {
+                    const int c = lane & 15;                                    // 16-byte chunk of the row
+                    const uint4 fresh = reinterpret_cast<const uint4*>(new_s + (lane >= 16 ? D : 0))[c];
+                    unsigned char* tile = smem + (s * 2 + (lane >= 16 ? 1 : 0)) * kTileBytes;
+                    *reinterpret_cast<uint4*>(tile + (c >> 3) * kBlockBytes + r * 128 + (((c & 7) ^ (r & 7)) << 4)) = fresh;
+                    __syncwarp();
+                }
+            }
 
             // scores of this warp's 16 keys
             float sc[2][4] = {{0.f, 0.f, 0.f, 0.f}, {0.f, 0.f, 0.f, 0.f}};
@@ -244,13 +357,13 @@ __global__ void __launch_bounds__(kDtThreads, D <= 128 ? 3 : 1) decode_attention
     }
 }
 
-template <int D>
+template <int D, bool FUSED>
 int launch_decode_tma(const CUtensorMap* map_k, const CUtensorMap* map_v, const void* q, void* out,
                       float* partial_o, float* partial_ml, const int* seq_lens, const int* block_table,
                       int num_requests, int max_pages, int nq, int nkv, int page_size, float scale, int window,
-                      int splits, int* error_flag, cudaStream_t stream) {
-    auto kernel = decode_attention_tma_kernel<D>;
-    const int smem = kDtStages * 2 * (D / 64) * kKeys * 128 + 64 + 1024;
+                      int splits, int* error_flag, cudaStream_t stream, DecodeRope rope = DecodeRope()) {
+    auto kernel = decode_attention_tma_kernel<D, FUSED>;
+    const int smem = kDtStages * 2 * (D / 64) * kKeys * 128 + 64 + 1024 + (FUSED ? decode_rope_smem<D>() : 0);
     static bool configured = false;
     if (!configured) {
         cudaError_t status = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
@@ -260,7 +373,7 @@ int launch_decode_tma(const CUtensorMap* map_k, const CUtensorMap* map_v, const 
     dim3 grid(splits, nkv, num_requests);
     launch_overlapped(kernel, grid, kDtThreads, smem, stream, *map_k, *map_v, (const bf16*)q, (bf16*)out, partial_o,
                       partial_ml, seq_lens, block_table, max_pages, nq, nkv, page_size, scale * kLog2e, window,
-                      splits, error_flag);
+                      splits, error_flag, rope);
     if (int rc = check_launch("decode_attention")) return rc;
     if (splits > 1) {
         launch_overlapped(merge_splits_kernel<D>, num_requests * nq, D < 128 ? D : 128, 0, stream,

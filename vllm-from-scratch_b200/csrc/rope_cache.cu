@@ -91,8 +91,10 @@ __global__ void head_norm_rope_cache_kernel(
             const int j = lane + 32 * i;
             if (j < half) {
                 const float x1 = to_float(src[j]) * inv * w1_r[i], x2 = to_float(src[j + half]) * inv * w2_r[i];
-                dst[j] = from_float<T>(x1 * cos_r[i] - x2 * sin_r[i]);
-                dst[j + half] = from_float<T>(x2 * cos_r[i] + x1 * sin_r[i]);
+                float o1, o2;
+                rotate_pair(x1, x2, cos_r[i], sin_r[i], o1, o2);
+                dst[j] = from_float<T>(o1);
+                dst[j + half] = from_float<T>(o2);
             }
         }
     } else {
@@ -101,8 +103,10 @@ __global__ void head_norm_rope_cache_kernel(
             if (weight) { x1 *= weight[j]; x2 *= weight[j + half]; }
             float s, c;
             sincosf(pos * inv_freq[j], &s, &c);
-            dst[j] = from_float<T>(x1 * c - x2 * s);
-            dst[j + half] = from_float<T>(x2 * c + x1 * s);
+            float o1, o2;
+            rotate_pair(x1, x2, c, s, o1, o2);
+            dst[j] = from_float<T>(o1);
+            dst[j + half] = from_float<T>(o2);
         }
     }
     for (int j = rotary_dim + lane; j < d; j += 32) {
@@ -174,8 +178,10 @@ __global__ void __launch_bounds__(128) head_norm_rope_cache_token_kernel(
 #pragma unroll
         for (int e = 0; e < PER; ++e) {
             const float s = sin_s[sub * PER + e], c = cos_s[sub * PER + e];
-            out_lo.v[e] = __float2bfloat16_rn(x1[e] * c - x2[e] * s);
-            out_hi.v[e] = __float2bfloat16_rn(x2[e] * c + x1[e] * s);
+            float o1, o2;
+            rotate_pair(x1[e], x2[e], c, s, o1, o2);
+            out_lo.v[e] = __float2bfloat16_rn(o1);
+            out_hi.v[e] = __float2bfloat16_rn(o2);
         }
         *reinterpret_cast<Vec*>(dst) = out_lo;
         *reinterpret_cast<Vec*>(dst + HALF) = out_hi;

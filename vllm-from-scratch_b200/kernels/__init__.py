@@ -228,6 +228,39 @@ def head_norm_rope_cache(qkv: torch.Tensor, positions: torch.Tensor, slots: torc
          _F(eps), _I(_code(dtype)), _stream())
 
 
+def fused_decode_attention(qkv: torch.Tensor, positions: torch.Tensor, slots: torch.Tensor,
+                           q_weight: torch.Tensor | None, k_weight: torch.Tensor | None,
+                           inv_freq: torch.Tensor | None, rotary_dim: int, eps: float, k_pages: torch.Tensor,
+                           v_pages: torch.Tensor, out: torch.Tensor, seq_lens: torch.Tensor,
+                           block_table: torch.Tensor, num_q_heads: int, num_kv_heads: int, head_dim: int,
+                           page_size: int, scale: float, window: int | None, max_seq_len: int) -> bool:
+    """``head_norm_rope_cache`` and ``paged_attention`` of a decode step (one new token per
+    request, in the order of the requests) as one kernel, where there is one for the shape:
+    returns False, having done nothing, where there is not."""
+    tokens = qkv.shape[0]
+    requests = seq_lens.shape[0]
+    if (qkv.dtype != torch.bfloat16 or tokens != requests or inv_freq is None or k_pages is None
+            or v_pages is None):
+        return False
+    width = (num_q_heads + 2 * num_kv_heads) * head_dim
+    page_shape = (None, num_kv_heads, page_size, head_dim)
+    _check("qkv", qkv, torch.bfloat16, (tokens, width))
+    _check("positions", positions, torch.int32, (tokens,))
+    _check("slot mapping", slots, torch.int32, (tokens,))
+    _check("q head-norm weight", q_weight, torch.float32, (head_dim,), optional=True)
+    _check("k head-norm weight", k_weight, torch.float32, (head_dim,), optional=True)
+    _check("inverse frequencies", inv_freq, torch.float32, (rotary_dim // 2,))
+    _check("key pages", k_pages, torch.bfloat16, page_shape)
+    _check("value pages", v_pages, torch.bfloat16, page_shape)
+    _check("attention output", out, torch.bfloat16, (tokens, num_q_heads * head_dim))
+    _check("sequence lengths", seq_lens, torch.int32, (requests,))
+    _check("block table", block_table, torch.int32, (requests, None))
+    from . import attention_bf16
+    return attention_bf16.fused_decode_attention_bf16(
+        qkv, positions, slots, q_weight, k_weight, inv_freq, rotary_dim, eps, k_pages, v_pages, out, seq_lens,
+        block_table, num_q_heads, num_kv_heads, head_dim, page_size, scale, window, max_seq_len)
+
+
 def paged_attention(q: torch.Tensor, k_pages: torch.Tensor, v_pages: torch.Tensor, out: torch.Tensor,
                     query_start: torch.Tensor, seq_lens: torch.Tensor, block_table: torch.Tensor,
                     num_q_heads: int, num_kv_heads: int, head_dim: int, page_size: int, scale: float,

@@ -87,6 +87,39 @@ def paged_attention_bf16(q, k_pages, v_pages, out, query_start, seq_lens, block_
     return True
 
 
+def fused_decode_attention_bf16(qkv, positions, slots, q_weight, k_weight, inv_freq, rotary_dim, eps, k_pages,
+                                v_pages, out, seq_lens, block_table, num_q_heads, num_kv_heads, head_dim,
+                                page_size, scale, window, max_seq_len) -> bool:
+    """A decode step's attention straight from the packed projection: head norms, rotation,
+    the store of the new key and value, and the attention over the pages in one kernel (and
+    the merge of the splits).  False if the shape is not one that kernel takes (or
+    ``B200_NO_FUSED_DECODE`` is set): the caller then runs the two kernels one after the other."""
+    if os.environ.get("B200_NO_FUSED_DECODE") is not None or os.environ.get("B200_NO_TMA_DECODE") is not None:
+        return False
+    lib = load_library("attention_bf16")
+    if not lib.b200_decode_attention_fused_supports(num_q_heads, num_kv_heads, head_dim, rotary_dim, page_size):
+        return False
+    from . import KernelError, _stream, count_launch
+    requests = seq_lens.shape[0]
+    splits = decode_splits(requests, num_kv_heads, max_seq_len)
+    partial_o = partial_ml = None
+    if splits > 1:
+        partial_o = torch.empty((requests * num_q_heads * splits, head_dim), dtype=torch.float32, device=qkv.device)
+        partial_ml = torch.empty((requests * num_q_heads * splits, 2), dtype=torch.float32, device=qkv.device)
+    status = lib.b200_decode_attention_fused_bf16(
+        _P(qkv.data_ptr()), _P(positions.data_ptr()), _P(slots.data_ptr()),
+        _P(q_weight.data_ptr() if q_weight is not None else 0), _P(k_weight.data_ptr() if k_weight is not None else 0),
+        _P(inv_freq.data_ptr()), _F(eps), _P(k_pages.data_ptr()), _P(v_pages.data_ptr()), _P(out.data_ptr()),
+        _P(partial_o.data_ptr() if splits > 1 else 0), _P(partial_ml.data_ptr() if splits > 1 else 0),
+        _P(seq_lens.data_ptr()), _P(block_table.data_ptr()), _I(requests), _I(block_table.shape[1]),
+        _I(num_q_heads), _I(num_kv_heads), _I(head_dim), _I(page_size), _I(k_pages.shape[0]), _F(scale),
+        _I(window or 0), _I(splits), _stream())
+    if status != 0:
+        raise KernelError(lib.b200_last_error().decode())
+    count_launch()
+    return True
+
+
 def attention_error_code() -> int:
     """0, or the code left by an attention kernel whose bounded wait ran out (synchronises)."""
     return int(load_library("attention_bf16").b200_attention_error())

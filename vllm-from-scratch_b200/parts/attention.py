@@ -83,12 +83,23 @@ class PagedAttention(Mixer):
         nq, nkv, d = self.num_heads, self.num_kv_heads, self.head_dim
         qkv = torch.empty((tokens, (nq + 2 * nkv) * d), dtype=x.dtype, device=x.device)
         kernels.gemm(x, self.qkv, qkv)
-        q = torch.empty((tokens, nq * d), dtype=x.dtype, device=x.device)
         store = cache.writable
+        eps = self.qk_norm_eps if self.qk_norm_eps is not None else 0.0
+        if store and ctx.max_query_len == 1:
+            # a decode step: norms, rotation, the store of the new key and value and the attention in one kernel
+            attended = torch.empty((tokens, nq * d), dtype=x.dtype, device=x.device)
+            if kernels.fused_decode_attention(
+                    qkv, ctx.positions, group.slot_mapping, self.q_norm, self.k_norm,
+                    self.position.inverse_frequencies(), self.position.rotary_dim, eps, cache.keys, cache.values,
+                    attended, ctx.seq_lens, group.block_table, nq, nkv, d, group.page_size, self.scale, self.window,
+                    ctx.max_seq_len):
+                out = torch.empty((tokens, self.env.hidden_size), dtype=x.dtype, device=x.device)
+                kernels.gemm(attended, self.out_proj, out)
+                return out
+        q = torch.empty((tokens, nq * d), dtype=x.dtype, device=x.device)
         kernels.head_norm_rope_cache(
             qkv, ctx.positions, group.slot_mapping, self.q_norm, self.k_norm,
-            self.position.inverse_frequencies(), self.position.rotary_dim,
-            self.qk_norm_eps if self.qk_norm_eps is not None else 0.0, q,
+            self.position.inverse_frequencies(), self.position.rotary_dim, eps, q,
             cache.keys if store else None, cache.values if store else None, nq, nkv, d, group.page_size)
         attended = torch.empty_like(q)
         kernels.paged_attention(
