@@ -1,6 +1,7 @@
 """Time one kernel on synthetic inputs of a given shape.
 
     python -m vllm_from_scratch_b200.kernels.microbench decode_attention --batch 64 --context 2048
+    python -m vllm_from_scratch_b200.kernels.microbench decode_attention --batch 64 --context 2048 --fused
     python -m vllm_from_scratch_b200.kernels.microbench prefill_attention --tokens 2048
     python -m vllm_from_scratch_b200.kernels.microbench gemm --m 8 --n 12288 --k 2048
     python -m vllm_from_scratch_b200.kernels.microbench norm | silu_mul | rope --tokens 2048
@@ -86,6 +87,9 @@ def main(argv=None) -> int:
                         help="attention: launches per timed graph replay (the time printed is per launch); "
                              "short kernels need several, CUDA events resolve no better than some microseconds")
     parser.add_argument("--gated", action="store_true", help="gemm: fused silu(gate) * up, N = 2 * inter")
+    parser.add_argument("--fused", action="store_true",
+                        help="decode_attention: the kernel that takes the packed projection and also normalises "
+                             "and rotates the heads and stores the new key and value")
     parser.add_argument("--kernel", default="default", choices=("default", "tc", "library"),
                         help="gemm: the engine's choice, the tcgen05 kernel, or the vendor library")
     args = parser.parse_args(argv)
@@ -104,6 +108,19 @@ def main(argv=None) -> int:
         planned = args.planned_context or context
         one = lambda: kernels.paged_attention(q, kp, vp, out, start, seq, table, nq, nkv, d, args.page,
                                               d ** -0.5, None, q_len, planned)
+        if decode and args.fused:
+            qkv = torch.randn(batch, (nq + 2 * nkv) * d, device="cuda").to(dtype)
+            positions = (seq - 1).to(torch.int32)
+            last_page = table[torch.arange(batch, device="cuda"), ((seq - 1) // args.page).long()]
+            slots = (last_page * args.page + (seq - 1) % args.page).to(torch.int32)
+            weight = torch.ones(d, device="cuda")
+            inv_freq = (1.0 / (1e6 ** (torch.arange(0, d, 2, dtype=torch.float32) / d))).cuda()
+
+            def one():
+                if not kernels.fused_decode_attention(qkv, positions, slots, weight, weight, inv_freq, d, 1e-6, kp, vp,
+                                                      out, seq, table, nq, nkv, d, args.page, d ** -0.5, None, planned):
+                    raise SystemExit("no fused kernel for this shape")
+            record["fused"] = True
 
         def fn():
             for _ in range(args.repeat):
