@@ -108,7 +108,9 @@ __global__ void __launch_bounds__(kDtThreads, D <= 128 ? 3 : 1) decode_attention
     asm volatile("fence.proxy.async.shared::cta;\n" ::: "memory");
     __syncthreads();
     // Only the newest key and value (and the queries) come from the kernel before this one:
-    // tiles that end before the newest position are requested before waiting for it.
+    // tiles that end before the newest position are requested before waiting for it.  (FUSED:
+    // the kernel makes the newest key and value itself, so no tile waits; block tables,
+    // lengths, positions and slots are inputs of the step, in place before its first kernel.)
     bool ok = true;
 
     float o[D / 8][4];
