@@ -80,7 +80,9 @@ def head_norm_rope_cache(qkv, positions, slots, q_weight, k_weight, inv_freq, ro
 
 
 def paged_attention(q, k_pages, v_pages, out, query_start, seq_lens, block_table, num_q_heads,
-                    num_kv_heads, head_dim, page_size, scale, window, max_query_len, max_seq_len):
+                    num_kv_heads, head_dim, page_size, scale, window, max_query_len, max_seq_len, num_decode=0,
+                    decode_done=False):
+    assert not decode_done, "the plain version runs every request itself"
     nq, nkv, d = num_q_heads, num_kv_heads, head_dim
     group = nq // nkv
     starts = query_start.tolist()
@@ -110,7 +112,13 @@ def paged_attention(q, k_pages, v_pages, out, query_start, seq_lens, block_table
         out[begin:end] = result.to(out.dtype)
 
 
-ALL = ("embedding", "add_rmsnorm", "silu_mul", "gemm", "gated_silu_gemm", "head_norm_rope_cache", "paged_attention")
+def fused_decode_attention(*args, **kwargs):
+    """There is no plain version of the kernel that does both: the caller runs the two steps."""
+    return False
+
+
+ALL = ("embedding", "add_rmsnorm", "silu_mul", "gemm", "gated_silu_gemm", "head_norm_rope_cache", "paged_attention",
+       "fused_decode_attention")
 
 
 def patch(monkeypatch) -> None:

@@ -122,7 +122,8 @@ def test_a_kernel_error_flag_stops_the_engine(folders, monkeypatch):
 
 def test_packing_with_empty_requests_and_repeated_wanted_rows(folders):
     """Shapes fixed in advance: requests without tokens after the real ones, wanted rows
-    filled up with row 0; nothing about the real requests changes."""
+    filled up with row 0; nothing about the real requests changes.  The request that brings
+    one token is put ahead of the one that brings a portion; the wanted rows follow it."""
     runner = engine.ModelRunner.from_folder(folders["A"], "float32", 16, 8, 4, device="cpu")
     for rid, n in (("a", 5), ("b", 1)):
         runner.manager.admit(rid)
@@ -132,15 +133,18 @@ def test_packing_with_empty_requests_and_repeated_wanted_rows(folders):
     plain, plain_meta = step.pack_host(entries, table_width=4)
     host, meta = step.pack_host(entries, pad_requests=4, table_width=4, pad_tokens=0, pad_wanted=4)
     assert meta["num_tokens"] == plain_meta["num_tokens"] == 6 and meta["num_requests"] == 4
-    assert meta["query_start"] == [0, 5, 6, 6, 6] and meta["seq_lens"] == [25, 21, 0, 0]
+    assert meta["query_start"] == [0, 1, 6, 6, 6] and meta["seq_lens"] == [21, 25, 0, 0]
     assert meta["num_wanted"] == 4 and meta["max_query_len"] == 5
+    assert meta["num_decode"] == plain_meta["num_decode"] == 1
     ctx, ids, want = step.context_from(host, meta)
     plain_ctx, plain_ids, plain_want = step.context_from(plain, plain_meta)
-    assert ids.tolist() == plain_ids.tolist() == [1, 2, 3, 4, 5, 9]
-    assert want.tolist() == [4, 0, 0, 0] and plain_want.tolist() == [4]
+    assert ids.tolist() == plain_ids.tolist() == [9, 1, 2, 3, 4, 5]
+    assert want.tolist() == [5, 0, 0, 0] and plain_want.tolist() == [5]
+    assert ctx.num_decode == 1
     assert ctx.groups[0].block_table[:2].tolist() == plain_ctx.groups[0].block_table.tolist()
     assert ctx.groups[0].block_table[2:].eq(-1).all()
     assert ctx.groups[0].slot_mapping.tolist() == plain_ctx.groups[0].slot_mapping.tolist()
     # the old form: padding requests of one token each
     host, meta = step.pack_host([entries[1]], pad_requests=2, table_width=4)
     assert meta["num_tokens"] == 2 and meta["query_start"] == [0, 1, 2] and meta["seq_lens"] == [21, 0]
+    assert meta["num_decode"] == 0                      # one kind only

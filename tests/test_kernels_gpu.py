@@ -382,6 +382,37 @@ def test_tensor_memory_gemm_by_switch(monkeypatch):
         assert float((got.float() - want.float()).abs().max()) <= float(want.float().abs().max()) * 2 ** -7
 
 
+SPLIT_BATCH_SHAPES = [
+    # nq, nkv, d, page, q_lens (single tokens first), seq_lens, window
+    (8, 2, 64, 16, [1, 1, 1, 40, 70], [300, 64, 1, 40, 170], None),
+    (4, 2, 128, 16, [1, 1, 200, 65], [500, 129, 200, 300], None),
+    (4, 4, 128, 8, [1, 130], [77, 130], 64),
+    (16, 8, 128, 16, [1] * 9 + [300, 2, 256], [2100, 64, 65, 1, 700, 33, 1000, 128, 4000, 300, 50, 900], None),
+]
+
+
+@pytest.mark.parametrize("shape", SPLIT_BATCH_SHAPES)
+def test_mixed_batch_in_two_launches(shape):
+    """A step whose first requests bring one token and whose others bring portions: the single
+    tokens go to the decode kernel, the portions (which begin at a row other than 0) to theirs."""
+    k = kernels()
+    from vllm_from_scratch_b200.kernels import attention_bf16
+    nq, nkv, d, page, q_lens, seq_lens, window = shape
+    singles = sum(1 for n in q_lens if n == 1)
+    q, kp, vp, start, seq, table = _attention_case(torch.bfloat16, nq, nkv, d, page, q_lens, seq_lens, window,
+                                                   seed=nq + d)
+    out_a = torch.full_like(q, 7.0)
+    out_b = torch.zeros_like(q)
+    before = k.launch_count
+    k.paged_attention(q, kp, vp, out_a, start, seq, table, nq, nkv, d, page, d ** -0.5, window, max(q_lens),
+                      max(seq_lens), singles)
+    assert k.launch_count == before + 2
+    assert attention_bf16.attention_error_code() == 0
+    plain_ops.paged_attention(q, kp, vp, out_b, start, seq, table, nq, nkv, d, page, d ** -0.5, window, max(q_lens),
+                              max(seq_lens))
+    close(out_a, out_b, torch.bfloat16, scale=2, what="mixed batch in two launches")
+
+
 FUSED_DECODE_SHAPES = [
     # nq, nkv, page, seq_lens, window, head norms
     (16, 8, 16, [1, 63, 64, 65, 129, 1000, 2100, 17], None, True),

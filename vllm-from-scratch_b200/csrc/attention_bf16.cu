@@ -109,14 +109,16 @@ B200_EXPORT int b200_decode_attention_fused_bf16(
 B200_EXPORT int b200_prefill_attention_bf16(
     const void* q, const void* k_pages, const void* v_pages, void* out, const int* query_start,
     const int* seq_lens, const int* block_table, int num_requests, int num_tokens, int max_pages, int nq,
-    int nkv, int d, int page_size, float scale, int window, cudaStream_t stream) {
+    int nkv, int d, int page_size, float scale, int window, int token_offset, cudaStream_t stream) {
     using namespace b200;
-    if (num_requests == 0 || num_tokens == 0) return 0;
+    if (num_requests == 0 || num_tokens - token_offset <= 0) return 0;
+    if (token_offset < 0) return fail("prefill_attention", "negative token offset");
     if (!b200_attention_bf16_supports(nq, nkv, d)) return fail("prefill_attention", "shape not built");
 #define B200_CASE(D)                                                                                     \
     if (d == D)                                                                                          \
         return launch_prefill<D>(q, k_pages, v_pages, out, query_start, seq_lens, block_table,           \
-                                 num_requests, num_tokens, max_pages, nq, nkv, page_size, scale, window, stream);
+                                 num_requests, num_tokens, max_pages, nq, nkv, page_size, scale, window, \
+                                 token_offset, stream);
     B200_CASE(64) B200_CASE(128) B200_CASE(256)
 #undef B200_CASE
     return fail("prefill_attention", "head_dim not built");
@@ -158,12 +160,16 @@ B200_EXPORT int b200_prefill_attention_tc_supports(int nq, int nkv, int d, int p
 }
 
 // The tensor-memory kernel for portions of prompts.  num_pages: pages in k_pages / v_pages.
+// q and out hold num_tokens rows and query_start rows of them; the num_requests requests
+// given here begin at row token_offset (what lies ahead of it is another launch's).
 B200_EXPORT int b200_prefill_attention_tc_bf16(
     const void* q, const void* k_pages, const void* v_pages, void* out, const int* query_start,
     const int* seq_lens, const int* block_table, int num_requests, int num_tokens, int max_pages, int nq,
-    int nkv, int d, int page_size, int num_pages, float scale, int window, cudaStream_t stream) {
+    int nkv, int d, int page_size, int num_pages, float scale, int window, int token_offset,
+    cudaStream_t stream) {
     using namespace b200;
-    if (num_requests == 0 || num_tokens == 0) return 0;
+    if (num_requests == 0 || num_tokens - token_offset <= 0) return 0;
+    if (token_offset < 0) return fail("prefill_attention_tc", "negative token offset");
     if (!b200_prefill_attention_tc_supports(nq, nkv, d, page_size)) return fail("prefill_attention_tc", "shape not built");
     int* error_flag = attention_error_flag();
     if (error_flag == nullptr) return fail("prefill_attention_tc", "no error flag");
@@ -175,11 +181,11 @@ B200_EXPORT int b200_prefill_attention_tc_bf16(
         return fail("prefill_attention_tc", "could not encode a tensor map");
     cudaError_t status = cudaFuncSetAttribute(prefill_attention_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kAtSmem);
     if (status != cudaSuccess) return fail("prefill_attention_tc", cudaGetErrorString(status));
-    const int blocks = num_tokens / kAtBlockRows + num_requests;
+    const int blocks = (num_tokens - token_offset) / kAtBlockRows + num_requests;
     if (blocks > 65535) return fail("prefill_attention_tc", "too many tokens for one launch");
     dim3 grid(nq, blocks);
     prefill_attention_tc_kernel<<<grid, kAtThreads, kAtSmem, stream>>>(
         *map_q, *map_k, *map_v, (__nv_bfloat16*)out, query_start, seq_lens, block_table, num_requests, max_pages,
-        nq, nkv, page_size, scale * kLog2e, window, error_flag);
+        nq, nkv, page_size, scale * kLog2e, window, token_offset, error_flag);
     return check_launch("prefill_attention_tc");
 }

@@ -340,7 +340,9 @@ __global__ void __launch_bounds__(kThreads, 3) prefill_attention_kernel(
     const bf16* __restrict__ q, const bf16* __restrict__ k_pages, const bf16* __restrict__ v_pages,
     bf16* __restrict__ out, const int* __restrict__ query_start, const int* __restrict__ seq_lens,
     const int* __restrict__ block_table, int num_requests, int max_pages, int nq, int nkv,
-    int page_size, float scale_log2, int window) {
+    int page_size, float scale_log2, int window, int token_offset) {
+    // token_offset: row of q and out at which the first of these requests begins (requests ahead of
+    // them in the batch are another launch's); query_start holds rows of the whole batch.
     extern __shared__ __align__(128) unsigned char smem_raw[];
     bf16* stage_base = reinterpret_cast<bf16*>(smem_raw);
     constexpr int kRows = 64;
@@ -350,12 +352,12 @@ __global__ void __launch_bounds__(kThreads, 3) prefill_attention_kernel(
     int lo = 0, hi = num_requests - 1;
     while (lo < hi) {
         const int mid = (lo + hi + 1) >> 1;
-        if (query_start[mid] / kRows + mid <= block) lo = mid; else hi = mid - 1;
+        if ((query_start[mid] - token_offset) / kRows + mid <= block) lo = mid; else hi = mid - 1;
     }
     const int request = lo;
     const int q_begin = query_start[request];
     const int q_len = query_start[request + 1] - q_begin;
-    const int tile_first = (block - (q_begin / kRows + request)) * kRows;
+    const int tile_first = (block - ((q_begin - token_offset) / kRows + request)) * kRows;
     if (tile_first >= q_len) return;
     const int rows_here = min(kRows, q_len - tile_first);
     const int seq_len = seq_lens[request];
@@ -533,15 +535,15 @@ template <int D>
 int launch_prefill(const void* q, const void* k_pages, const void* v_pages, void* out,
                    const int* query_start, const int* seq_lens, const int* block_table,
                    int num_requests, int num_tokens, int max_pages, int nq, int nkv, int page_size,
-                   float scale, int window, cudaStream_t stream) {
+                   float scale, int window, int token_offset, cudaStream_t stream) {
     auto kernel = prefill_attention_kernel<D>;
     const int smem = 2 * 2 * kKeys * D * (int)sizeof(bf16);
     cudaError_t status = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
     if (status != cudaSuccess) return fail("prefill_attention", cudaGetErrorString(status));
-    dim3 grid(num_tokens / 64 + num_requests, nq);
+    dim3 grid((num_tokens - token_offset) / 64 + num_requests, nq);
     kernel<<<grid, kThreads, smem, stream>>>(
         (const bf16*)q, (const bf16*)k_pages, (const bf16*)v_pages, (bf16*)out, query_start, seq_lens,
-        block_table, num_requests, max_pages, nq, nkv, page_size, scale * kLog2e, window);
+        block_table, num_requests, max_pages, nq, nkv, page_size, scale * kLog2e, window, token_offset);
     return check_launch("prefill_attention");
 }
 

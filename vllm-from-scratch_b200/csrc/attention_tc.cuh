@@ -175,7 +175,9 @@ __global__ void __launch_bounds__(kAtThreads, 1) prefill_attention_tc_kernel(
     const __grid_constant__ CUtensorMap map_v, __nv_bfloat16* __restrict__ out,
     const int* __restrict__ query_start, const int* __restrict__ seq_lens, const int* __restrict__ block_table,
     int num_requests, int max_pages, int nq, int nkv, int page_size, float scale_log2, int window,
-    int* __restrict__ error_flag) {
+    int token_offset, int* __restrict__ error_flag) {
+    // token_offset: row of q and out at which the first of these requests begins (requests ahead of
+    // them in the batch are another launch's); query_start holds rows of the whole batch.
     extern __shared__ unsigned char smem_raw[];
     unsigned char* smem = reinterpret_cast<unsigned char*>(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
     unsigned long long* q_bar = reinterpret_cast<unsigned long long*>(smem + kAtBars);
@@ -195,12 +197,12 @@ __global__ void __launch_bounds__(kAtThreads, 1) prefill_attention_tc_kernel(
     int lo = 0, hi = num_requests - 1;
     while (lo < hi) {
         const int mid = (lo + hi + 1) >> 1;
-        if (query_start[mid] / kAtBlockRows + mid <= block) lo = mid; else hi = mid - 1;
+        if ((query_start[mid] - token_offset) / kAtBlockRows + mid <= block) lo = mid; else hi = mid - 1;
     }
     const int request = lo;
     const int q_begin = query_start[request];
     const int q_len = query_start[request + 1] - q_begin;
-    const int tile_first = (block - (q_begin / kAtBlockRows + request)) * kAtBlockRows;
+    const int tile_first = (block - ((q_begin - token_offset) / kAtBlockRows + request)) * kAtBlockRows;
     if (tile_first >= q_len) return;
     const int rows_here = min(kAtBlockRows, q_len - tile_first);
     const int seq_len = seq_lens[request];

@@ -152,7 +152,9 @@ class MixedGraphs:
         wanted = sum(len(e.want) for e in entries)
         requests_up = 1 << (len(entries) - 1).bit_length()
         wanted_up = 0 if wanted == 0 else max(requests_up, 1 << (wanted - 1).bit_length())
-        key = (tokens, requests_up, wanted_up, self._portion_kind(max(len(e.tokens) for e in entries)))
+        singles = sum(1 for e in entries if len(e.tokens) == 1)      # the mixers' kernels split the batch there
+        key = (tokens, requests_up, wanted_up, self._portion_kind(max(len(e.tokens) for e in entries)),
+               singles if singles < len(entries) else 0)
         captured = self._graphs.get(key)
         if captured is None:
             self._seen[key] = self._seen.get(key, 0) + 1

@@ -16,6 +16,8 @@ through the cache manager before the step.
 
 from __future__ import annotations
 
+import os
+
 from dataclasses import dataclass, field
 
 import numpy as np
@@ -54,9 +56,19 @@ class StepFunction:
         """Describe the batch in one pinned int32 buffer.  For shapes fixed in advance:
         ``pad_requests`` adds requests of ``pad_tokens`` tokens (one or none) that read and
         write nothing, ``pad_wanted`` repeats the first token's row up to that many wanted
-        rows, ``table_width`` fixes the width of the block tables."""
+        rows, ``table_width`` fixes the width of the block tables.
+
+        Requests that bring one token are put ahead of those that bring a portion of a
+        prompt (the order among each kind stays), so that a mixer may give the first
+        ``num_decode`` rows to its kernel for single tokens and the rest to the one for
+        portions; the wanted rows keep the order of ``entries`` and of their ``want``."""
         page_size = self.page_size
         real = len(entries)
+        order = ([i for i, entry in enumerate(entries) if len(entry.tokens) == 1]
+                 + [i for i, entry in enumerate(entries) if len(entry.tokens) != 1])
+        num_decode = sum(1 for entry in entries if len(entry.tokens) == 1)
+        row_of = {index: row for row, index in enumerate(order)}
+        given, entries = entries, [entries[i] for i in order]
         num_requests = max(real, pad_requests or 0)
         padding = num_requests - real
         lengths = [len(entry.tokens) for entry in entries] + [pad_tokens] * padding
@@ -74,7 +86,8 @@ class StepFunction:
                                     for entry in entries] + [zeros])
         token_request = np.repeat(np.arange(num_requests, dtype=np.int32), lengths)
         want_rows: list[int] = []
-        for row, entry in enumerate(entries):
+        for index, entry in enumerate(given):
+            row = row_of[index]
             for place in entry.want:
                 if not 0 <= place < lengths[row]:
                     raise ValueError(f"request {entry.request_id!r}: wanted place {place} is outside "
@@ -117,6 +130,8 @@ class StepFunction:
             "num_wanted": len(want_rows), "max_query_len": max(lengths),
             "max_seq_len": int(seq_lens.max()), "query_start": query_start.tolist(),
             "seq_lens": seq_lens.tolist(), "slots": slots.tolist(),
+            # single-token requests ahead of portions; 0 when the step has only one kind
+            "num_decode": num_decode if 0 < num_decode < real and "B200_NO_SPLIT_BATCH" not in os.environ else 0,
         }
         return host, meta
 
@@ -130,7 +145,7 @@ class StepFunction:
             query_start=start_d, seq_lens=lens_d, state_slots=slots_d, token_request=req_d,
             max_query_len=meta["max_query_len"], max_seq_len=meta["max_seq_len"],
             host_query_start=meta["query_start"], host_seq_lens=meta["seq_lens"],
-            host_state_slots=meta["slots"])
+            host_state_slots=meta["slots"], num_decode=meta.get("num_decode", 0))
         for group, width in enumerate(meta["widths"]):
             slot_d, table_d = parts[7 + 2 * group], parts[8 + 2 * group]
             ctx.groups[group] = GroupContext(self.page_size, table_d.view(meta["num_requests"], width),

@@ -264,8 +264,12 @@ def fused_decode_attention(qkv: torch.Tensor, positions: torch.Tensor, slots: to
 def paged_attention(q: torch.Tensor, k_pages: torch.Tensor, v_pages: torch.Tensor, out: torch.Tensor,
                     query_start: torch.Tensor, seq_lens: torch.Tensor, block_table: torch.Tensor,
                     num_q_heads: int, num_kv_heads: int, head_dim: int, page_size: int, scale: float,
-                    window: int | None, max_query_len: int, max_seq_len: int) -> None:
-    """Causal attention of every request's new queries over its pages."""
+                    window: int | None, max_query_len: int, max_seq_len: int, num_decode: int = 0,
+                    decode_done: bool = False) -> None:
+    """Causal attention of every request's new queries over its pages.  ``num_decode``: in a
+    step that mixes them, the first that many requests bring one token each (the bfloat16
+    kernels then take the two kinds in a launch each); ``decode_done``: those requests have
+    their output already, only the others are run."""
     tokens = q.shape[0]
     requests = seq_lens.shape[0]
     dtype = q.dtype
@@ -283,8 +287,11 @@ def paged_attention(q: torch.Tensor, k_pages: torch.Tensor, v_pages: torch.Tenso
         from . import attention_bf16
         if attention_bf16.paged_attention_bf16(
                 q, k_pages, v_pages, out, query_start, seq_lens, block_table, num_q_heads,
-                num_kv_heads, head_dim, page_size, scale, window, max_query_len, max_seq_len):
+                num_kv_heads, head_dim, page_size, scale, window, max_query_len, max_seq_len, num_decode,
+                decode_done):
             return
+    if decode_done:
+        raise KernelError("paged_attention: decode_done is for the bfloat16 kernels only")
     _run("attention_generic", "b200_paged_attention_generic",
          *(_P(a) for a in args_checked),
          _I(requests), _I(tokens), _I(block_table.shape[1]), _I(num_q_heads), _I(num_kv_heads),

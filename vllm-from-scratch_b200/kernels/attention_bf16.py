@@ -40,49 +40,82 @@ def decode_splits(num_requests: int, num_kv_heads: int, max_seq_len: int) -> int
     return best
 
 
+def _decode(lib, q, k_pages, v_pages, out, seq_lens, block_table, num_q_heads, num_kv_heads, head_dim,
+            page_size, scale, window, max_seq_len) -> int:
+    """One token per request (row r of q belongs to request r)."""
+    from . import _stream
+    requests = seq_lens.shape[0]
+    splits = decode_splits(requests, num_kv_heads, max_seq_len)
+    partial_o = partial_ml = None
+    if splits > 1:
+        partial_o = torch.empty((requests * num_q_heads * splits, head_dim), dtype=torch.float32, device=q.device)
+        partial_ml = torch.empty((requests * num_q_heads * splits, 2), dtype=torch.float32, device=q.device)
+    common = (_P(q.data_ptr()), _P(k_pages.data_ptr()), _P(v_pages.data_ptr()), _P(out.data_ptr()),
+              _P(partial_o.data_ptr() if splits > 1 else 0), _P(partial_ml.data_ptr() if splits > 1 else 0),
+              _P(seq_lens.data_ptr()), _P(block_table.data_ptr()), _I(requests), _I(block_table.shape[1]),
+              _I(num_q_heads), _I(num_kv_heads), _I(head_dim), _I(page_size))
+    tail = (_F(scale), _I(window or 0), _I(splits), _stream())
+    if (os.environ.get("B200_NO_TMA_DECODE") is None
+            and lib.b200_decode_attention_tma_supports(num_q_heads, num_kv_heads, head_dim, page_size)):
+        # keys and values by tensor copies straight from the pages
+        return lib.b200_decode_attention_tma_bf16(*common, _I(k_pages.shape[0]), *tail)
+    return lib.b200_decode_attention_bf16(*common, *tail)
+
+
+def _portions(lib, q, k_pages, v_pages, out, query_start, seq_lens, block_table, num_q_heads, num_kv_heads,
+              head_dim, page_size, scale, window, max_query_len, token_offset) -> int:
+    """Portions of prompts (any number of tokens per request).  ``q`` and ``out`` are the whole
+    batch's, ``query_start`` holds rows of them; the requests given begin at ``token_offset``."""
+    from . import _stream
+    requests = seq_lens.shape[0]
+    tokens = q.shape[0]
+    if (max_query_len >= TC_MIN_QUERY_LEN and os.environ.get("B200_NO_TC_ATTENTION") is None
+            and lib.b200_prefill_attention_tc_supports(num_q_heads, num_kv_heads, head_dim, page_size)):
+        # long portions of prompts: the tcgen05 / tensor-memory kernel
+        return lib.b200_prefill_attention_tc_bf16(
+            _P(q.data_ptr()), _P(k_pages.data_ptr()), _P(v_pages.data_ptr()), _P(out.data_ptr()),
+            _P(query_start.data_ptr()), _P(seq_lens.data_ptr()), _P(block_table.data_ptr()), _I(requests),
+            _I(tokens), _I(block_table.shape[1]), _I(num_q_heads), _I(num_kv_heads), _I(head_dim),
+            _I(page_size), _I(k_pages.shape[0]), _F(scale), _I(window or 0), _I(token_offset), _stream())
+    return lib.b200_prefill_attention_bf16(
+        _P(q.data_ptr()), _P(k_pages.data_ptr()), _P(v_pages.data_ptr()), _P(out.data_ptr()),
+        _P(query_start.data_ptr()), _P(seq_lens.data_ptr()), _P(block_table.data_ptr()), _I(requests),
+        _I(tokens), _I(block_table.shape[1]), _I(num_q_heads), _I(num_kv_heads), _I(head_dim),
+        _I(page_size), _F(scale), _I(window or 0), _I(token_offset), _stream())
+
+
 def paged_attention_bf16(q, k_pages, v_pages, out, query_start, seq_lens, block_table, num_q_heads,
                          num_kv_heads, head_dim, page_size, scale, window, max_query_len,
-                         max_seq_len) -> bool:
+                         max_seq_len, num_decode: int = 0, decode_done: bool = False) -> bool:
+    """``num_decode``: the first that many requests bring one token each and the others
+    portions (0: one kind only); the two kinds then go to their own kernels.
+    ``decode_done``: the single tokens have been attended to already (by the fused kernel)."""
     lib = load_library("attention_bf16")
     if not lib.b200_attention_bf16_supports(num_q_heads, num_kv_heads, head_dim):
         return False
-    from . import KernelError, _stream
+    from . import KernelError, count_launch
     requests = seq_lens.shape[0]
     tokens = q.shape[0]
+    shape = (num_q_heads, num_kv_heads, head_dim, page_size, scale, window)
     if max_query_len == 1 and tokens == requests:
-        splits = decode_splits(requests, num_kv_heads, max_seq_len)
-        partial_o = partial_ml = None
-        if splits > 1:
-            partial_o = torch.empty((tokens * num_q_heads * splits, head_dim), dtype=torch.float32, device=q.device)
-            partial_ml = torch.empty((tokens * num_q_heads * splits, 2), dtype=torch.float32, device=q.device)
-        common = (_P(q.data_ptr()), _P(k_pages.data_ptr()), _P(v_pages.data_ptr()), _P(out.data_ptr()),
-                  _P(partial_o.data_ptr() if splits > 1 else 0), _P(partial_ml.data_ptr() if splits > 1 else 0),
-                  _P(seq_lens.data_ptr()), _P(block_table.data_ptr()), _I(requests), _I(block_table.shape[1]),
-                  _I(num_q_heads), _I(num_kv_heads), _I(head_dim), _I(page_size))
-        tail = (_F(scale), _I(window or 0), _I(splits), _stream())
-        if (os.environ.get("B200_NO_TMA_DECODE") is None
-                and lib.b200_decode_attention_tma_supports(num_q_heads, num_kv_heads, head_dim, page_size)):
-            # keys and values by tensor copies straight from the pages
-            status = lib.b200_decode_attention_tma_bf16(*common, _I(k_pages.shape[0]), *tail)
-        else:
-            status = lib.b200_decode_attention_bf16(*common, *tail)
-    elif (max_query_len >= TC_MIN_QUERY_LEN and os.environ.get("B200_NO_TC_ATTENTION") is None
-          and lib.b200_prefill_attention_tc_supports(num_q_heads, num_kv_heads, head_dim, page_size)):
-        # long portions of prompts: the tcgen05 / tensor-memory kernel
-        status = lib.b200_prefill_attention_tc_bf16(
-            _P(q.data_ptr()), _P(k_pages.data_ptr()), _P(v_pages.data_ptr()), _P(out.data_ptr()),
-            _P(query_start.data_ptr()), _P(seq_lens.data_ptr()), _P(block_table.data_ptr()), _I(requests),
-            _I(tokens), _I(block_table.shape[1]), _I(num_q_heads), _I(num_kv_heads), _I(head_dim),
-            _I(page_size), _I(k_pages.shape[0]), _F(scale), _I(window or 0), _stream())
+        status = _decode(lib, q, k_pages, v_pages, out, seq_lens, block_table, *shape, max_seq_len)
+    elif 0 < num_decode < requests:
+        n = num_decode
+        status = 0
+        if not decode_done:
+            status = _decode(lib, q[:n], k_pages, v_pages, out[:n], seq_lens[:n], block_table[:n], *shape,
+                             max_seq_len)
+            count_launch()
+        if status == 0:
+            status = _portions(lib, q, k_pages, v_pages, out, query_start[n:], seq_lens[n:], block_table[n:],
+                               *shape, max_query_len, n)
+    elif decode_done:
+        raise KernelError("paged_attention: decode_done without a split of the batch")
     else:
-        status = lib.b200_prefill_attention_bf16(
-            _P(q.data_ptr()), _P(k_pages.data_ptr()), _P(v_pages.data_ptr()), _P(out.data_ptr()),
-            _P(query_start.data_ptr()), _P(seq_lens.data_ptr()), _P(block_table.data_ptr()), _I(requests),
-            _I(tokens), _I(block_table.shape[1]), _I(num_q_heads), _I(num_kv_heads), _I(head_dim),
-            _I(page_size), _F(scale), _I(window or 0), _stream())
+        status = _portions(lib, q, k_pages, v_pages, out, query_start, seq_lens, block_table, *shape,
+                           max_query_len, 0)
     if status != 0:
         raise KernelError(lib.b200_last_error().decode())
-    from . import count_launch
     count_launch()
     return True
 

@@ -85,26 +85,27 @@ class PagedAttention(Mixer):
         kernels.gemm(x, self.qkv, qkv)
         store = cache.writable
         eps = self.qk_norm_eps if self.qk_norm_eps is not None else 0.0
-        if store and ctx.max_query_len == 1:
-            # a decode step: norms, rotation, the store of the new key and value and the attention in one kernel
-            attended = torch.empty((tokens, nq * d), dtype=x.dtype, device=x.device)
-            if kernels.fused_decode_attention(
-                    qkv, ctx.positions, group.slot_mapping, self.q_norm, self.k_norm,
-                    self.position.inverse_frequencies(), self.position.rotary_dim, eps, cache.keys, cache.values,
-                    attended, ctx.seq_lens, group.block_table, nq, nkv, d, group.page_size, self.scale, self.window,
-                    ctx.max_seq_len):
-                out = torch.empty((tokens, self.env.hidden_size), dtype=x.dtype, device=x.device)
-                kernels.gemm(attended, self.out_proj, out)
-                return out
-        q = torch.empty((tokens, nq * d), dtype=x.dtype, device=x.device)
-        kernels.head_norm_rope_cache(
-            qkv, ctx.positions, group.slot_mapping, self.q_norm, self.k_norm,
-            self.position.inverse_frequencies(), self.position.rotary_dim, eps, q,
-            cache.keys if store else None, cache.values if store else None, nq, nkv, d, group.page_size)
-        attended = torch.empty_like(q)
-        kernels.paged_attention(
-            q, cache.keys, cache.values, attended, ctx.query_start, ctx.seq_lens, group.block_table,
-            nq, nkv, d, group.page_size, self.scale, self.window, ctx.max_query_len, ctx.max_seq_len)
+        rope = (self.q_norm, self.k_norm, self.position.inverse_frequencies(), self.position.rotary_dim, eps)
+        attended = torch.empty((tokens, nq * d), dtype=x.dtype, device=x.device)
+        # Requests that bring one token (all of a decode step, the first ctx.num_decode of a
+        # mixed one): norms, rotation, the store of the new key and value and the attention
+        # in one kernel, where there is one for the shape.
+        single = tokens if ctx.max_query_len == 1 and tokens == ctx.num_requests else ctx.num_decode
+        fused = 0
+        if store and single > 0 and kernels.fused_decode_attention(
+                qkv[:single], ctx.positions[:single], group.slot_mapping[:single], *rope, cache.keys, cache.values,
+                attended[:single], ctx.seq_lens[:single], group.block_table[:single], nq, nkv, d, group.page_size,
+                self.scale, self.window, ctx.max_seq_len):
+            fused = single
+        if fused < tokens:
+            q = torch.empty((tokens, nq * d), dtype=x.dtype, device=x.device)
+            kernels.head_norm_rope_cache(
+                qkv[fused:], ctx.positions[fused:], group.slot_mapping[fused:], *rope, q[fused:],
+                cache.keys if store else None, cache.values if store else None, nq, nkv, d, group.page_size)
+            kernels.paged_attention(
+                q, cache.keys, cache.values, attended, ctx.query_start, ctx.seq_lens, group.block_table,
+                nq, nkv, d, group.page_size, self.scale, self.window, ctx.max_query_len, ctx.max_seq_len,
+                ctx.num_decode, decode_done=fused > 0)
         out = torch.empty((tokens, self.env.hidden_size), dtype=x.dtype, device=x.device)
         kernels.gemm(attended, self.out_proj, out)
         return out

@@ -87,6 +87,9 @@ class StepContext:
     host_query_start: list[int] = field(default_factory=list)
     host_seq_lens: list[int] = field(default_factory=list)
     host_state_slots: list[int] = field(default_factory=list)
+    # In a step that mixes them, the first num_decode requests bring one token each and the
+    # others portions of prompts; 0 in a step of one kind (and for code that does not care).
+    num_decode: int = 0
 
 
 @dataclass
