@@ -219,30 +219,34 @@ int launch_slab(const bf16* x, const bf16* w, OutT* y, int M, int N, int K, int 
         if (cudaGetSymbolAddress(&found, g_stream_error) != cudaSuccess) return fail("slab_gemm", "no error flag");
         error_flag = static_cast<int*>(found);
     }
-    static bool configured = false;
-    if (!configured) {
-        cudaError_t status = cudaFuncSetAttribute(slab_gemm_kernel<OutT, false, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024);
-        if (status == cudaSuccess)
-            status = cudaFuncSetAttribute(slab_gemm_kernel<OutT, true, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024);
-        if (status == cudaSuccess)
-            status = cudaFuncSetAttribute(slab_gemm_kernel<OutT, false, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024);
-        if (status == cudaSuccess)
-            status = cudaFuncSetAttribute(slab_gemm_kernel<OutT, true, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024);
-        if (status != cudaSuccess) return fail("slab_gemm", cudaGetErrorString(status));
-        configured = true;
-    }
     const size_t smem = slab_smem_bytes(K, gated);
     const int rows = gated ? gated_inter : N;
     const int blocks = (rows + kSlabRows - 1) / kSlabRows, threads = kSlabWarps * 32;
     const bool wide = M > 8;
-    if (gated && wide)
-        launch_overlapped(slab_gemm_kernel<OutT, true, true>, blocks, threads, smem, stream, x, w, y, M, rows, K, error_flag);
-    else if (gated)
-        launch_overlapped(slab_gemm_kernel<OutT, true, false>, blocks, threads, smem, stream, x, w, y, M, rows, K, error_flag);
-    else if (wide)
-        launch_overlapped(slab_gemm_kernel<OutT, false, true>, blocks, threads, smem, stream, x, w, y, M, rows, K, error_flag);
-    else
-        launch_overlapped(slab_gemm_kernel<OutT, false, false>, blocks, threads, smem, stream, x, w, y, M, rows, K, error_flag);
+    // More fragments of the token rows in flight (the sums are formed in the same order either
+    // way): for one or two token rows, where a decode step took 1.193 against 1.213 ms with it (at 8
+    // rows 1.504 against 1.499), in the plain form where two blocks of such rows fill an SM's shared
+    // memory, in the gated form always.
+    const bool deep = M <= 2 && (gated || K >= 4096) && getenv("B200_SLAB_SHALLOW") == nullptr;
+    auto launch = [&](auto kernel, bool* configured) {
+        if (!*configured) {
+            cudaError_t status = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024);
+            if (status != cudaSuccess) return fail("slab_gemm", cudaGetErrorString(status));
+            *configured = true;
+        }
+        launch_overlapped(kernel, blocks, threads, smem, stream, x, w, y, M, rows, K, error_flag);
+        return 0;
+    };
+    static bool configured[7] = {};
+    int rc;
+    if (gated && wide) rc = launch(slab_gemm_kernel<OutT, true, true, false>, configured + 0);
+    else if (gated && deep) rc = launch(slab_gemm_kernel<OutT, true, false, true>, configured + 1);
+    else if (gated) rc = launch(slab_gemm_kernel<OutT, true, false, false>, configured + 6);
+    else if (wide && deep) rc = launch(slab_gemm_kernel<OutT, false, true, true>, configured + 2);
+    else if (wide) rc = launch(slab_gemm_kernel<OutT, false, true, false>, configured + 3);
+    else if (deep) rc = launch(slab_gemm_kernel<OutT, false, false, true>, configured + 4);
+    else rc = launch(slab_gemm_kernel<OutT, false, false, false>, configured + 5);
+    if (rc != 0) return -1;
     return check_launch("slab_gemm") == 0 ? 1 : -1;
 }
 

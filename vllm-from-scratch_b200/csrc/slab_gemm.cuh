@@ -35,8 +35,13 @@ inline size_t slab_smem_bytes(int K, bool gated) {
 }
 
 // WIDE: 9 to 16 token rows (both halves of the 16-row operand are read).
-template <typename OutT, bool GATED, bool WIDE>
-__global__ void __launch_bounds__(kSlabWarps * 32, GATED ? 3 : 4) slab_gemm_kernel(
+// After the wait a warp's time is round trips to L2 for its fragments of the token rows (the
+// weights are in shared memory by then), one per kUnroll blocks of 32 elements of K.
+// DEEP: more of them in flight.  Plain form: rows so long (K of 4096 and more) that two blocks
+// fill an SM's shared memory, so a block may have the registers of the blocks that do not fit
+// (twelve fragments in flight, six for WIDE).  Gated form: eight instead of four.
+template <typename OutT, bool GATED, bool WIDE, bool DEEP>
+__global__ void __launch_bounds__(kSlabWarps * 32, GATED ? 3 : (DEEP ? 2 : 4)) slab_gemm_kernel(
     const __nv_bfloat16* __restrict__ x, const __nv_bfloat16* __restrict__ w, OutT* __restrict__ y, int M, int N,
     int K, int* __restrict__ error_flag) {
     extern __shared__ __align__(128) unsigned char slab_smem[];
@@ -86,7 +91,7 @@ __global__ void __launch_bounds__(kSlabWarps * 32, GATED ? 3 : 4) slab_gemm_kern
     const int blocks_per_quarter = blocks / kSlabQuarters;        // K a multiple of 128 (checked by the caller)
     const uint4 zero = make_uint4(0, 0, 0, 0);
     bool ok = true;
-    constexpr int kUnroll = WIDE ? 2 : 4;
+    constexpr int kUnroll = GATED ? (WIDE ? 2 : (DEEP ? 8 : 4)) : (DEEP ? (WIDE ? 6 : 12) : (WIDE ? 2 : 4));
     for (int q = 0; q < kSlabQuarters; ++q) {
         const int first = q * blocks_per_quarter, last = first + blocks_per_quarter;
         bool waited = false;
