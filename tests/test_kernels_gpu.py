@@ -487,13 +487,20 @@ TENSOR_MEMORY_ATTENTION_SHAPES = [
     (4, 4, 128, 128, [257, 64], [257, 640], None),
     (2, 2, 128, 16, [1, 2, 63, 65, 129], [1, 2, 63, 65, 129], None),
     (2, 1, 128, 16, [384, 100], [2500, 1100], 700),
+    (16, 8, 128, 16, [512], [8192], None),
+    (1, 1, 128, 16, [64, 300], [3000, 300], None),
 ]
 
 
+@pytest.mark.parametrize("divide_keys", [True, False])
 @pytest.mark.parametrize("shape", TENSOR_MEMORY_ATTENTION_SHAPES)
-def test_tensor_memory_attention(shape):
-    """The tcgen05 kernel for portions of prompts against the plain reference."""
+def test_tensor_memory_attention(shape, divide_keys, monkeypatch):
+    """The tcgen05 kernel for portions of prompts against the plain reference, with and without
+    the division of a row block's keys over several blocks (which launches of few row blocks
+    over many keys get, as all of these do whose requests are 512 keys long and more)."""
     from vllm_from_scratch_b200.kernels import attention_bf16
+    if not divide_keys:
+        monkeypatch.setenv("B200_NO_TC_KEY_SPLIT", "1")
     nq, nkv, d, page, q_lens, seq_lens, window = shape
     for standout in (False, True):
         q, kp, vp, start, seq, table = _attention_case(torch.bfloat16, nq, nkv, d, page, q_lens, seq_lens,

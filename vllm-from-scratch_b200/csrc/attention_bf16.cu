@@ -159,17 +159,36 @@ B200_EXPORT int b200_prefill_attention_tc_supports(int nq, int nkv, int d, int p
                ? 1 : 0;
 }
 
+// Over how many blocks the tensor-memory kernel divides the keys of a row block for a launch of
+// num_tokens tokens of num_requests requests (1: not at all).  The caller provides
+// partial_o [rows of q * nq * splits, 128] and partial_ml [rows of q * nq * splits, 2] floats.
+B200_EXPORT int b200_prefill_attention_tc_splits(int num_tokens, int num_requests, int nq, int max_seq_len) {
+    if (getenv("B200_NO_TC_KEY_SPLIT") != nullptr) return 1;
+    const long long blocks = (long long)(num_tokens / b200::kAtBlockRows + num_requests) * nq;
+    if (blocks <= 0 || blocks * 2 > 148) return 1;                      // half the SMs busy: leave it
+    int splits = (int)(148 / blocks);
+    // Sixteen tiles of keys a block at least: 512 tokens over 512 keys took 25 us in two shares
+    // against 15 us whole, 512 over 8192 keys 75 against 156 us, 128 over 16384 keys 48 against 288.
+    const int by_keys = max_seq_len / 1024;
+    if (splits > by_keys) splits = by_keys;
+    if (splits > 8) splits = 8;
+    return splits < 2 ? 1 : splits;
+}
+
 // The tensor-memory kernel for portions of prompts.  num_pages: pages in k_pages / v_pages.
 // q and out hold num_tokens rows and query_start rows of them; the num_requests requests
 // given here begin at row token_offset (what lies ahead of it is another launch's).
 B200_EXPORT int b200_prefill_attention_tc_bf16(
     const void* q, const void* k_pages, const void* v_pages, void* out, const int* query_start,
     const int* seq_lens, const int* block_table, int num_requests, int num_tokens, int max_pages, int nq,
-    int nkv, int d, int page_size, int num_pages, float scale, int window, int token_offset,
-    cudaStream_t stream) {
+    int nkv, int d, int page_size, int num_pages, float scale, int window, int token_offset, int key_splits,
+    float* partial_o, float* partial_ml, cudaStream_t stream) {
     using namespace b200;
     if (num_requests == 0 || num_tokens - token_offset <= 0) return 0;
     if (token_offset < 0) return fail("prefill_attention_tc", "negative token offset");
+    if (key_splits < 1 || key_splits > 16) return fail("prefill_attention_tc", "key_splits out of range");
+    if (key_splits > 1 && (partial_o == nullptr || partial_ml == nullptr))
+        return fail("prefill_attention_tc", "scratch for the splits is missing");
     if (!b200_prefill_attention_tc_supports(nq, nkv, d, page_size)) return fail("prefill_attention_tc", "shape not built");
     int* error_flag = attention_error_flag();
     if (error_flag == nullptr) return fail("prefill_attention_tc", "no error flag");
@@ -183,9 +202,18 @@ B200_EXPORT int b200_prefill_attention_tc_bf16(
     if (status != cudaSuccess) return fail("prefill_attention_tc", cudaGetErrorString(status));
     const int blocks = (num_tokens - token_offset) / kAtBlockRows + num_requests;
     if (blocks > 65535) return fail("prefill_attention_tc", "too many tokens for one launch");
-    dim3 grid(nq, blocks);
+    dim3 grid(nq, blocks, key_splits);
     prefill_attention_tc_kernel<<<grid, kAtThreads, kAtSmem, stream>>>(
         *map_q, *map_k, *map_v, (__nv_bfloat16*)out, query_start, seq_lens, block_table, num_requests, max_pages,
-        nq, nkv, page_size, scale * kLog2e, window, token_offset, error_flag);
-    return check_launch("prefill_attention_tc");
+        nq, nkv, page_size, scale * kLog2e, window, token_offset, key_splits, partial_o, partial_ml, error_flag);
+    if (int rc = check_launch("prefill_attention_tc")) return rc;
+    if (key_splits > 1) {
+        const size_t first = (size_t)token_offset * nq;                 // (row of q, head) pairs ahead of this launch
+        launch_overlapped(merge_splits_kernel<kAtD>, (num_tokens - token_offset) * nq, 128, 0, stream,
+                          (const float*)(partial_o + first * key_splits * kAtD),
+                          (const float*)(partial_ml + first * key_splits * 2),
+                          (bf16*)out + first * kAtD, key_splits);
+        return check_launch("merge_splits");
+    }
+    return 0;
 }

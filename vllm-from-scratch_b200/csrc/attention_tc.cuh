@@ -175,7 +175,12 @@ __global__ void __launch_bounds__(kAtThreads, 1) prefill_attention_tc_kernel(
     const __grid_constant__ CUtensorMap map_v, __nv_bfloat16* __restrict__ out,
     const int* __restrict__ query_start, const int* __restrict__ seq_lens, const int* __restrict__ block_table,
     int num_requests, int max_pages, int nq, int nkv, int page_size, float scale_log2, int window,
-    int token_offset, int* __restrict__ error_flag) {
+    int token_offset, int key_splits, float* __restrict__ partial_o, float* __restrict__ partial_ml,
+    int* __restrict__ error_flag) {
+    // key_splits > 1 (grid.z): the block visits only its share of the row block's tiles of keys and
+    // leaves O unnormalised, its reference exponent and its sum at
+    // [(row of q * nq + head) * key_splits + blockIdx.z] of partial_o / partial_ml, for
+    // merge_splits_kernel: few row blocks over many keys would leave most SMs idle otherwise.
     // token_offset: row of q and out at which the first of these requests begins (requests ahead of
     // them in the batch are another launch's); query_start holds rows of the whole batch.
     extern __shared__ unsigned char smem_raw[];
@@ -213,7 +218,7 @@ __global__ void __launch_bounds__(kAtThreads, 1) prefill_attention_tc_kernel(
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
 
     const int first_pos = past + tile_first;
-    int k_first = window > 0 ? max(0, first_pos - window + 1) : 0;
+    int k_first = window > 0 ? max(0, first_pos - window + 1) : 0;   // (moved on to this block's share below)
     k_first = (k_first / page_size) * page_size;
     k_first = (k_first / kAtKeys) * kAtKeys;                // pages larger than a tile: start on a tile's edge too
     // Tiles of 64 keys each group visits (a group without rows visits none).
@@ -223,7 +228,17 @@ __global__ void __launch_bounds__(kAtThreads, 1) prefill_attention_tc_kernel(
         const int rows_g = min(kAtRows, rows_here - g * kAtRows);
         group_tiles[g] = rows_g > 0 ? (first_pos + g * kAtRows + rows_g - k_first + kAtKeys - 1) / kAtKeys : 0;
     }
-    const int tiles = max(group_tiles[0], group_tiles[1]);
+    int tiles = max(group_tiles[0], group_tiles[1]);
+    if (key_splits > 1) {
+        // This block's share: tiles [begin, end) of the row block.  From here on the first key and
+        // the tile counts are those of the share; nothing below knows of the others.
+        const int share = (tiles + key_splits - 1) / key_splits;
+        const int begin = min(tiles, (int)blockIdx.z * share), end = min(tiles, begin + share);
+#pragma unroll
+        for (int g = 0; g < kAtGroups; ++g) group_tiles[g] = max(0, min(group_tiles[g], end) - begin);
+        tiles = end - begin;
+        k_first += begin * kAtKeys;
+    }
     const int copy_rows = min(page_size, kAtKeys);          // rows of one tensor copy (the tensor maps' box)
     const int copies_per_tile = kAtKeys / copy_rows;
     const int table_len = (seq_len + page_size - 1) / page_size;
@@ -466,7 +481,28 @@ __global__ void __launch_bounds__(kAtThreads, 1) prefill_attention_tc_kernel(
         const float inv = row_sum > 0.0f ? 1.0f / row_sum : 0.0f;
         const int row_in_block = g * kAtRows + row;
         __nv_bfloat16* dst = out + ((size_t)(q_begin + tile_first + row_in_block) * nq + head) * kAtD;
-        if (my_tiles > 0 && ok) {
+        if (key_splits > 1) {
+            // (row_ref is -inf and row_sum 0 where the share held no tile for this group)
+            const size_t slot = ((size_t)(q_begin + tile_first + row_in_block) * nq + head) * key_splits + blockIdx.z;
+            float4* share_o = reinterpret_cast<float4*>(partial_o + slot * kAtD);
+#pragma unroll
+            for (int c = 0; c < 4; ++c) {
+                float v[32];
+                if (my_tiles > 0 && ok) tmem_ld32(tmem_o + c * 32, v);
+                else
+#pragma unroll
+                    for (int e = 0; e < 32; ++e) v[e] = 0.0f;
+                if (row_in_block < rows_here && ok) {
+#pragma unroll
+                    for (int q4 = 0; q4 < 8; ++q4)
+                        share_o[c * 8 + q4] = make_float4(v[4 * q4], v[4 * q4 + 1], v[4 * q4 + 2], v[4 * q4 + 3]);
+                }
+            }
+            if (row_in_block < rows_here && ok) {
+                partial_ml[slot * 2] = row_ref;
+                partial_ml[slot * 2 + 1] = row_sum;
+            }
+        } else if (my_tiles > 0 && ok) {
 #pragma unroll
             for (int c = 0; c < 4; ++c) {
                 float v[32];

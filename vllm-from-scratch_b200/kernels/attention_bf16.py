@@ -63,7 +63,7 @@ def _decode(lib, q, k_pages, v_pages, out, seq_lens, block_table, num_q_heads, n
 
 
 def _portions(lib, q, k_pages, v_pages, out, query_start, seq_lens, block_table, num_q_heads, num_kv_heads,
-              head_dim, page_size, scale, window, max_query_len, token_offset) -> int:
+              head_dim, page_size, scale, window, max_query_len, max_seq_len, token_offset) -> int:
     """Portions of prompts (any number of tokens per request).  ``q`` and ``out`` are the whole
     batch's, ``query_start`` holds rows of them; the requests given begin at ``token_offset``."""
     from . import _stream
@@ -71,12 +71,20 @@ def _portions(lib, q, k_pages, v_pages, out, query_start, seq_lens, block_table,
     tokens = q.shape[0]
     if (max_query_len >= TC_MIN_QUERY_LEN and os.environ.get("B200_NO_TC_ATTENTION") is None
             and lib.b200_prefill_attention_tc_supports(num_q_heads, num_kv_heads, head_dim, page_size)):
-        # long portions of prompts: the tcgen05 / tensor-memory kernel
+        # long portions of prompts: the tcgen05 / tensor-memory kernel; few row blocks over many
+        # keys are divided over several blocks each, with partial results that a second kernel merges
+        splits = lib.b200_prefill_attention_tc_splits(_I(tokens - token_offset), _I(requests), _I(num_q_heads),
+                                                      _I(max_seq_len))
+        partial_o = partial_ml = None
+        if splits > 1:
+            partial_o = torch.empty((tokens * num_q_heads * splits, head_dim), dtype=torch.float32, device=q.device)
+            partial_ml = torch.empty((tokens * num_q_heads * splits, 2), dtype=torch.float32, device=q.device)
         return lib.b200_prefill_attention_tc_bf16(
             _P(q.data_ptr()), _P(k_pages.data_ptr()), _P(v_pages.data_ptr()), _P(out.data_ptr()),
             _P(query_start.data_ptr()), _P(seq_lens.data_ptr()), _P(block_table.data_ptr()), _I(requests),
             _I(tokens), _I(block_table.shape[1]), _I(num_q_heads), _I(num_kv_heads), _I(head_dim),
-            _I(page_size), _I(k_pages.shape[0]), _F(scale), _I(window or 0), _I(token_offset), _stream())
+            _I(page_size), _I(k_pages.shape[0]), _F(scale), _I(window or 0), _I(token_offset), _I(splits),
+            _P(partial_o.data_ptr() if splits > 1 else 0), _P(partial_ml.data_ptr() if splits > 1 else 0), _stream())
     return lib.b200_prefill_attention_bf16(
         _P(q.data_ptr()), _P(k_pages.data_ptr()), _P(v_pages.data_ptr()), _P(out.data_ptr()),
         _P(query_start.data_ptr()), _P(seq_lens.data_ptr()), _P(block_table.data_ptr()), _I(requests),
@@ -108,12 +116,12 @@ def paged_attention_bf16(q, k_pages, v_pages, out, query_start, seq_lens, block_
             count_launch()
         if status == 0:
             status = _portions(lib, q, k_pages, v_pages, out, query_start[n:], seq_lens[n:], block_table[n:],
-                               *shape, max_query_len, n)
+                               *shape, max_query_len, max_seq_len, n)
     elif decode_done:
         raise KernelError("paged_attention: decode_done without a split of the batch")
     else:
         status = _portions(lib, q, k_pages, v_pages, out, query_start, seq_lens, block_table, *shape,
-                           max_query_len, 0)
+                           max_query_len, max_seq_len, 0)
     if status != 0:
         raise KernelError(lib.b200_last_error().decode())
     count_launch()
