@@ -467,7 +467,6 @@ def test_fused_decode_attention(shape):
     # reference given the pages after the store.
     assert torch.equal(out_a[:-1], out_b[:-1])
     kp_c, vp_c = kp_a.clone(), vp_a.clone()
-    last_page, last_offset = int(page_of[-1]), int((seq[-1] - 1) % page)
     q_c = torch.empty_like(q)
     all_slots = (page_of * page + (seq - 1) % page).to(torch.int32)
     k.head_norm_rope_cache(qkv, positions, all_slots, q_w, k_w, inv_freq, d, 1e-6, q_c, kp_c, vp_c, nq, nkv, d, page)
