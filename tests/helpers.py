@@ -76,7 +76,15 @@ def cut_changing_portions(lengths: dict[str, int], seed: int = 0) -> list[list[t
     return steps
 
 
-def cut_mixed(lengths: dict[str, int], seed: int = 0, live: int = 4) -> list[list[tuple[str, int]]]:
+SMALL_PORTIONS = (2, 3, 5, 8, 13, 16, 21, 33)
+# With portions of 64 tokens and more a bfloat16 step at head size 128 reaches the tcgen05 kernel
+# (at a row offset, behind the single tokens that went to the decode kernel), 300 and more its
+# second row block.
+LARGE_PORTIONS = (2, 3, 5, 8, 13, 16, 21, 33, 64, 100, 130, 300)
+
+
+def cut_mixed(lengths: dict[str, int], seed: int = 0, live: int = 4, sizes=SMALL_PORTIONS
+              ) -> list[list[tuple[str, int]]]:
     """Up to ``live`` requests at a time; each step takes a portion of some and a
     single token of others, leaves some out, and lets new requests in when one ends."""
     rng = random.Random(seed)
@@ -96,7 +104,7 @@ def cut_mixed(lengths: dict[str, int], seed: int = 0, live: int = 4) -> list[lis
             if choice < 0.6:
                 size = 1
             else:
-                size = rng.choice([2, 3, 5, 8, 13, 16, 21, 33])
+                size = rng.choice(sizes)
             size = min(size, left)
             step.append((rid, size))
             running[rid] = left - size
@@ -107,23 +115,27 @@ def cut_mixed(lengths: dict[str, int], seed: int = 0, live: int = 4) -> list[lis
     return steps
 
 
-def run_schedule(runner, sequences: dict[str, list[int]], steps, want_all: bool = True
-                 ) -> dict[str, torch.Tensor]:
+def run_schedule(runner, sequences: dict[str, list[int]], steps, want_all: bool = True, on_device: bool = False,
+                 step=None) -> dict[str, torch.Tensor]:
     """Drive a ``ModelRunner`` through ``steps``; returns the logits of every
-    position of every request, [length, vocab] on the CPU."""
+    position of every request, [length, vocab] on the CPU (``on_device``: where they
+    were computed).  ``step``: the function that runs a list of entries (default: the
+    runner's step function; a graph cache's ``run`` takes the same list)."""
+    step_fn = step or runner.step
     from vllm_from_scratch_b200 import StepEntry
     done = {rid: 0 for rid in sequences}
     rows: dict[str, list[torch.Tensor]] = {rid: [] for rid in sequences}
-    for step in steps:
+    for planned in steps:
         entries = []
-        for rid, n in step:
+        for rid, n in planned:
             if not runner.manager.is_admitted(rid):
                 runner.manager.admit(rid)
             start = done[rid]
             assert runner.manager.allocate(rid, start + n), f"no pages for {rid} at {start + n}"
             entries.append(StepEntry(rid, sequences[rid][start:start + n], start,
                                      list(range(n)) if want_all else [n - 1]))
-        logits = runner.step(entries).cpu()
+        logits = step_fn(entries)
+        logits = logits.clone() if on_device else logits.cpu()
         at = 0
         for entry in entries:
             count = len(entry.want)

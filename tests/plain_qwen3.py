@@ -5,8 +5,9 @@ inside tutu04538/vllm-from-scratch); it shares no code with the engine.  It was
 compared once with the reference's own ``Qwen3ForCausalLM`` on the CPU for two
 tiny random models; the script and its small outputs are in ``tests/golden/``.
 
-Everything is computed in the dtype of the weights handed in (float32 or
-float64), never lower.
+Everything is computed in the dtype asked for (float32 or float64), never lower,
+on the device the weights are on (the CPU for the tiny models; a CUDA device, with
+its reduced-precision matrix modes switched off by the caller, for wide ones).
 """
 
 from __future__ import annotations
@@ -54,7 +55,7 @@ def rms_norm(x: torch.Tensor, weight: torch.Tensor, eps: float) -> torch.Tensor:
 def rope_cos_sin(positions: torch.Tensor, rotary_dim: int, theta: float, dtype: torch.dtype):
     """minivllm/layers/rotary_embedding.py:143-185: inv_freq_j = theta^(-2j/rotary_dim)
     built in float32, angle = position * inv_freq_j."""
-    inv_freq = 1.0 / (theta ** (torch.arange(0, rotary_dim, 2, dtype=torch.float32) / rotary_dim))
+    inv_freq = (1.0 / (theta ** (torch.arange(0, rotary_dim, 2, dtype=torch.float32) / rotary_dim))).to(positions.device)
     if dtype == torch.float64:   # a finer oracle: the same float32 frequencies, exact product
         angles = positions.to(torch.float64)[:, None] * inv_freq.to(torch.float64)[None, :]
     else:
@@ -83,8 +84,8 @@ def causal_attention(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, scale: f
     k = k.repeat_interleave(group, dim=1)
     v = v.repeat_interleave(group, dim=1)
     scores = torch.einsum("ihd,jhd->hij", q, k) * scale
-    i = torch.arange(seq)[:, None]
-    j = torch.arange(seq)[None, :]
+    i = torch.arange(seq, device=q.device)[:, None]
+    j = torch.arange(seq, device=q.device)[None, :]
     visible = j <= i
     if window is not None:
         visible = visible & (j > i - window)
@@ -121,7 +122,7 @@ def feed_forward(x: torch.Tensor, w: dict, prefix: str) -> torch.Tensor:
 def qwen3_hidden(cfg: dict, w: dict, tokens: torch.Tensor) -> torch.Tensor:
     """minivllm/models/qwen3.py:308-338 in its net effect: h += attn(norm(h));
     h += mlp(norm(h)) per layer, then the final norm."""
-    positions = torch.arange(tokens.shape[0])
+    positions = torch.arange(tokens.shape[0], device=tokens.device)
     h = w["model.embed_tokens.weight"][tokens]
     for layer in range(cfg["layers"]):
         prefix = f"model.layers.{layer}."
@@ -138,7 +139,7 @@ def qwen3_logits(raw_config: dict, weights: dict, tokens, dtype: torch.dtype = t
     (minivllm/models/qwen3.py:393-395; tied head :372-376)."""
     cfg = read_config(raw_config)
     w = {name: tensor.to(dtype) for name, tensor in weights.items()}
-    tokens = torch.as_tensor(tokens, dtype=torch.long)
+    tokens = torch.as_tensor(tokens, dtype=torch.long).to(w["model.embed_tokens.weight"].device)
     hidden = qwen3_hidden(cfg, w, tokens)
     head = w["model.embed_tokens.weight"] if cfg["tied"] else w["lm_head.weight"]
     return hidden @ head.T

@@ -65,7 +65,8 @@ def test_registry():
     spec = entry.build_spec(config)
     assert len(spec.layers) == 2 and [e.layer for e in spec.schedule] == [0, 1]
     assert spec.layers[1].mixer.params["num_kv_heads"] == 2
-    assert spec.layers[0].mixer_norm.params["eps"] == 1e-6
+    assert spec.layers[0].norms["mixer"].params["eps"] == 1e-6
+    assert set(spec.layers[0].norms) == {"mixer", "feed_forward"}
 
 
 def _model(raw, dtype=torch.float32):
@@ -90,7 +91,7 @@ def test_random_weights_folder_loads(tmp_path):
         assert attention.q_norm.dtype == torch.float32            # vectors stay 32-bit
         feed_forward = model.layers[1].feed_forward
         assert torch.equal(feed_forward.gate_up[160:].float(), stored["model.layers.1.mlp.up_proj.weight"].float())
-        assert model.output_weight is not model.embedding
+        assert model.output_head.weight is not model.embedding.weight
 
 
 def test_tied_model_ignores_a_stored_head(tmp_path):
@@ -101,7 +102,7 @@ def test_tied_model_ignores_a_stored_head(tmp_path):
     save_file(tensors, str(folder / "model.safetensors"))
     model = _model(tiny_configs.TINY_A)
     engine.load_weights(model, folder)
-    assert model.output_weight is model.embedding
+    assert model.output_head.weight is model.embedding.weight
 
 
 def test_one_error_lists_every_mismatch(tmp_path):
@@ -148,7 +149,7 @@ def test_sharded_checkpoint(tmp_path):
     (folder / "model.safetensors.index.json").write_text(json.dumps({"weight_map": weight_map}))
     model = _model(tiny_configs.TINY_A)
     engine.load_weights(model, folder)
-    assert torch.equal(model.embedding, tensors["model.embed_tokens.weight"])
+    assert torch.equal(model.embedding.weight, tensors["model.embed_tokens.weight"])
 
 
 def test_engine_refuses_to_run_without_a_gpu_kernel():

@@ -120,6 +120,37 @@ def test_a_kernel_error_flag_stops_the_engine(folders, monkeypatch):
         llm.engine.step()
 
 
+def test_error_words_come_with_every_sampling_step(folders, monkeypatch):
+    """The kernels' error words travel with the sampled ids of every step: a step in which a
+    kernel gave up is refused before its tokens are committed or handed out, not steps later."""
+    import vllm_from_scratch_b200.kernels as kernels
+    llm = engine.LLM(folders["A"], dtype="float32", device="cpu", enforce_eager=True, max_model_len=64)
+    core = llm.engine
+    core._carry_status = True
+    words = [0, 0, 0]
+    monkeypatch.setattr(kernels, "collect_status",
+                        lambda flag, out: out.copy_(torch.tensor(words, dtype=torch.int32)))
+    core.add_request("r", [1, 2, 3], engine.SamplingParams(temperature=0.0, max_tokens=8))
+    first = core.step()
+    assert len(first) == 1 and len(first[0].token_ids) == 1
+    words[1] = 25                                            # from now on: an attention kernel gave up
+    with pytest.raises(RuntimeError, match=r"the step is void: attention kernel gave up waiting \(code 25\)"):
+        core.step()
+    assert len(core.scheduler.requests["r"].output_token_ids) == 1, "nothing of the void step was committed"
+    with pytest.raises(engine.EngineDeadError):
+        core.step()
+    assert kernels.status_problem([4, 0, 41], 256) == (
+        "token id outside the vocabulary [0, 256) at batch row 3; matrix-product kernel gave up waiting (code 41)")
+    assert kernels.status_problem([0, 0, 0]) is None
+
+
+def test_max_model_len_beyond_the_trained_positions_is_refused(folders):
+    """minivllm/worker/worker.py:140: max_position_embeddings < max_model_len is an error."""
+    with pytest.raises(ValueError, match="max_position_embeddings=128"):
+        engine.LLM(folders["A"], dtype="float32", device="cpu", enforce_eager=True, max_model_len=129)
+    engine.LLM(folders["A"], dtype="float32", device="cpu", enforce_eager=True, max_model_len=128)
+
+
 def test_packing_with_empty_requests_and_repeated_wanted_rows(folders):
     """Shapes fixed in advance: requests without tokens after the real ones, wanted rows
     filled up with row 0; nothing about the real requests changes.  The request that brings

@@ -18,6 +18,7 @@ def folders(tmp_path_factory):
     return {"A": helpers.make_model_folder(base, tiny_configs.TINY_A, seed=11),
             "B": helpers.make_model_folder(base, tiny_configs.TINY_B, seed=12),
             "C": helpers.make_model_folder(base, tiny_configs.TINY_C, seed=13),
+            "D": helpers.make_model_folder(base, tiny_configs.TINY_D, seed=14),
             "E": helpers.make_model_folder(base, tiny_configs.TINY_E, seed=15)}
 
 
@@ -60,6 +61,75 @@ def test_greedy_generation_matches_plain(folders, name, lengths, page, eager):
         assert llm.engine.decode_graphs.replays > 0, "decode steps must go through the captured graphs"
     llm.engine.runner.manager.check_invariants()
     assert llm.engine.runner.manager.stats()["requests"] == 0
+
+
+@pytest.mark.parametrize("eager", [True, False])
+@pytest.mark.parametrize("name,page", [("D", 16), ("E", 16), ("E", 48)])
+def test_bfloat16_greedy_generation_matches_plain(folders, name, page, eager):
+    """bfloat16 through the entry point at head sizes 64 and 128 (the tensor-core attention
+    kernels, the few-rows products, for 128 the decode kernel that also rotates and stores and
+    the tcgen05 kernel for the prompts), with and without graphs, against the plain model with
+    weights rounded to bfloat16.  A token may differ only where the plain model's two best
+    logits lie closer than the rounding of bfloat16 activations can move them."""
+    import vllm_from_scratch_b200 as engine
+    raw = getattr(tiny_configs, f"TINY_{name}")
+    lengths = [5, 70, 33, 1, 150, 64]
+    prompts = [helpers.random_tokens(raw["vocab_size"], n, seed=150 + i) for i, n in enumerate(lengths)]
+    llm = engine.LLM(folders[name], dtype="bfloat16", max_model_len=256, block_size=page,
+                     max_num_seqs=4, max_num_batched_tokens=96, enforce_eager=eager)
+    outputs = llm.generate(prompts, engine.SamplingParams(temperature=0.0, max_tokens=12))
+    same = 0
+    for prompt, output in zip(prompts, outputs):
+        tokens, flipped = list(prompt), False
+        for place, got in enumerate(output.token_ids):
+            logits = helpers.plain_logits(folders[name], tokens, round_weights_to=torch.bfloat16)[-1]
+            top = torch.topk(logits, 2)
+            if got != int(top.indices[0]):
+                margin = float(top.values[0] - top.values[1])
+                assert margin < 2 * 0.03 * float(logits.abs().max()), (
+                    f"{name} prompt of {len(prompt)}: token {place} is {got}, plain says {int(top.indices[0])} "
+                    f"(margin {margin:.3e})")
+                flipped = True
+                break
+            tokens.append(got)
+        same += not flipped
+    assert same >= len(prompts) - 2, "most requests must generate the plain model's tokens throughout"
+    if not eager:
+        assert llm.engine.decode_graphs.replays > 0
+    llm.engine.runner.manager.check_invariants()
+    assert llm.engine.runner.manager.stats()["requests"] == 0
+
+
+def test_demo_command_line_prints_the_tokens_of_the_entry_point(tmp_path, capsys):
+    """The command line (``demo.main``) with ``--random-weights`` in both precisions: the tokens
+    it prints are those ``LLM.generate`` gives for the same model folder, prompts and options."""
+    import json
+    import re
+    import vllm_from_scratch_b200 as engine
+    from vllm_from_scratch_b200 import demo
+    config_file = tmp_path / "tiny_b.json"
+    config_file.write_text(json.dumps(tiny_configs.TINY_B))
+    questions = ["1 2 3 4 5 6 7 8 9", "11, 12, 13", " ".join(str(7 * i % 503) for i in range(40))]
+    for dtype in ("float32", "bfloat16"):
+        code = demo.main([*questions, "--random-weights", str(config_file), "--random-seed", "4", "--dtype", dtype,
+                          "--max-model-len", "128", "--max-new-tokens", "9", "--block-size", "8",
+                          "--num-kv-blocks", "48", "--max-num-seqs", "2", "--max-num-batched-tokens", "32",
+                          "--trace", "--scheduler-trace"])
+        assert code == 0
+        printed = capsys.readouterr().out
+        answers = {int(m.group(1)): json.loads(m.group(2)) for m in re.finditer(r"answer\[q(\d+)\]: (\[.*\])", printed)}
+        assert sorted(answers) == [0, 1, 2] and all(len(a) == 9 for a in answers.values())
+        assert "finish reason LENGTH" in printed and "first step (num_scheduled_tokens=" in printed
+        assert "Qwen3ForCausalLM" in printed and "prefix caching: on" in printed
+        folder = engine.write_random_model(tiny_configs.TINY_B, 4, tmp_path / f"model_{dtype}",
+                                           dtype=torch.bfloat16 if dtype == "bfloat16" else torch.float32)
+        llm = engine.LLM(folder, dtype=dtype, max_model_len=128, block_size=8, num_gpu_blocks=48, max_num_seqs=2,
+                         max_num_batched_tokens=32, enable_prefix_caching=True)
+        prompts = [demo.parse_prompt(q) for q in questions]
+        expected = llm.generate(prompts, engine.SamplingParams(temperature=0.0, max_tokens=9))
+        assert [answers[i] for i in range(3)] == [out.token_ids for out in expected], dtype
+    with pytest.raises(SystemExit, match="not a list of token ids"):
+        demo.parse_prompt("hello there")
 
 
 def test_small_pool_preempts_and_gives_the_same_tokens(folders):
@@ -258,8 +328,8 @@ def test_every_engine_setting_gives_the_same_tokens(folders, name):
         params = [engine.SamplingParams(temperature=0.0 if i % 2 == 0 else 0.8, seed=i, top_k=0 if i % 4 else 20,
                                         max_tokens=rng.choice([1, 5, 20, 40])) for i in range(10)]
         arrivals = sorted(rng.randrange(0, 30) for _ in prompts)
-        llm = engine.LLM(folders[name], dtype="float32", max_model_len=160, block_size=8, max_num_seqs=4,
-                         max_num_batched_tokens=32, enforce_eager=eager, async_scheduling=ahead,
+        llm = engine.LLM(folders[name], dtype="float32", max_model_len=min(160, raw["max_position_embeddings"]),
+                         block_size=8, max_num_seqs=4, max_num_batched_tokens=32, enforce_eager=eager, async_scheduling=ahead,
                          enable_prefix_caching=prefix, num_gpu_blocks=blocks)
         core, latest, step, added = llm.engine, {}, 0, 0
         while added < len(prompts) or core.has_unfinished_requests():
@@ -296,15 +366,13 @@ def test_decode_attention_in_one_kernel_gives_the_same_tokens(folders, eager, mo
     the windowed layer come back and are used again."""
     import vllm_from_scratch_b200 as engine
     from vllm_from_scratch_b200 import kernels
+    from vllm_from_scratch_b200.kernels import attention_bf16
     raw = tiny_configs.TINY_E
     prompts = [helpers.random_tokens(raw["vocab_size"], n, seed=70 + i) for i, n in enumerate([3, 60, 17, 130, 64])]
     params = engine.SamplingParams(temperature=0.0, max_tokens=70)
     results, launches = {}, {}
     for fused in (True, False):
-        if fused:
-            monkeypatch.delenv("B200_NO_FUSED_DECODE", raising=False)
-        else:
-            monkeypatch.setenv("B200_NO_FUSED_DECODE", "1")
+        monkeypatch.setattr(attention_bf16, "USE_FUSED_DECODE", fused)
         llm = engine.LLM(folders["E"], dtype="bfloat16", max_model_len=256, block_size=16, max_num_seqs=4,
                          max_num_batched_tokens=64, enforce_eager=eager)
         before = kernels.launch_count

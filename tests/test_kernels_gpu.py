@@ -243,6 +243,11 @@ TENSOR_CORE_SHAPES = [
     (8, 2, 64, 16, [130, 70], [130, 1000], None),
     (6, 3, 128, 16, [300], [1500], 256),
     (2, 1, 256, 8, [65, 1], [65, 90], None),
+    # pages whose size is no power of two: the decode kernel with per-thread copies and the general one
+    (16, 8, 128, 24, [1, 1, 1], [700, 23, 2900], None),
+    (8, 2, 64, 48, [1, 1], [49, 1500], 300),
+    (8, 4, 128, 48, [130, 1, 70], [130, 500, 1000], None),
+    (4, 2, 64, 24, [200, 3], [333, 75], 100),
 ]
 
 
@@ -323,63 +328,6 @@ def test_gated_silu_gemm(m, inter, k_, dtype):
         fused = torch.empty_like(out_a)
         gemm_bf16._skinny(x, w, fused, inter)
         assert float((fused.float() - out_b.float()).abs().max()) <= bound
-
-
-@pytest.mark.parametrize("m,n,k_", [(1, 256, 128), (8, 4096, 2048), (16, 2048, 6144), (17, 1000, 264), (64, 12288, 2048),
-                                    (100, 503, 96), (256, 384, 512), (5, 151936, 256), (24, 2048, 2048),
-                                    (128, 4096, 2048), (33, 2050, 6144)])
-@pytest.mark.parametrize("out_dtype", [torch.bfloat16, torch.float32])
-def test_tensor_memory_gemm(m, n, k_, out_dtype):
-    """The tcgen05 / TMA kernel against a float64 product; no bounded wait may run out."""
-    from vllm_from_scratch_b200.kernels import gemm_bf16
-    g = torch.Generator(device="cuda").manual_seed(m + n + k_)
-    x = torch.randn(m, k_, device="cuda", generator=g).bfloat16()
-    w = torch.randn(n, k_, device="cuda", generator=g).bfloat16()
-    out = torch.full((m, n), 7.0, device="cuda", dtype=out_dtype)
-    for _ in range(2):                               # twice: nothing may be left over from a launch
-        gemm_bf16.tc_gemm_bf16(x, w, out)
-    assert gemm_bf16.device_error_code() == 0
-    exact = x.double() @ w.double().T
-    scale = float(exact.abs().max())
-    bound = scale * (2 ** -8 if out_dtype == torch.bfloat16 else 1e-5)
-    assert float((out.double() - exact).abs().max()) <= bound
-
-
-@pytest.mark.parametrize("m,inter,k_", [(1, 256, 128), (8, 6144, 2048), (33, 1000, 320), (64, 1536, 1024),
-                                        (64, 6144, 2048), (128, 3001, 512)])
-def test_tensor_memory_gated_gemm(m, inter, k_):
-    from vllm_from_scratch_b200.kernels import gemm_bf16
-    g = torch.Generator(device="cuda").manual_seed(m + inter)
-    x = torch.randn(m, k_, device="cuda", generator=g).bfloat16()
-    w = (torch.randn(2 * inter, k_, device="cuda", generator=g) * 0.1).bfloat16()
-    out = torch.empty(m, inter, device="cuda", dtype=torch.bfloat16)
-    expected = torch.empty_like(out)
-    gemm_bf16.tc_gemm_bf16(x, w, out, gated=True)
-    assert gemm_bf16.device_error_code() == 0
-    plain_ops.gated_silu_gemm(x, w, expected)
-    bound = float(expected.float().abs().max()) * 2 ** -7
-    assert float((out.float() - expected.float()).abs().max()) <= bound
-
-
-def test_tensor_memory_gemm_by_switch(monkeypatch):
-    """With B200_TC_GEMM_ROWS the engine's products of 17 rows and more go to the tcgen05 kernel."""
-    from vllm_from_scratch_b200.kernels import gemm_bf16
-    k = kernels()
-    g = torch.Generator(device="cuda").manual_seed(5)
-    x = torch.randn(40, 512, device="cuda", generator=g).bfloat16()
-    w = (torch.randn(2 * 384, 512, device="cuda", generator=g) * 0.1).bfloat16()
-    plain, gated = torch.empty(40, 768, device="cuda", dtype=torch.bfloat16), torch.empty(40, 384, device="cuda", dtype=torch.bfloat16)
-    expected_plain, expected_gated = torch.empty_like(plain), torch.empty_like(gated)
-    plain_ops.gemm(x, w, expected_plain)
-    plain_ops.gated_silu_gemm(x, w, expected_gated)
-    monkeypatch.setenv("B200_TC_GEMM_ROWS", "128")
-    before = k.launch_count
-    k.gemm(x, w, plain)
-    k.gated_silu_gemm(x, w, gated)
-    assert k.launch_count == before + 2              # one kernel each: no separate activation
-    assert gemm_bf16.device_error_code() == 0
-    for got, want in ((plain, expected_plain), (gated, expected_gated)):
-        assert float((got.float() - want.float()).abs().max()) <= float(want.float().abs().max()) * 2 ** -7
 
 
 SPLIT_BATCH_SHAPES = [
@@ -498,8 +446,7 @@ def test_tensor_memory_attention(shape, divide_keys, monkeypatch):
     the division of a row block's keys over several blocks (which launches of few row blocks
     over many keys get, as all of these do whose requests are 512 keys long and more)."""
     from vllm_from_scratch_b200.kernels import attention_bf16
-    if not divide_keys:
-        monkeypatch.setenv("B200_NO_TC_KEY_SPLIT", "1")
+    monkeypatch.setattr(attention_bf16, "USE_TC_KEY_SPLIT", divide_keys)
     nq, nkv, d, page, q_lens, seq_lens, window = shape
     for standout in (False, True):
         q, kp, vp, start, seq, table = _attention_case(torch.bfloat16, nq, nkv, d, page, q_lens, seq_lens,
@@ -511,3 +458,36 @@ def test_tensor_memory_attention(shape, divide_keys, monkeypatch):
         assert attention_bf16.attention_error_code() == 0
         plain_ops.paged_attention(q, kp, vp, out_b, *args)
         close(out_a, out_b, torch.bfloat16, scale=2, what=f"tensor-memory attention standout={standout}")
+
+
+def test_tensor_map_cache_keeps_copies_valid():
+    """The cache of tensor maps empties itself when it is full; a launcher that has taken one map
+    and then asks for another must not be left with a dangling one.  Host-only: more maps than
+    the cache holds are encoded over one buffer, nothing is launched."""
+    from vllm_from_scratch_b200.kernels import attention_bf16
+    assert attention_bf16.tensor_map_cache_self_check(5000) == 0
+    assert attention_bf16.tensor_map_cache_self_check(9000) == 0
+
+
+def test_sm_count_comes_from_the_device():
+    from vllm_from_scratch_b200.kernels import attention_bf16
+    assert attention_bf16.sm_count() == torch.cuda.get_device_properties(0).multi_processor_count
+
+
+def test_status_words_are_collected_without_a_wait():
+    """The words a step carries to the host beside its sampled ids: the token-id flag of the
+    embedding kernel and the error words of the libraries that are loaded."""
+    k = kernels()
+    table = torch.randn(50, 32, device="cuda")
+    out = torch.empty(3, 32, device="cuda")
+    flag = torch.zeros(1, dtype=torch.int32, device="cuda")
+    words = torch.full((k.STATUS_WORDS,), -1, dtype=torch.int32, device="cuda")
+    k.embedding(table, torch.tensor([1, 2, 3], dtype=torch.int32, device="cuda"), out, flag)
+    k.collect_status(flag, words)
+    assert words.tolist() == [0, 0, 0] and k.status_problem(words.tolist()) is None
+    k.embedding(table, torch.tensor([1, 50, 3], dtype=torch.int32, device="cuda"), out, flag)
+    k.collect_status(flag, words)
+    assert words.tolist() == [2, 0, 0]
+    assert "batch row 1" in k.status_problem(words.tolist(), 50)
+    k.collect_status(None, words)
+    assert words.tolist() == [0, 0, 0]

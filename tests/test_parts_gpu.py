@@ -140,10 +140,10 @@ def small_spec(schedule, layers=2, hidden=64, vocab=97):
         name=f"model.layers.{i}", block=PartSpec("pre_norm"),
         mixer=PartSpec("paged_attention", {"num_heads": 4, "num_kv_heads": 2, "head_dim": 16,
                                            "window": None, "qk_norm_eps": 1e-6}, name="self_attn"),
-        mixer_norm=PartSpec("rms_norm", norm, name="input_layernorm"),
         feed_forward=PartSpec("gated_silu", {"intermediate_size": 72}, name="mlp"),
-        feed_forward_norm=PartSpec("rms_norm", norm, name="post_attention_layernorm"),
-        position=PartSpec("rotary", {"theta": 1e4, "rotary_dim": 16})) for i in range(layers)]
+        position=PartSpec("rotary", {"theta": 1e4, "rotary_dim": 16}),
+        norms={"mixer": PartSpec("rms_norm", norm, name="input_layernorm"),
+               "feed_forward": PartSpec("rms_norm", norm, name="post_attention_layernorm")}) for i in range(layers)]
     return ModelSpec(hidden_size=hidden, vocab_size=vocab, embedding=PartSpec("token_embedding", name="model.embed_tokens"),
                      layers=tuple(specs), schedule=tuple(ScheduleEntry(*entry) for entry in schedule),
                      final_norm=PartSpec("rms_norm", norm, name="model.norm"),
@@ -364,3 +364,257 @@ def test_toy_routed_feed_forward_and_toy_frequencies_register_build_and_step():
     finally:
         FEED_FORWARDS.unregister("toy_top_one_experts")
         POSITION_ENCODINGS.unregister("toy_band_frequencies")
+
+
+# ---------------------------------------------- what the engine does with parts it does not know
+def _plain_attention_layer(weights, h, layer, cfg):
+    p = f"model.layers.{layer}."
+    w = {"a." + k[len(p + "self_attn."):]: v for k, v in weights.items() if k.startswith(p + "self_attn.")}
+    h = h + plain_attention(plain_qwen3.rms_norm(h, weights[p + "input_layernorm.weight"], 1e-6), w, cfg, None)
+    return h + plain_qwen3.feed_forward(
+        plain_qwen3.rms_norm(h, weights[p + "post_attention_layernorm.weight"], 1e-6), weights, p + "mlp.")
+
+
+def _greedy_by(plain, prompt, new_tokens):
+    tokens, margins = list(prompt), []
+    for _ in range(new_tokens):
+        logits = plain(tokens)[-1]
+        top = torch.topk(logits, 2).values
+        margins.append(float(top[0] - top[1]))
+        tokens.append(int(logits.argmax()))
+    return tokens[len(prompt):], margins
+
+
+@pytest.mark.parametrize("device_path", [False, True])
+def test_state_mixer_through_the_engine_with_graphs_asked_for(device_path):
+    """The toy mixer with state of its own, driven by ``LLMEngine`` with graph replay asked for.
+    Written with host lists (``ctx.host_state_slots``) it does not say ``graph_safe``: the engine
+    must then run without graphs rather than bake one step's slots into a graph.  Written so
+    that a decode step reads its slots from device data, and saying so, it is replayed.  Either
+    way the greedy tokens are the plain model's."""
+    import dataclasses
+    import vllm_from_scratch_b200 as engine
+    from vllm_from_scratch_b200 import ModelRunner, PartSpec
+    from vllm_from_scratch_b200.parts import MIXERS, DecoderModel, Mixer, StateNeed, WeightInfo
+
+    class RunningSum(Mixer):
+        graph_safe = device_path
+
+        def __init__(self, params, env, position):
+            super().__init__(params, env, position)
+            self.decay, self.weight = float(params["decay"]), None
+
+        def expected_weights(self):
+            return {"mix.weight": WeightInfo((self.env.hidden_size, self.env.hidden_size))}
+
+        def load_weights(self, tensors):
+            self.weight = tensors["mix.weight"]
+
+        def cache_need(self):
+            return StateNeed((self.env.hidden_size,), torch.float32)
+
+        def forward(self, x, ctx, cache):
+            if device_path and ctx.max_query_len == 1 and x.shape[0] == ctx.num_requests:
+                # one token per request: the slots come from the device, nothing from the host
+                slots = ctx.state_slots.long()
+                state = self.decay * cache.state[slots] + x.float()
+                cache.state[slots] = state
+                return (state @ self.weight.float().T).to(x.dtype)
+            out = torch.empty_like(x)
+            starts = ctx.host_query_start
+            for row, slot in enumerate(ctx.host_state_slots):
+                state = cache.state[slot]
+                for t in range(starts[row], starts[row + 1]):
+                    state = self.decay * state + x[t].float()
+                    out[t] = (state @ self.weight.float().T).to(x.dtype)
+                cache.state[slot] = state
+            return out
+
+    kind = f"toy_running_sum_{int(device_path)}"
+    MIXERS.register(kind)(RunningSum)
+    try:
+        base = small_spec([(0, None), (1, None)])
+        toy_layer = dataclasses.replace(base.layers[1], mixer=PartSpec(kind, {"decay": 0.6}, name="toy"),
+                                        position=PartSpec("none"))
+        spec = dataclasses.replace(base, layers=(base.layers[0], toy_layer))
+        weights = random_weights_for(DecoderModel(spec, torch.float32, "cpu"), seed=5)
+        cfg = {"heads": 4, "kv_heads": 2, "head_dim": 16, "eps": 1e-6, "theta": 1e4}
+
+        def plain(tokens):
+            h = _plain_attention_layer(weights, weights["model.embed_tokens.weight"][torch.tensor(tokens)], 0, cfg)
+            p = "model.layers.1."
+            normed = plain_qwen3.rms_norm(h, weights[p + "input_layernorm.weight"], 1e-6)
+            state, mixed = torch.zeros(64), []
+            for t in range(len(tokens)):
+                state = 0.6 * state + normed[t]
+                mixed.append(state @ weights[p + "toy.mix.weight"].T)
+            h = h + torch.stack(mixed)
+            h = h + plain_qwen3.feed_forward(plain_qwen3.rms_norm(h, weights[p + "post_attention_layernorm.weight"], 1e-6), weights, p + "mlp.")
+            return plain_qwen3.rms_norm(h, weights["model.norm.weight"], 1e-6) @ weights["model.embed_tokens.weight"].T
+
+        runner = ModelRunner(spec, weights, "float32", 8, 48, 3, device="cuda")
+        llm = engine.LLMEngine(engine.EngineConfig(
+            engine.ModelConfig("(toy)", "float32", 96), engine.CacheConfig(8, 48),
+            engine.SchedulerConfig(3, 32)), runner=runner)
+        if device_path:
+            assert llm.decode_graphs is not None and llm.mixed_graphs is None and not llm.graphs_refused_by_parts
+        else:
+            assert llm.decode_graphs is None and llm.graphs_refused_by_parts
+        # five requests for three slots: slots are used again, by requests that join while others decode
+        prompts = [helpers.random_tokens(97, n, seed=40 + n) for n in (9, 20, 3, 14, 6)]
+        params = engine.SamplingParams(temperature=0.0, max_tokens=10, ignore_eos=True)
+        for index, prompt in enumerate(prompts):
+            llm.add_request(f"t{index}", prompt, params)
+        latest = {}
+        while llm.has_unfinished_requests():
+            for output in llm.step():
+                latest[output.request_id] = output
+        if device_path:
+            assert llm.decode_graphs.replays > 5, "decode steps must have been replayed"
+        for index, prompt in enumerate(prompts):
+            expected, margins = _greedy_by(plain, prompt, 10)
+            got = latest[f"t{index}"].token_ids
+            for place, (a, b) in enumerate(zip(got, expected)):
+                if a != b:
+                    assert margins[place] < 1e-4, f"request {index}: token {place} is {a}, expected {b}"
+                    break
+    finally:
+        MIXERS.unregister(kind)
+
+
+def test_toy_embedding_and_output_head_register_build_and_step():
+    """The two ends of the model are parts like the others: an embedding that scales its rows and
+    a head that caps its logits, defined and registered here, in a model that is otherwise the
+    small one.  No file of the framework changes."""
+    import dataclasses
+    from vllm_from_scratch_b200 import ModelRunner, PartSpec
+    from vllm_from_scratch_b200.parts import EMBEDDINGS, OUTPUT_HEADS, DecoderModel, Embedding, OutputHead, WeightInfo
+
+    class ScaledEmbedding(Embedding):
+        graph_safe = True
+
+        def __init__(self, params, env):
+            super().__init__(params, env)
+            self.scale, self.weight = float(params["scale"]), None
+
+        def expected_weights(self):
+            return {"weight": WeightInfo((int(self.params["vocab_size"]), self.env.hidden_size))}
+
+        def load_weights(self, tensors):
+            self.weight = tensors["weight"]
+
+        def forward(self, token_ids, ctx, residual, error_flag):
+            residual.copy_(self.weight[token_ids.long()].float() * self.scale)
+
+        def table(self):
+            return self.weight
+
+    class CappedHead(OutputHead):
+        graph_safe = True
+
+        def __init__(self, params, env):
+            super().__init__(params, env)
+            self.cap, self.weight = float(params["cap"]), None
+
+        def bind_embedding(self, embedding):
+            self.weight = embedding.table()
+
+        def forward(self, normed):
+            logits = normed.float() @ self.weight.float().T
+            return self.cap * torch.tanh(logits / self.cap)
+
+    EMBEDDINGS.register("toy_scaled_embedding")(ScaledEmbedding)
+    OUTPUT_HEADS.register("toy_capped_head")(CappedHead)
+    try:
+        base = small_spec([(0, None), (1, None)])
+        spec = dataclasses.replace(
+            base, embedding=PartSpec("toy_scaled_embedding", {"scale": 8.0}, name="model.embed_tokens"),
+            output_head=PartSpec("toy_capped_head", {"cap": 0.5}, name="lm_head"))
+        weights = random_weights_for(DecoderModel(spec, torch.float32, "cpu"), seed=6)
+        assert "lm_head.weight" not in weights
+        runner = ModelRunner(spec, weights, "float32", 8, 16, 2, device="cuda")
+        assert runner.model.graph_safe()
+        cfg = {"heads": 4, "kv_heads": 2, "head_dim": 16, "eps": 1e-6, "theta": 1e4}
+        tokens = helpers.random_tokens(97, 33, seed=2)
+        h = weights["model.embed_tokens.weight"][torch.tensor(tokens)] * 8.0
+        for layer in (0, 1):
+            h = _plain_attention_layer(weights, h, layer, cfg)
+        logits = plain_qwen3.rms_norm(h, weights["model.norm.weight"], 1e-6) @ weights["model.embed_tokens.weight"].T
+        expected = 0.5 * torch.tanh(logits / 0.5)
+        assert float(expected.abs().max()) > 0.3, "the cap must matter"
+        for steps in ([[("r", 33)]], [[("r", 5)], [("r", 27)], [("r", 1)]]):
+            result = helpers.run_schedule(runner, {"r": tokens}, steps)["r"]
+            assert float((result - expected).abs().max()) < 3e-5
+    finally:
+        EMBEDDINGS.unregister("toy_scaled_embedding")
+        OUTPUT_HEADS.unregister("toy_capped_head")
+
+
+def test_toy_arrangements_with_four_norms_and_without_a_feed_forward():
+    """Two arrangements defined and registered here: one with a norm in front of and behind both
+    the mixer and the feed-forward (four norms a layer), one with a mixer only.  The layer's spec
+    brings the norms by role; a layer that brings other roles than its block arranges is refused."""
+    import dataclasses
+    from vllm_from_scratch_b200 import LayerSpec, ModelRunner, PartSpec
+    from vllm_from_scratch_b200.parts import BLOCKS, Block, DecoderModel
+
+    def branch_norm(norm, branch):
+        # a norm of the branch itself, not of the stream: add it into an empty stream
+        return norm.forward(branch, torch.zeros(branch.shape, dtype=torch.float32, device=branch.device))
+
+    class SandwichBlock(Block):
+        norm_roles = ("pre_mixer", "post_mixer", "pre_feed_forward", "post_feed_forward")
+        graph_safe = True
+
+        def forward(self, x, residual, ctx, cache):
+            mixed = self.mixer.forward(self.norms["pre_mixer"].forward(x, residual), ctx, cache)
+            mixed = branch_norm(self.norms["post_mixer"], mixed)
+            out = self.feed_forward.forward(self.norms["pre_feed_forward"].forward(mixed, residual), ctx)
+            return branch_norm(self.norms["post_feed_forward"], out)
+
+    class MixerOnlyBlock(Block):
+        norm_roles = ("mixer",)
+        needs_feed_forward = False
+        graph_safe = True
+
+        def forward(self, x, residual, ctx, cache):
+            return self.mixer.forward(self.norms["mixer"].forward(x, residual), ctx, cache)
+
+    BLOCKS.register("toy_sandwich")(SandwichBlock)
+    BLOCKS.register("toy_mixer_only")(MixerOnlyBlock)
+    try:
+        base = small_spec([(0, None), (1, None)])
+        norm = {"eps": 1e-6}
+        sandwich = dataclasses.replace(base.layers[0], block=PartSpec("toy_sandwich"), norms={
+            role: PartSpec("rms_norm", norm, name=f"norm_{index}")
+            for index, role in enumerate(SandwichBlock.norm_roles)})
+        mixer_only = dataclasses.replace(base.layers[1], block=PartSpec("toy_mixer_only"), feed_forward=None,
+                                         norms={"mixer": PartSpec("rms_norm", norm, name="only_norm")})
+        spec = dataclasses.replace(base, layers=(sandwich, mixer_only))
+        weights = random_weights_for(DecoderModel(spec, torch.float32, "cpu"), seed=9)
+        assert "model.layers.0.norm_3.weight" in weights and "model.layers.1.mlp.down_proj.weight" not in weights
+        with pytest.raises(ValueError, match="arranges norms"):
+            DecoderModel(dataclasses.replace(base, layers=(dataclasses.replace(sandwich, norms=base.layers[0].norms),
+                                                           mixer_only)), torch.float32, "cpu")
+        with pytest.raises(ValueError, match="needs a feed-forward"):
+            DecoderModel(dataclasses.replace(base, layers=(dataclasses.replace(base.layers[0], feed_forward=None),
+                                                           mixer_only)), torch.float32, "cpu")
+        runner = ModelRunner(spec, weights, "float32", 8, 16, 2, device="cuda")
+        cfg = {"heads": 4, "kv_heads": 2, "head_dim": 16, "eps": 1e-6, "theta": 1e4}
+        tokens = helpers.random_tokens(97, 29, seed=12)
+        rms = lambda t, name: plain_qwen3.rms_norm(t, weights[name], 1e-6)
+        attention_weights = lambda p: {"a." + k[len(p + "self_attn."):]: v for k, v in weights.items()
+                                       if k.startswith(p + "self_attn.")}
+        h = weights["model.embed_tokens.weight"][torch.tensor(tokens)]
+        p = "model.layers.0."
+        h = h + rms(plain_attention(rms(h, p + "norm_0.weight"), attention_weights(p), cfg, None), p + "norm_1.weight")
+        h = h + rms(plain_qwen3.feed_forward(rms(h, p + "norm_2.weight"), weights, p + "mlp."), p + "norm_3.weight")
+        p = "model.layers.1."
+        h = h + plain_attention(rms(h, p + "only_norm.weight"), attention_weights(p), cfg, None)
+        expected = rms(h, "model.norm.weight") @ weights["model.embed_tokens.weight"].T
+        for steps in ([[("r", 29)]], [[("r", 11)], [("r", 2)], [("r", 15)], [("r", 1)]]):
+            result = helpers.run_schedule(runner, {"r": tokens}, steps)["r"]
+            assert float((result - expected).abs().max()) < 3e-5
+    finally:
+        BLOCKS.unregister("toy_sandwich")
+        BLOCKS.unregister("toy_mixer_only")

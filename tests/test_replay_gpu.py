@@ -65,7 +65,7 @@ def make_runner(folder, dtype, page_size, num_pages, max_requests=4):
 
 
 def compare(results, expected, dtype, what):
-    worst = 0.0
+    worst = worst_rel = 0.0
     for rid, logits in results.items():
         reference = expected[rid]
         assert logits.shape == reference.shape, (what, rid, logits.shape, reference.shape)
@@ -78,7 +78,8 @@ def compare(results, expected, dtype, what):
                 f"(max |diff| there {float(diff[position].max()):.3e}, bound {bound:.3e}, "
                 f"largest anywhere {float(diff.max()):.3e})")
         worst = max(worst, float(diff.max()))
-    print(f"{what}: max |diff| {worst:.3e}")
+        worst_rel = max(worst_rel, float(diff.max()) / float(reference.abs().max()))
+    print(f"{what}: max |diff| {worst:.3e}, as a fraction of the largest logit {worst_rel:.3e}")
 
 
 CUTS = {
@@ -116,6 +117,70 @@ def test_mixed_batches_with_few_pages(folders, references, name, seed, dtype):
     results = helpers.run_schedule(runner, sequences, steps)
     compare(results, expected[dtype], dtype, f"{name}/mixed{seed}/{dtype}")
     assert runner.manager.stats()["requests"] == 0
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("seed", [2, 3])
+@pytest.mark.parametrize("name", ["D", "E"])
+def test_mixed_batches_with_long_portions(folders, references, name, seed, dtype):
+    """The mixed cut with portions of 64, 100, 130 and 300 tokens: in bfloat16 one step then holds
+    single tokens (the decode kernel; for head size 128 the one that also rotates and stores),
+    a long portion at a row offset (head size 128: the tcgen05 kernel) and pages used again."""
+    raw, page_size = CONFIGS[name]
+    sequences, expected = references[name]
+    steps = helpers.cut_mixed(LENGTHS[name], seed=seed, live=4, sizes=helpers.LARGE_PORTIONS)
+    assert any(n >= 64 for step in steps for _, n in step if len(step) > 1), "a long portion beside other requests"
+    pages = sum(sorted((-(-n // page_size) for n in LENGTHS[name].values()), reverse=True)[:4])
+    runner = make_runner(folders[name], dtype, page_size, pages)
+    results = helpers.run_schedule(runner, sequences, steps)
+    compare(results, expected[dtype], dtype, f"{name}/mixed-long{seed}/{dtype}")
+    assert runner.manager.stats()["requests"] == 0
+    runner.check_device()
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("name,page_size", [("D", 24), ("D", 48), ("E", 24), ("E", 48)])
+def test_pages_whose_size_is_no_power_of_two(folders, references, name, page_size, dtype):
+    """Pages of 24 and 48 positions (head sizes 64 and 128): the kernels fed by tensor copies
+    refuse them, the ones with per-thread copies serve them."""
+    sequences, expected = references[name]
+    longest = max(LENGTHS[name].values())
+    for cut, steps in (("tail", helpers.cut_tail_one_by_one(LENGTHS[name], 32)),
+                       ("portions", helpers.cut_changing_portions(LENGTHS[name], seed=5))):
+        runner = make_runner(folders[name], dtype, page_size, -(-longest // page_size) + 1)
+        results = helpers.run_schedule(runner, sequences, steps)
+        compare(results, expected[dtype], dtype, f"{name}/page{page_size}/{cut}/{dtype}")
+    steps = helpers.cut_mixed(LENGTHS[name], seed=6, live=4, sizes=helpers.LARGE_PORTIONS)
+    pages = sum(sorted((-(-n // page_size) for n in LENGTHS[name].values()), reverse=True)[:4])
+    runner = make_runner(folders[name], dtype, page_size, pages)
+    results = helpers.run_schedule(runner, sequences, steps)
+    compare(results, expected[dtype], dtype, f"{name}/page{page_size}/mixed/{dtype}")
+    runner.check_device()
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("name", ["B", "E"])
+def test_mixed_steps_as_graph_replays_match_plain(folders, references, name, dtype):
+    """The mixed cut through ``MixedGraphs``, twice over (the second pass under other request
+    ids): a shape met again is captured for the longest context and replayed.  Both passes
+    against the plain model; for head size 128 in bfloat16 the replayed steps hold the decode
+    kernel beside the tcgen05 kernel with a key split planned for a length they do not have."""
+    from vllm_from_scratch_b200.engine.decode_graph import MixedGraphs
+    raw, page_size = CONFIGS[name]
+    sequences, expected = references[name]
+    steps = helpers.cut_mixed(LENGTHS[name], seed=7, live=4, sizes=helpers.LARGE_PORTIONS)
+    pages = sum(sorted((-(-n // page_size) for n in LENGTHS[name].values()), reverse=True)[:4])
+    runner = make_runner(folders[name], dtype, page_size, pages)
+    graphs = MixedGraphs(runner, raw["max_position_embeddings"], max_graphs=512)
+    for suffix in ("", "-again"):
+        renamed = {rid + suffix: tokens for rid, tokens in sequences.items()}
+        plan = [[(rid + suffix, n) for rid, n in step] for step in steps]
+        results = helpers.run_schedule(runner, renamed, plan, step=graphs.run)
+        compare({rid[:len(rid) - len(suffix)] if suffix else rid: logits for rid, logits in results.items()},
+                expected[dtype], dtype, f"{name}/mixed-graphs{suffix}/{dtype}")
+    assert graphs.replays >= len(steps) // 2, "most steps of the second pass must have been replays"
+    assert runner.manager.stats()["requests"] == 0
+    runner.check_device()
 
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])

@@ -224,3 +224,19 @@ def test_schedule_ahead_leaves_out_what_ends_by_length_and_declines_when_unsure(
     plan = _decoding(full, [("a", 7)], max_tokens=9)         # 8 tokens fill both pages
     assert full.schedule_ahead(plan) is None
     cache.check_invariants()
+
+
+def test_an_id_is_free_again_only_after_its_finished_notice_went_out():
+    """minivllm/core/sched/scheduler.py:163-170: between the end of a request and the next plan
+    (which carries the notice that it finished) its id is refused."""
+    scheduler, _ = make(pages=16)
+    scheduler.add_request(request("r", 5, max_tokens=1))
+    plan = scheduler.schedule()
+    scheduler.update(plan, {"r": 7})
+    assert not scheduler.has_unfinished_requests()
+    with pytest.raises(ValueError, match="has just finished"):
+        scheduler.add_request(request("r", 3))
+    assert scheduler.schedule().finished_ids == ["r"]
+    scheduler.add_request(request("r", 3))
+    with pytest.raises(ValueError, match="already in use"):
+        scheduler.add_request(request("r", 3))

@@ -55,9 +55,10 @@ B200_EXPORT int b200_decode_attention_tma_bf16(
     int* error_flag = attention_error_flag();
     if (error_flag == nullptr) return fail("decode_attention", "no error flag");
     const int copy_rows = page_size < kKeys ? page_size : kKeys;
-    const CUtensorMap* map_k = tensor_map_for(k_pages, num_pages * nkv * page_size, d, copy_rows);
-    const CUtensorMap* map_v = tensor_map_for(v_pages, num_pages * nkv * page_size, d, copy_rows);
-    if (map_k == nullptr || map_v == nullptr) return fail("decode_attention", "could not encode a tensor map");
+    CUtensorMap map_k, map_v;
+    if (!tensor_map_for(k_pages, num_pages * nkv * page_size, d, copy_rows, &map_k) ||
+        !tensor_map_for(v_pages, num_pages * nkv * page_size, d, copy_rows, &map_v))
+        return fail("decode_attention", "could not encode a tensor map");
 #define B200_CASE(D)                                                                                        \
     if (d == D)                                                                                             \
         return launch_decode_tma<D, false>(map_k, map_v, q, out, partial_o, partial_ml, seq_lens,          \
@@ -89,9 +90,10 @@ B200_EXPORT int b200_decode_attention_fused_bf16(
     int* error_flag = attention_error_flag();
     if (error_flag == nullptr) return fail("decode_attention", "no error flag");
     const int copy_rows = page_size < kKeys ? page_size : kKeys;
-    const CUtensorMap* map_k = tensor_map_for(k_pages, num_pages * nkv * page_size, d, copy_rows);
-    const CUtensorMap* map_v = tensor_map_for(v_pages, num_pages * nkv * page_size, d, copy_rows);
-    if (map_k == nullptr || map_v == nullptr) return fail("decode_attention", "could not encode a tensor map");
+    CUtensorMap map_k, map_v;
+    if (!tensor_map_for(k_pages, num_pages * nkv * page_size, d, copy_rows, &map_k) ||
+        !tensor_map_for(v_pages, num_pages * nkv * page_size, d, copy_rows, &map_v))
+        return fail("decode_attention", "could not encode a tensor map");
     DecodeRope rope;
     rope.positions = positions;
     rope.slots = slots;
@@ -142,6 +144,9 @@ static int* attention_error_flag() {
     return address[device];
 }
 
+// Device address of the error word (for a reader that copies it with other results), or null.
+B200_EXPORT void* b200_attention_error_address() { return attention_error_flag(); }
+
 B200_EXPORT int b200_attention_error() {
     int code = 0;
     if (cudaMemcpyFromSymbol(&code, b200::g_attention_error, sizeof(int)) != cudaSuccess) return -1;
@@ -159,14 +164,24 @@ B200_EXPORT int b200_prefill_attention_tc_supports(int nq, int nkv, int d, int p
                ? 1 : 0;
 }
 
+// Number of SMs of the calling thread's device, 0 if it cannot be read.
+B200_EXPORT int b200_sm_count() { return b200::sm_count(); }
+
+// Host-only check that maps handed out by the tensor-map cache stay valid when the cache is
+// emptied (see tensor_map.cuh); buffer: `bytes` of device memory whose addresses are encoded
+// and never read.  0 = all copies agree.
+B200_EXPORT int b200_tensor_map_cache_self_check(const void* buffer, long long bytes, int count) {
+    return b200::tensor_map_cache_self_check(buffer, (size_t)bytes, count);
+}
+
 // Over how many blocks the tensor-memory kernel divides the keys of a row block for a launch of
 // num_tokens tokens of num_requests requests (1: not at all).  The caller provides
 // partial_o [rows of q * nq * splits, 128] and partial_ml [rows of q * nq * splits, 2] floats.
 B200_EXPORT int b200_prefill_attention_tc_splits(int num_tokens, int num_requests, int nq, int max_seq_len) {
-    if (getenv("B200_NO_TC_KEY_SPLIT") != nullptr) return 1;
+    const int sms = b200::sm_count();
     const long long blocks = (long long)(num_tokens / b200::kAtBlockRows + num_requests) * nq;
-    if (blocks <= 0 || blocks * 2 > 148) return 1;                      // half the SMs busy: leave it
-    int splits = (int)(148 / blocks);
+    if (sms <= 0 || blocks <= 0 || blocks * 2 > sms) return 1;          // half the SMs busy: leave it
+    int splits = (int)(sms / blocks);
     // Sixteen tiles of keys a block at least: 512 tokens over 512 keys took 25 us in two shares
     // against 15 us whole, 512 over 8192 keys 75 against 156 us, 128 over 16384 keys 48 against 288.
     const int by_keys = max_seq_len / 1024;
@@ -192,11 +207,11 @@ B200_EXPORT int b200_prefill_attention_tc_bf16(
     if (!b200_prefill_attention_tc_supports(nq, nkv, d, page_size)) return fail("prefill_attention_tc", "shape not built");
     int* error_flag = attention_error_flag();
     if (error_flag == nullptr) return fail("prefill_attention_tc", "no error flag");
-    const CUtensorMap* map_q = tensor_map_for(q, num_tokens, nq * d, kAtRows);   // one group of rows per copy
     const int copy_rows = page_size < kAtKeys ? page_size : kAtKeys;            // a page, or the part of it in one tile
-    const CUtensorMap* map_k = tensor_map_for(k_pages, num_pages * nkv * page_size, d, copy_rows);
-    const CUtensorMap* map_v = tensor_map_for(v_pages, num_pages * nkv * page_size, d, copy_rows);
-    if (map_q == nullptr || map_k == nullptr || map_v == nullptr)
+    CUtensorMap map_q, map_k, map_v;
+    if (!tensor_map_for(q, num_tokens, nq * d, kAtRows, &map_q) ||             // one group of rows per copy
+        !tensor_map_for(k_pages, num_pages * nkv * page_size, d, copy_rows, &map_k) ||
+        !tensor_map_for(v_pages, num_pages * nkv * page_size, d, copy_rows, &map_v))
         return fail("prefill_attention_tc", "could not encode a tensor map");
     cudaError_t status = cudaFuncSetAttribute(prefill_attention_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kAtSmem);
     if (status != cudaSuccess) return fail("prefill_attention_tc", cudaGetErrorString(status));
@@ -204,7 +219,7 @@ B200_EXPORT int b200_prefill_attention_tc_bf16(
     if (blocks > 65535) return fail("prefill_attention_tc", "too many tokens for one launch");
     dim3 grid(nq, blocks, key_splits);
     prefill_attention_tc_kernel<<<grid, kAtThreads, kAtSmem, stream>>>(
-        *map_q, *map_k, *map_v, (__nv_bfloat16*)out, query_start, seq_lens, block_table, num_requests, max_pages,
+        map_q, map_k, map_v, (__nv_bfloat16*)out, query_start, seq_lens, block_table, num_requests, max_pages,
         nq, nkv, page_size, scale * kLog2e, window, token_offset, key_splits, partial_o, partial_ml, error_flag);
     if (int rc = check_launch("prefill_attention_tc")) return rc;
     if (key_splits > 1) {

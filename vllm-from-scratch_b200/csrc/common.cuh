@@ -30,6 +30,20 @@ inline int check_launch(const char* where) {
     return 0;
 }
 
+// Number of SMs of the calling thread's device, asked of the device once; 0 if it cannot be read.
+// Launch planning (how many blocks fill the GPU) uses this, never a literal.
+inline int sm_count() {
+    static int count[64] = {};
+    int device = 0;
+    if (cudaGetDevice(&device) != cudaSuccess || device < 0 || device >= 64) return 0;
+    if (count[device] == 0) {
+        int value = 0;
+        if (cudaDeviceGetAttribute(&value, cudaDevAttrMultiProcessorCount, device) != cudaSuccess) return 0;
+        count[device] = value;
+    }
+    return count[device];
+}
+
 __device__ __forceinline__ float to_float(float v) { return v; }
 __device__ __forceinline__ float to_float(__nv_bfloat16 v) { return __bfloat162float(v); }
 

@@ -360,7 +360,7 @@ __global__ void __launch_bounds__(kDtThreads, D <= 128 ? 3 : 1) decode_attention
 }
 
 template <int D, bool FUSED>
-int launch_decode_tma(const CUtensorMap* map_k, const CUtensorMap* map_v, const void* q, void* out,
+int launch_decode_tma(const CUtensorMap& map_k, const CUtensorMap& map_v, const void* q, void* out,
                       float* partial_o, float* partial_ml, const int* seq_lens, const int* block_table,
                       int num_requests, int max_pages, int nq, int nkv, int page_size, float scale, int window,
                       int splits, int* error_flag, cudaStream_t stream, DecodeRope rope = DecodeRope()) {
@@ -373,7 +373,7 @@ int launch_decode_tma(const CUtensorMap* map_k, const CUtensorMap* map_v, const 
         configured = true;
     }
     dim3 grid(splits, nkv, num_requests);
-    launch_overlapped(kernel, grid, kDtThreads, smem, stream, *map_k, *map_v, (const bf16*)q, (bf16*)out, partial_o,
+    launch_overlapped(kernel, grid, kDtThreads, smem, stream, map_k, map_v, (const bf16*)q, (bf16*)out, partial_o,
                       partial_ml, seq_lens, block_table, max_pages, nq, nkv, page_size, scale * kLog2e, window,
                       splits, error_flag, rope);
     if (int rc = check_launch("decode_attention")) return rc;

@@ -17,12 +17,7 @@
 #include <stdlib.h>
 
 #include "common.cuh"
-#include "stream_gemm.cuh"
-#include "tensor_map.cuh"
-
-#include <map>
-#include <mutex>
-#include <tuple>
+#include "async_copy.cuh"
 
 namespace b200 {
 
@@ -57,7 +52,6 @@ template <typename T> __device__ __forceinline__ void store_one(T* p, float a) {
 
 }  // namespace b200
 #include "slab_gemm.cuh"
-#include "tc_gemm.cuh"
 namespace b200 {
 
 constexpr int kSkinnyMaxWarps = 16;
@@ -183,13 +177,12 @@ int launch_skinny(const bf16* x, const bf16* w, OutT* y, int M, int N, int K, in
     // The GPU should hold a few thousand warps, each with all of its loads in flight:
     // the fewer blocks a product has, the more warps split K inside each block.
     const int k_blocks = K >> 5;
-    const bool two_tiles = gated_inter > 0 || (N >= 148 * 4 * 16 && getenv("B200_SKINNY_ONE_TILE") == nullptr);
+    const bool two_tiles = gated_inter > 0 || N >= sm_count() * 4 * 16;
     const int ctas = gated_inter > 0 ? (gated_inter + 7) / 8 : two_tiles ? (N + 15) / 16 : (N + 7) / 8;
     const int wanted = 6144 / (ctas * (two_tiles ? 2 : 1));
     int warps = 4;
     while (warps * 2 <= wanted && warps < kSkinnyMaxWarps) warps *= 2;
     while (warps > 1 && warps > k_blocks) warps /= 2;
-    if (const char* forced = getenv("B200_SKINNY_WARPS")) warps = atoi(forced);
     const int threads = warps * 32;
     if (gated_inter > 0) {
         launch_overlapped(skinny_gemm_kernel<2, true, OutT, 4>, ctas, threads, 0, stream, x, w, y, M, gated_inter, K, gated_inter);
@@ -205,20 +198,27 @@ int launch_skinny(const bf16* x, const bf16* w, OutT* y, int M, int N, int K, in
 // b200_stream_gemm_error().
 __device__ int g_stream_error;
 
+// Device address of the error word, per device of the calling thread, or null.
+inline int* stream_error_flag() {
+    static int* address[64] = {};
+    int device = 0;
+    if (cudaGetDevice(&device) != cudaSuccess || device < 0 || device >= 64) return nullptr;
+    if (address[device] == nullptr) {
+        void* found = nullptr;
+        if (cudaGetSymbolAddress(&found, g_stream_error) != cudaSuccess) return nullptr;
+        address[device] = static_cast<int*>(found);
+    }
+    return address[device];
+}
+
 // 1 = launched, 0 = not a shape for the kernel with resident weight rows, < 0 = error.
 // gated_inter > 0: w is [2 * gated_inter, K], the result [M, gated_inter].
 template <typename OutT>
 int launch_slab(const bf16* x, const bf16* w, OutT* y, int M, int N, int K, int gated_inter, cudaStream_t stream) {
-    const bool disabled = getenv("B200_NO_SLAB_GEMM") != nullptr;
     const bool gated = gated_inter > 0;
-    if (gated && getenv("B200_NO_SLAB_GATED") != nullptr) return 0;
-    if (disabled || M > 16 || K % 128 != 0 || slab_smem_bytes(K, gated) > 200 * 1024) return 0;
-    static int* error_flag = nullptr;
-    if (error_flag == nullptr) {
-        void* found = nullptr;
-        if (cudaGetSymbolAddress(&found, g_stream_error) != cudaSuccess) return fail("slab_gemm", "no error flag");
-        error_flag = static_cast<int*>(found);
-    }
+    if (M > 16 || K % 128 != 0 || slab_smem_bytes(K, gated) > 200 * 1024) return 0;
+    int* error_flag = stream_error_flag();
+    if (error_flag == nullptr) return fail("slab_gemm", "no error flag");
     const size_t smem = slab_smem_bytes(K, gated);
     const int rows = gated ? gated_inter : N;
     const int blocks = (rows + kSlabRows - 1) / kSlabRows, threads = kSlabWarps * 32;
@@ -227,7 +227,7 @@ int launch_slab(const bf16* x, const bf16* w, OutT* y, int M, int N, int K, int 
     // way): for one or two token rows, where a decode step took 1.193 against 1.213 ms with it (at 8
     // rows 1.504 against 1.499), in the plain form where two blocks of such rows fill an SM's shared
     // memory, in the gated form always.
-    const bool deep = M <= 2 && (gated || K >= 4096) && getenv("B200_SLAB_SHALLOW") == nullptr;
+    const bool deep = M <= 2 && (gated || K >= 4096);
     auto launch = [&](auto kernel, bool* configured) {
         if (!*configured) {
             cudaError_t status = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024);
@@ -250,59 +250,14 @@ int launch_slab(const bf16* x, const bf16* w, OutT* y, int M, int N, int K, int 
     return check_launch("slab_gemm") == 0 ? 1 : -1;
 }
 
-// Returns 1 when the shape was launched, 0 when its token rows do not fit in shared
-// memory beside at least three weight stages (the caller then uses the other kernel).
-template <int TILES, bool GATED, typename OutT>
-int launch_stream_one(const bf16* x, const bf16* w, OutT* y, int M, int N, int K, int up_offset,
-                      int* error_flag, cudaStream_t stream) {
-    auto kernel = stream_gemm_kernel<TILES, GATED, OutT>;
-    const int x_rows = M <= 8 ? 8 : 16;
-    const int limit = 227 * 1024;
-    const int half = limit / 2 - 1024;                       // two blocks per SM when they fit
-    int stages = 8;
-    while (stages > 3 && stream_gemm_smem(TILES, stages, x_rows, K) > half) --stages;
-    if (stream_gemm_smem(TILES, stages, x_rows, K) > half) {
-        stages = 8;                                          // one block per SM, as many stages as fit
-        while (stages > 3 && stream_gemm_smem(TILES, stages, x_rows, K) > limit) --stages;
-    }
-    const int smem = stream_gemm_smem(TILES, stages, x_rows, K);
-    if (smem > limit) return 0;
-    cudaError_t status = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
-    if (status != cudaSuccess) return fail("stream_gemm", cudaGetErrorString(status));
-    const int rows_per_tile = GATED ? 8 : 8 * TILES;
-    const int num_tiles = (N + rows_per_tile - 1) / rows_per_tile;
-    const int resident = 148 * (limit / (smem + 1024));
-    const int grid = num_tiles < resident ? num_tiles : resident;
-    kernel<<<grid, (kStreamConsumers + 1) * 32, smem, stream>>>(x, w, y, M, N, K, up_offset, num_tiles, stages,
-                                                                x_rows, error_flag);
-    if (check_launch("stream_gemm")) return -1;
-    return 1;
-}
-
-template <typename OutT>
-int launch_stream(const bf16* x, const bf16* w, OutT* y, int M, int N, int K, int gated_inter,
-                  cudaStream_t stream) {
-    static int* error_flag[64] = {};
-    int device = 0;
-    if (cudaGetDevice(&device) != cudaSuccess || device < 0 || device >= 64) return fail("stream_gemm", "no device");
-    if (error_flag[device] == nullptr) {
-        void* found = nullptr;
-        cudaError_t status = cudaGetSymbolAddress(&found, g_stream_error);
-        if (status != cudaSuccess) return fail("stream_gemm", cudaGetErrorString(status));
-        error_flag[device] = static_cast<int*>(found);
-    }
-    if (gated_inter > 0)
-        return launch_stream_one<2, true, OutT>(x, w, y, M, gated_inter, K, gated_inter, error_flag[device], stream);
-    if (N >= 148 * 3 * 16)
-        return launch_stream_one<2, false, OutT>(x, w, y, M, N, K, 0, error_flag[device], stream);
-    return launch_stream_one<1, false, OutT>(x, w, y, M, N, K, 0, error_flag[device], stream);
-}
-
 }  // namespace b200
 
-// 0, or the code a kernel left when one of its bounded waits ran out (1: the producer
-// waited for a free stage, 2: for its own copies, 3: a consumer waited for data).
+// 0, or the code a kernel left when one of its bounded waits ran out (41, 42: a block of the
+// resident-rows kernel waited for its weight rows).
 // Synchronises with the device and clears the code.
+// Device address of the error word (for a reader that copies it with other results), or null.
+B200_EXPORT void* b200_stream_gemm_error_address() { return b200::stream_error_flag(); }
+
 B200_EXPORT int b200_stream_gemm_error() {
     int code = 0;
     if (cudaMemcpyFromSymbol(&code, b200::g_stream_error, sizeof(int)) != cudaSuccess) return -1;
@@ -311,132 +266,6 @@ B200_EXPORT int b200_stream_gemm_error() {
         cudaMemcpyToSymbol(b200::g_stream_error, &zero, sizeof(int));
     }
     return code;
-}
-
-namespace b200 {
-
-struct TcPlan {
-    int ntok, stages, splits, steps_per_split, row_tiles, smem;
-};
-
-inline int env_int(const char* name, int fallback) {
-    const char* text = getenv(name);
-    return text != nullptr ? atoi(text) : fallback;
-}
-
-inline TcPlan tc_plan(int M, int N, int K, bool gated) {
-    TcPlan plan;
-    plan.ntok = ((M + 15) / 16) * 16;
-    const int rows_per_tile = gated ? 64 : kTcRows;
-    plan.row_tiles = (N + rows_per_tile - 1) / rows_per_tile;
-    const int total_steps = (K + kTcK - 1) / kTcK;
-    // Matrices with few rows are split along K, over a cluster: as many splits as still leave
-    // every block one of the two places of an SM (so that all of them stream at once, and the
-    // kernel after this one finds room to start its own copies), the steps divided evenly if
-    // that is possible.  The split depends on the matrix only, never on the number of tokens,
-    // so a token's sums are formed in the same order in every batch.
-    const int places = env_int("B200_TC_BLOCKS", 2 * 148);
-    int splits = 1;
-    for (int s = kTcMaxSplits; s > 1; --s)
-        if (plan.row_tiles * s <= places && s * 2 <= total_steps && total_steps % s == 0) {
-            splits = s;
-            break;
-        }
-    if (splits == 1)
-        for (int s = kTcMaxSplits; s > 1; --s)
-            if (plan.row_tiles * s <= places && s * 2 <= total_steps) {
-                splits = s;
-                break;
-            }
-    splits = env_int("B200_TC_SPLITS", splits);
-    if (splits > kTcMaxSplits) splits = kTcMaxSplits;
-    if (splits > total_steps / 2) splits = total_steps / 2;
-    if (splits < 1) splits = 1;
-    plan.steps_per_split = (total_steps + splits - 1) / splits;
-    plan.splits = (total_steps + plan.steps_per_split - 1) / plan.steps_per_split;
-    // As many stages as a split has steps (its whole share of the matrix is then requested at
-    // once, before the kernel ahead has ended), within half of an SM's shared memory.
-    const int budget = env_int("B200_TC_SMEM_KB", 100) * 1024;
-    plan.stages = plan.steps_per_split < 12 ? plan.steps_per_split : 12;
-    while (plan.stages > 2 && TcLayout(plan.stages, plan.ntok).total() > budget) --plan.stages;
-    plan.smem = TcLayout(plan.stages, plan.ntok).total();
-    // A block's share of an SM's shared memory is never below its share of the SM's 512 columns of
-    // tensor memory, so the blocks that fit on an SM never ask for more columns than it has: a
-    // block that spun in tcgen05.alloc while the holders of the columns waited for it (at the
-    // cluster barrier, or for its whole kernel to end) would be a deadlock.
-    int columns = 32;
-    while (columns < plan.ntok) columns *= 2;
-    const int least = (228 * 1024 / 512) * columns;
-    if (plan.smem < least) plan.smem = least;
-    return plan;
-}
-
-template <bool GATED, typename OutT>
-int launch_tc(const bf16* x, const bf16* w, OutT* y, int M, int N, int K, int w_rows, int* error_flag,
-              cudaStream_t stream) {
-    const TcPlan plan = tc_plan(M, N, K, GATED);
-    if (plan.smem > 227 * 1024) return fail("tc_gemm", "the tiles of this shape do not fit in shared memory");
-    const CUtensorMap* map_w = tensor_map_for(w, w_rows, K, GATED ? 64 : kTcRows);
-    const CUtensorMap* map_x = tensor_map_for(x, M, K, plan.ntok);
-    if (map_w == nullptr || map_x == nullptr) return fail("tc_gemm", "could not encode a tensor map");
-    auto kernel = tc_gemm_kernel<GATED, OutT>;
-    cudaError_t status = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, plan.smem);
-    if (status != cudaSuccess) return fail("tc_gemm", cudaGetErrorString(status));
-    cudaLaunchConfig_t config = {};
-    config.gridDim = dim3(plan.row_tiles, plan.splits);
-    config.blockDim = dim3(128);
-    config.dynamicSmemBytes = plan.smem;
-    config.stream = stream;
-    cudaLaunchAttribute attributes[2];
-    attributes[0].id = cudaLaunchAttributeClusterDimension;
-    attributes[0].val.clusterDim.x = 1;
-    attributes[0].val.clusterDim.y = plan.splits;
-    attributes[0].val.clusterDim.z = 1;
-    attributes[1].id = cudaLaunchAttributeProgrammaticStreamSerialization;
-    attributes[1].val.programmaticStreamSerializationAllowed = overlap_enabled() ? 1 : 0;
-    config.attrs = attributes;
-    config.numAttrs = 2;
-    status = cudaLaunchKernelEx(&config, kernel, *map_w, *map_x, y, M, N, K, plan.ntok, plan.stages,
-                                plan.steps_per_split, GATED ? N : 0, error_flag);
-    if (status != cudaSuccess) return fail("tc_gemm", cudaGetErrorString(status));
-    return check_launch("tc_gemm");
-}
-
-}  // namespace b200
-
-// Whether the tcgen05 product takes a shape (token rows M, weight rows N, width K).
-B200_EXPORT int b200_tc_gemm_supports(int M, int N, int K) {
-    if (M < 1 || M > 256 || K < 64 || K % 8 != 0 || N < 1) return 0;
-    return b200::tc_plan(M, N, K, false).smem <= 227 * 1024 ? 1 : 0;
-}
-
-// y[M, N] = x[M, K] . w[N, K]^T (gated_inter = 0), or y[M, I] = silu(x w[:I]^T) * (x w[I:]^T)
-// with w of 2 I rows (gated_inter = I, N = 2 I).  out_dtype: 0 float32, 1 bfloat16.
-B200_EXPORT int b200_tc_gemm_bf16(const void* x, const void* w, void* y, int M, int N, int K, int gated_inter,
-                                  int out_dtype, cudaStream_t stream) {
-    using namespace b200;
-    if (M == 0 || N == 0) return 0;
-    if (M < 1 || M > 256 || K < 64 || K % 8 != 0) return fail("tc_gemm", "needs 1 <= M <= 256 and K >= 64, a multiple of 8");
-    if (((uintptr_t)x | (uintptr_t)w) & 15) return fail("tc_gemm", "operands must be 16-byte aligned");
-    if (gated_inter > 0 && N != 2 * gated_inter) return fail("tc_gemm", "gated product needs N = 2 * inter");
-    if (out_dtype != 0 && out_dtype != 1) return fail("tc_gemm", "out_dtype must be 0 (float32) or 1 (bfloat16)");
-    static int* error_flag[64] = {};
-    int device = 0;
-    if (cudaGetDevice(&device) != cudaSuccess || device < 0 || device >= 64) return fail("tc_gemm", "no device");
-    if (error_flag[device] == nullptr) {
-        void* found = nullptr;
-        if (cudaGetSymbolAddress(&found, g_stream_error) != cudaSuccess) return fail("tc_gemm", "no error flag");
-        error_flag[device] = static_cast<int*>(found);
-    }
-    const bf16* xb = (const bf16*)x;
-    const bf16* wb = (const bf16*)w;
-    if (gated_inter > 0) {
-        if (out_dtype == 1)
-            return launch_tc<true, bf16>(xb, wb, (bf16*)y, M, gated_inter, K, N, error_flag[device], stream);
-        return launch_tc<true, float>(xb, wb, (float*)y, M, gated_inter, K, N, error_flag[device], stream);
-    }
-    if (out_dtype == 1) return launch_tc<false, bf16>(xb, wb, (bf16*)y, M, N, K, N, error_flag[device], stream);
-    return launch_tc<false, float>(xb, wb, (float*)y, M, N, K, N, error_flag[device], stream);
 }
 
 // Largest M and the divisibility of K the few-rows kernel takes.
@@ -453,13 +282,6 @@ B200_EXPORT int b200_skinny_gemm_bf16(const void* x, const void* w, void* y, int
     if (!b200_skinny_gemm_supports(M, N, K)) return fail("skinny_gemm", "needs 1 <= M <= 16 and K a multiple of 32");
     if (((uintptr_t)x | (uintptr_t)w) & 15) return fail("skinny_gemm", "operands must be 16-byte aligned");
     if (gated_inter > 0 && N != 2 * gated_inter) return fail("skinny_gemm", "gated product needs N = 2 * inter");
-    const bool streamed = K >= 512 && getenv("B200_STREAM_GEMM") != nullptr;
-    if (streamed && (out_dtype == 0 || out_dtype == 1)) {
-        const int rc = out_dtype == 1
-            ? launch_stream<bf16>((const bf16*)x, (const bf16*)w, (bf16*)y, M, N, K, gated_inter, stream)
-            : launch_stream<float>((const bf16*)x, (const bf16*)w, (float*)y, M, N, K, gated_inter, stream);
-        if (rc != 0) return rc < 0 ? rc : 0;       // launched (1) or failed (< 0); 0 = shape too large for it
-    }
     if ((out_dtype == 0 || out_dtype == 1) && ((uintptr_t)y & (out_dtype == 1 ? 3 : 7)) == 0) {
         const int rc = out_dtype == 1
             ? launch_slab<bf16>((const bf16*)x, (const bf16*)w, (bf16*)y, M, N, K, gated_inter, stream)

@@ -246,7 +246,8 @@ B200_EXPORT int b200_silu_mul(const void* gate_up, void* out, int num_tokens, in
     }
     const int threads = 256;
     size_t blocks = (total + threads - 1) / threads;
-    if (blocks > 148 * 32) blocks = 148 * 32;
+    const size_t most = (size_t)(sm_count() > 0 ? sm_count() : 1) * 32;
+    if (blocks > most) blocks = most;
     if (dtype == 0)
         silu_mul_kernel<float><<<(int)blocks, threads, 0, stream>>>((const float*)gate_up, (float*)out, inter, total);
     else if (dtype == 1)

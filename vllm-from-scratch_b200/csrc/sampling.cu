@@ -440,6 +440,22 @@ B200_EXPORT int b200_sample(const float* logits, int rows, int vocab, const floa
     return check_launch("sample");
 }
 
+namespace b200 {
+__global__ void collect_status_kernel(const int* a, const int* b, const int* c, int* out) {
+    if (threadIdx.x == 0) out[0] = a != nullptr ? *a : 0;
+    if (threadIdx.x == 1) out[1] = b != nullptr ? *b : 0;
+    if (threadIdx.x == 2) out[2] = c != nullptr ? *c : 0;
+}
+}  // namespace b200
+
+// out[0..2] = the words at a, b, c (0 for a null pointer): the error words that kernels of a step
+// may have set, put beside the step's sampled ids so that one copy brings both to the host.
+B200_EXPORT int b200_collect_status(const int* a, const int* b, const int* c, int* out, cudaStream_t stream) {
+    using namespace b200;
+    collect_status_kernel<<<1, 32, 0, stream>>>(a, b, c, out);
+    return check_launch("collect_status");
+}
+
 B200_EXPORT int b200_penalties(float* logits, int rows, int vocab, const int* offsets,
                                const int* seen_tokens, const int* output_counts, const float* repetition,
                                const float* frequency, const float* presence, cudaStream_t stream) {

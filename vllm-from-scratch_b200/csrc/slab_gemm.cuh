@@ -18,7 +18,7 @@
 // Waits are bounded; a block that gives up sets `error_flag` and stores nothing.
 #pragma once
 
-#include "stream_gemm.cuh"
+#include "async_copy.cuh"
 
 namespace b200 {
 

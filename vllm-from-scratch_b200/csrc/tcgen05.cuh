@@ -5,7 +5,7 @@
 
 #include <cuda.h>
 
-#include "stream_gemm.cuh"
+#include "async_copy.cuh"
 
 namespace b200 {
 

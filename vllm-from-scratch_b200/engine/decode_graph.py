@@ -73,10 +73,18 @@ class DecodeGraphs:
             x, residual = model.forward(token_ids, ctx, views)
             return model.logits(x, residual, rows)
 
+        # Warm-up: kernels compiled and loaded before the capture.  It runs this very batch, and
+        # the replay after the capture runs it again: keys and values land in the same slots
+        # both times, but state of fixed size per request would be advanced twice, so it is
+        # put back as it was.
+        states = self.runner.storage.states
+        saved = {index: state.clone() for index, state in states.items()}
         stream = torch.cuda.Stream(device=device)
         stream.wait_stream(torch.cuda.current_stream(device))
         with torch.cuda.stream(stream):
-            body()                      # warm-up: kernels compiled and loaded before the capture
+            body()
+            for index, state in states.items():
+                state.copy_(saved[index])
         torch.cuda.current_stream(device).wait_stream(stream)
         torch.cuda.synchronize(device)
         graph = torch.cuda.CUDAGraph()
@@ -183,9 +191,18 @@ class MixedGraphs:
             x, residual = model.forward(token_ids, ctx, views)
             return None if meta["num_wanted"] == 0 else model.logits(x, residual, want_rows)
 
-        # No warm-up run: a step of this very shape has gone through the ordinary step
-        # function before (that is why it is captured now), so every kernel it launches is
-        # compiled, loaded and configured.
+        # A warm-up run of this very body: the step that came before went through the ordinary
+        # step function with its own request count, table width and longest context, so the
+        # padded shape planned for max_model_len may pick other kernels or splits (a key
+        # split, the merge kernel), whose first launch (module load, attribute set-up) must
+        # not fall inside the capture.  The body writes the same keys and values to the same
+        # slots as the capture and the replay after it, so running it once more changes nothing.
+        stream = torch.cuda.Stream(device=device)
+        stream.wait_stream(torch.cuda.current_stream(device))
+        with torch.cuda.stream(stream):
+            body()
+        torch.cuda.current_stream(device).wait_stream(stream)
+        torch.cuda.synchronize(device)
         graph = torch.cuda.CUDAGraph()
         with torch.cuda.graph(graph, pool=self._pool):
             logits = body()

@@ -19,6 +19,7 @@ from typing import Sequence
 
 import torch
 
+from .. import kernels
 from ..config.engine_config import CacheConfig, EngineConfig, ModelConfig, SchedulerConfig
 from ..sampling.params import SamplingParams
 from ..sampling.sampler import Sampler
@@ -34,11 +35,14 @@ class EngineDeadError(RuntimeError):
 
 class _InFlight:
     """A step whose work is queued on the GPU: the plan, the requests that sample (in
-    row order), their ids on the device, and the pinned copy on its way to the host."""
+    row order), their ids on the device (followed by the step's status words when
+    ``has_status``), and the pinned copy on its way to the host."""
 
     def __init__(self, plan: SchedulerOutput, sampling: list[Request], tokens: torch.Tensor | None,
-                 host: torch.Tensor | None) -> None:
+                 host: torch.Tensor | None, has_status: bool = False) -> None:
         self.plan, self.sampling, self.tokens, self.host = plan, sampling, tokens, host
+        self.has_status = has_status
+        self.status: list[int] | None = None        # filled by wait()
         self.arrived: torch.cuda.Event | None = None
         if tokens is not None and host is not None:
             host[:tokens.shape[0]].copy_(tokens, non_blocking=True)
@@ -50,9 +54,11 @@ class _InFlight:
             return {}
         if self.arrived is not None:
             self.arrived.synchronize()
-            values = self.host[:len(self.sampling)].tolist()
+            values = self.host[:self.tokens.shape[0]].tolist()
         else:
             values = self.tokens.tolist()
+        if self.has_status:
+            self.status = values[len(self.sampling):]
         return {request.request_id: token for request, token in zip(self.sampling, values)}
 
 
@@ -63,6 +69,13 @@ class LLMEngine:
         self.runner = runner or ModelRunner.from_folder(
             model.model, model.dtype, cache.block_size, cache.num_gpu_blocks, sched.max_num_seqs,
             device=config.device, enable_prefix_caching=cache.enable_prefix_caching)
+        trained = getattr(self.runner.model_config, "max_position_embeddings", None)
+        if trained is not None and model.max_model_len > trained:
+            # minivllm/worker/worker.py:140: positions past the range the position encoding was
+            # trained for are refused (rotation angles are computed on the fly here, so nothing
+            # else would stop them).
+            raise ValueError(f"max_model_len={model.max_model_len} exceeds the model's "
+                             f"max_position_embeddings={trained}")
         self.scheduler = Scheduler(sched, self.runner.manager, model.max_model_len)
         self.sampler = Sampler(self.runner.model.vocab_size, self.runner.device)
         self._seed_source = random.Random(model.seed)
@@ -72,13 +85,22 @@ class LLMEngine:
         self.num_steps_ahead = 0            # steps queued before their input tokens reached the host
         self._pending: _InFlight | None = None
         self._host_tokens: list[torch.Tensor] = []
+        # Every step that samples brings the kernels' error words to the host beside its ids.
+        self._carry_status = self.runner.device.type == "cuda"
         self.decode_graphs = None
         self.mixed_graphs = None
-        if not model.enforce_eager and self.runner.device.type == "cuda":
+        # Steps are replayed as CUDA graphs only if every part of the model says that it reads
+        # what differs between steps from device data (``Part.graph_safe``): a part that looks
+        # at the batch from the host would have its first step's values baked into a graph.
+        self.graphs_refused_by_parts = (not model.enforce_eager and self.runner.device.type == "cuda"
+                                        and not self.runner.model.graph_safe())
+        if not model.enforce_eager and self.runner.device.type == "cuda" and self.runner.model.graph_safe():
             from .decode_graph import DecodeGraphs, MixedGraphs
             self.decode_graphs = DecodeGraphs(self.runner, sched.max_num_seqs, model.max_model_len)
             if not self.runner.storage.has_state:
-                # (parts with state of their own may look at the step from the host)
+                # Prompt steps of models with per-request state stay on the ordinary path: the
+                # padding requests of a replayed prompt step bring no tokens at all, which a
+                # state-keeping part would have to know how to skip.
                 self.mixed_graphs = MixedGraphs(self.runner, model.max_model_len)
 
     # ----------------------------------------------------------------- requests
@@ -133,12 +155,21 @@ class LLMEngine:
                 self.num_steps += 1
                 self.num_steps_ahead += 1
                 self._pending = self._execute(ahead, previous=current)
-        outputs = self.scheduler.update(current.plan, current.wait())
+        sampled = current.wait()
+        if current.status is not None:
+            # The step's error words came with its ids: a step that fed a bad token id, or in which
+            # a kernel gave up a bounded wait, is refused before anything of it is committed,
+            # handed out or published to the prefix cache.
+            problem = kernels.status_problem(current.status, self.runner.model.vocab_size)
+            if problem:
+                self.runner.clear_device_errors()
+                raise RuntimeError(f"the step is void: {problem}")
+        outputs = self.scheduler.update(current.plan, sampled)
         idle = not self.scheduler.has_unfinished_requests()
         if self._pending is not None and idle:
             self._pending = None            # everyone stopped: what was queued ahead is of no use
-        if idle or self.num_steps % 256 == 0:
-            self.runner.check_device()      # error flags of the kernels, now and then and at the end
+        if idle:
+            self.runner.check_device()      # steps that sampled nothing (prompt portions) carry no words
         return outputs
 
     def _overlaps(self) -> bool:
@@ -150,7 +181,7 @@ class LLMEngine:
         if self.runner.device.type != "cuda":
             return None
         if not self._host_tokens:
-            size = max(rows, self.config.scheduler_config.max_num_seqs)
+            size = max(rows, self.config.scheduler_config.max_num_seqs + kernels.STATUS_WORDS)
             self._host_tokens = [torch.empty(size, dtype=torch.int32, pin_memory=True) for _ in range(2)]
         self._host_tokens.reverse()
         buffer = self._host_tokens[0]
@@ -185,11 +216,14 @@ class LLMEngine:
             self._first_inputs = self._describe_inputs(plan)
         if not sampling:
             return _InFlight(plan, [], None, None)
+        on_gpu = self._carry_status
         tokens = self.sampler.sample_device(
             logits, [r.sampling_params for r in sampling], [r.seed for r in sampling],
             [r.prompt_token_ids for r in sampling], [r.output_token_ids for r in sampling],
-            ahead=0 if previous is None else 1)
-        return _InFlight(plan, sampling, tokens, self._pinned(len(sampling)))
+            ahead=0 if previous is None else 1, extra=kernels.STATUS_WORDS if on_gpu else 0)
+        if on_gpu:
+            self.runner.write_status(tokens[len(sampling):])
+        return _InFlight(plan, sampling, tokens, self._pinned(tokens.shape[0]), has_status=on_gpu)
 
     # -------------------------------------------------------------------- trace
     def _describe_inputs(self, plan: SchedulerOutput) -> dict | None:

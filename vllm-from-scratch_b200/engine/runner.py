@@ -66,6 +66,18 @@ class ModelRunner:
     def step(self, entries: list[StepEntry]) -> torch.Tensor | None:
         return self.step_function.run(entries)
 
+    def write_status(self, out: torch.Tensor) -> None:
+        """The error words of the steps so far into ``out`` (int32 ``[kernels.STATUS_WORDS]`` on the
+        device), without waiting; read them on the host with ``kernels.status_problem``."""
+        from .. import kernels
+        kernels.collect_status(self.model._token_error, out)
+
+    def clear_device_errors(self) -> None:
+        """Reset the error words (after their content has been reported)."""
+        from .. import kernels
+        self.model._token_error.zero_()
+        kernels.device_error()
+
     def check_device(self) -> None:
         """Raise if a step since the last check fed a token id outside the vocabulary or
         a kernel gave up a bounded wait (waits for the device; not for every step)."""

@@ -66,6 +66,12 @@ class Scheduler:
     def add_request(self, request: Request) -> None:
         if request.request_id in self.requests:
             raise ValueError(f"request id {request.request_id!r} is already in use")
+        if request.request_id in self._finished_since_last:
+            # minivllm/core/sched/scheduler.py:163-170: an id may be used again only after the
+            # notice that its last holder has finished went out with a step's plan; until then
+            # one plan would name the id both as finished and as new.
+            raise ValueError(f"request id {request.request_id!r} has just finished and its notice has not "
+                             f"gone out with a step yet: use it again after the next step")
         if not request.prompt_token_ids:
             raise ValueError("a request needs at least one prompt token")
         if len(request.prompt_token_ids) >= self.max_model_len:

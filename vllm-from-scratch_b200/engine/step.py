@@ -16,8 +16,6 @@ through the cache manager before the step.
 
 from __future__ import annotations
 
-import os
-
 from dataclasses import dataclass, field
 
 import numpy as np
@@ -131,7 +129,7 @@ class StepFunction:
             "max_seq_len": int(seq_lens.max()), "query_start": query_start.tolist(),
             "seq_lens": seq_lens.tolist(), "slots": slots.tolist(),
             # single-token requests ahead of portions; 0 when the step has only one kind
-            "num_decode": num_decode if 0 < num_decode < real and "B200_NO_SPLIT_BATCH" not in os.environ else 0,
+            "num_decode": num_decode if 0 < num_decode < real else 0,
         }
         return host, meta
 

@@ -116,6 +116,50 @@ def device_error() -> str | None:
     return "; ".join(found) or None
 
 
+STATUS_WORDS = 3        # token-id flag, attention kernels' error word, matrix-product kernels' error word
+_status_addresses: dict[int, tuple[int, int]] = {}
+
+
+def collect_status(token_flag: torch.Tensor | None, out: torch.Tensor) -> None:
+    """Write the step's error words into ``out`` (int32 ``[STATUS_WORDS]`` on the device) without
+    waiting for anything: ``token_flag`` (the embedding kernel's word for a token id outside the
+    vocabulary) and the words that kernels with bounded waits set when they give up.  A caller
+    copies ``out`` to the host with results it waits for anyway and hands the values to
+    :func:`status_problem`.  Words of libraries that are not loaded read as 0."""
+    device = out.device.index if out.device.index is not None else torch.cuda.current_device()
+    attention = is_loaded("attention_bf16")
+    product = is_loaded("gemm_bf16")
+    cached = _status_addresses.get(device)
+    if cached is None or (attention and not cached[0]) or (product and not cached[1]):
+        a = b = 0
+        if attention:
+            fn = load_library("attention_bf16").b200_attention_error_address
+            fn.restype = ctypes.c_void_p
+            a = fn() or 0
+        if product:
+            fn = load_library("gemm_bf16").b200_stream_gemm_error_address
+            fn.restype = ctypes.c_void_p
+            b = fn() or 0
+        cached = _status_addresses[device] = (a, b)
+    _run("sampling", "b200_collect_status",
+         ctypes.c_void_p(token_flag.data_ptr() if token_flag is not None else 0), ctypes.c_void_p(cached[0]),
+         ctypes.c_void_p(cached[1]), ctypes.c_void_p(_check("status words", out, torch.int32, (STATUS_WORDS,))),
+         _stream())
+
+
+def status_problem(words: Sequence[int], vocab_size: int | None = None) -> str | None:
+    """What the words written by :func:`collect_status` say, or None if all is well."""
+    found = []
+    if words[0]:
+        found.append(f"token id outside the vocabulary{'' if vocab_size is None else f' [0, {vocab_size})'} "
+                     f"at batch row {words[0] - 1}")
+    if words[1]:
+        found.append(f"attention kernel gave up waiting (code {words[1]})")
+    if words[2]:
+        found.append(f"matrix-product kernel gave up waiting (code {words[2]})")
+    return "; ".join(found) or None
+
+
 _P = ctypes.c_void_p
 _I = ctypes.c_int
 _F = ctypes.c_float

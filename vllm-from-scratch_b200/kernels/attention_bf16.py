@@ -9,15 +9,43 @@ float32-arithmetic kernel, which takes every shape.
 from __future__ import annotations
 
 import ctypes
-import os
 
 import torch
 
 from ..csrc.build import load_library
 
-NUM_SMS = 148
 TC_MIN_QUERY_LEN = 64      # shorter portions go to the 64-row mma.sync kernel
+# Which kernel serves a shape that more than one takes.  Each default is the faster one; a test
+# sets a switch to False to drive the kernel behind it through the same call.
+USE_TMA_DECODE = True      # decode attention fed by tensor copies (pages of 8, 16, 32, ... keys)
+USE_FUSED_DECODE = True    # head norms, rotation and the store of the new key and value in the decode kernel
+USE_TC_ATTENTION = True    # tcgen05 / tensor-memory kernel for portions of TC_MIN_QUERY_LEN tokens and more
+USE_TC_KEY_SPLIT = True    # ... with the keys of a row block divided over several blocks where few blocks would run
 _P, _I, _F = ctypes.c_void_p, ctypes.c_int, ctypes.c_float
+
+
+_sm_count: dict[int, int] = {}
+
+
+def sm_count() -> int:
+    """Number of SMs of the current device, asked of the device once."""
+    device = torch.cuda.current_device()
+    count = _sm_count.get(device)
+    if count is None:
+        count = int(load_library("attention_bf16").b200_sm_count())
+        if count <= 0:
+            raise RuntimeError("could not read the number of SMs of the current device")
+        _sm_count[device] = count
+    return count
+
+
+def tensor_map_cache_self_check(count: int = 5000) -> int:
+    """Host-only check of the tensor-map cache: more maps than it holds are encoded over one
+    buffer (nothing is launched) and the first ones compared with fresh copies.  0 = sound."""
+    buffer = torch.empty(count * 16 + 64 * 64 * 2 + 256, dtype=torch.uint8, device="cuda")
+    lib = load_library("attention_bf16")
+    return int(lib.b200_tensor_map_cache_self_check(_P(buffer.data_ptr()), ctypes.c_longlong(buffer.numel()),
+                                                    _I(count)))
 
 
 def decode_splits(num_requests: int, num_kv_heads: int, max_seq_len: int) -> int:
@@ -26,7 +54,7 @@ def decode_splits(num_requests: int, num_kv_heads: int, max_seq_len: int) -> int
     whole rounds of the GPU (a last round with few blocks would leave it idle), with
     at least 512 keys per block at the planned length (256 for one or two requests)."""
     pairs = max(1, num_requests * num_kv_heads)
-    slots = 3 * NUM_SMS
+    slots = 3 * sm_count()
     best, best_fill = 1, 0.0
     # One or two requests cannot fill half of the GPU with 512 keys a block: they get 256
     # (a step at batch 1 takes 1.21 against 1.29 ms, at batch 2 1.27 against 1.31; from batch 4
@@ -55,7 +83,7 @@ def _decode(lib, q, k_pages, v_pages, out, seq_lens, block_table, num_q_heads, n
               _P(seq_lens.data_ptr()), _P(block_table.data_ptr()), _I(requests), _I(block_table.shape[1]),
               _I(num_q_heads), _I(num_kv_heads), _I(head_dim), _I(page_size))
     tail = (_F(scale), _I(window or 0), _I(splits), _stream())
-    if (os.environ.get("B200_NO_TMA_DECODE") is None
+    if (USE_TMA_DECODE
             and lib.b200_decode_attention_tma_supports(num_q_heads, num_kv_heads, head_dim, page_size)):
         # keys and values by tensor copies straight from the pages
         return lib.b200_decode_attention_tma_bf16(*common, _I(k_pages.shape[0]), *tail)
@@ -69,12 +97,14 @@ def _portions(lib, q, k_pages, v_pages, out, query_start, seq_lens, block_table,
     from . import _stream
     requests = seq_lens.shape[0]
     tokens = q.shape[0]
-    if (max_query_len >= TC_MIN_QUERY_LEN and os.environ.get("B200_NO_TC_ATTENTION") is None
+    if (max_query_len >= TC_MIN_QUERY_LEN and USE_TC_ATTENTION
             and lib.b200_prefill_attention_tc_supports(num_q_heads, num_kv_heads, head_dim, page_size)):
         # long portions of prompts: the tcgen05 / tensor-memory kernel; few row blocks over many
         # keys are divided over several blocks each, with partial results that a second kernel merges
-        splits = lib.b200_prefill_attention_tc_splits(_I(tokens - token_offset), _I(requests), _I(num_q_heads),
-                                                      _I(max_seq_len))
+        splits = 1
+        if USE_TC_KEY_SPLIT:
+            splits = lib.b200_prefill_attention_tc_splits(_I(tokens - token_offset), _I(requests), _I(num_q_heads),
+                                                          _I(max_seq_len))
         partial_o = partial_ml = None
         if splits > 1:
             partial_o = torch.empty((tokens * num_q_heads * splits, head_dim), dtype=torch.float32, device=q.device)
@@ -134,8 +164,8 @@ def fused_decode_attention_bf16(qkv, positions, slots, q_weight, k_weight, inv_f
     """A decode step's attention straight from the packed projection: head norms, rotation,
     the store of the new key and value, and the attention over the pages in one kernel (and
     the merge of the splits).  False if the shape is not one that kernel takes (or
-    ``B200_NO_FUSED_DECODE`` is set): the caller then runs the two kernels one after the other."""
-    if os.environ.get("B200_NO_FUSED_DECODE") is not None or os.environ.get("B200_NO_TMA_DECODE") is not None:
+    ``USE_FUSED_DECODE`` is off): the caller then runs the two kernels one after the other."""
+    if not (USE_FUSED_DECODE and USE_TMA_DECODE):
         return False
     lib = load_library("attention_bf16")
     if not lib.b200_decode_attention_fused_supports(num_q_heads, num_kv_heads, head_dim, rotary_dim, page_size):

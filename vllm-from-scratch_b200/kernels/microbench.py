@@ -90,8 +90,8 @@ def main(argv=None) -> int:
     parser.add_argument("--fused", action="store_true",
                         help="decode_attention: the kernel that takes the packed projection and also normalises "
                              "and rotates the heads and stores the new key and value")
-    parser.add_argument("--kernel", default="default", choices=("default", "tc", "library"),
-                        help="gemm: the engine's choice, the tcgen05 kernel, or the vendor library")
+    parser.add_argument("--kernel", default="default", choices=("default", "library"),
+                        help="gemm: the engine's choice or the vendor library")
     args = parser.parse_args(argv)
     dtype = torch.bfloat16 if args.dtype == "bfloat16" else torch.float32
     size = 2 if dtype == torch.bfloat16 else 4
@@ -140,10 +140,7 @@ def main(argv=None) -> int:
         copies = max(1, min(64, (512 * 1024 * 1024) // (args.n * args.k * size)))
         ws = [torch.randn(args.n, args.k, device="cuda").to(dtype) for _ in range(copies)]
         out = torch.empty(args.m, args.n // 2 if args.gated else args.n, device="cuda", dtype=dtype)
-        if args.kernel == "tc":
-            from . import gemm_bf16
-            one = lambda w: gemm_bf16.tc_gemm_bf16(x, w, out, gated=args.gated)
-        elif args.kernel == "library":
+        if args.kernel == "library":
             one = lambda w: torch.mm(x, w.t(), out=out)
         elif args.gated:
             one = lambda w: kernels.gated_silu_gemm(x, w, out)

@@ -31,10 +31,10 @@ def build_spec(config: Qwen3Config) -> ModelSpec:
                 "window": config.layer_windows[index],
                 "qk_norm_eps": config.rms_norm_eps,
             }, name="self_attn"),
-            mixer_norm=PartSpec("rms_norm", norm, name="input_layernorm"),
             feed_forward=PartSpec("gated_silu", {"intermediate_size": config.intermediate_size}, name="mlp"),
-            feed_forward_norm=PartSpec("rms_norm", norm, name="post_attention_layernorm"),
             position=PartSpec("rotary", {"theta": config.rope_theta, "rotary_dim": config.head_dim}),
+            norms={"mixer": PartSpec("rms_norm", norm, name="input_layernorm"),
+                   "feed_forward": PartSpec("rms_norm", norm, name="post_attention_layernorm")},
         ))
     return ModelSpec(
         hidden_size=config.hidden_size,

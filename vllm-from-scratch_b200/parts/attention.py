@@ -26,6 +26,8 @@ class PagedAttention(Mixer):
     ``head_dim ** -0.5``), ``window`` (None = all keys), ``qk_norm_eps`` (None =
     no per-head norm)."""
 
+    graph_safe = True
+
     def __init__(self, params: Mapping[str, Any], env: PartEnv, position: PositionEncoding) -> None:
         super().__init__(params, env, position)
         self.num_heads = int(params["num_heads"])

@@ -112,6 +112,13 @@ class CacheView:
 
 # ----------------------------------------------------------------------- parts
 class Part:
+    # Whether a step that runs this part may be captured into a CUDA graph and replayed with
+    # other batches: everything that differs from step to step must then reach the part as
+    # device data (the tensors of the StepContext), never as host values (its ``host_*``
+    # lists, ``.item()``, Python branches on the batch).  The engine replays graphs only for
+    # models all of whose parts say True; a part that does not say runs without graphs.
+    graph_safe: bool = False
+
     def __init__(self, params: Mapping[str, Any], env: PartEnv) -> None:
         self.params = params
         self.env = env
@@ -163,14 +170,54 @@ class FeedForward(Part):
         raise NotImplementedError
 
 
-class Block(Part):
-    """Arrangement of two norms, a mixer and a feed-forward around the residual."""
+class Embedding(Part):
+    """From token ids to the first content of the float32 residual stream.  params always
+    hold ``vocab_size``.  ``table()`` is the ``[vocab, hidden]`` matrix an output head that
+    is tied to the embedding multiplies by."""
 
-    def __init__(self, params: Mapping[str, Any], env: PartEnv, *, mixer: Mixer, mixer_norm: Norm,
-                 feed_forward: FeedForward, feed_forward_norm: Norm) -> None:
+    def forward(self, token_ids: torch.Tensor, ctx: StepContext, residual: torch.Tensor,
+                error_flag: torch.Tensor) -> None:
+        """Fill ``residual`` (float32 ``[T, hidden]``) for the int32 ``token_ids``; an id outside
+        the vocabulary sets ``error_flag[0]`` to 1 + its row and leaves zeros.  ``ctx`` is there
+        for embeddings that depend on more than the id (positions, for instance)."""
+        raise NotImplementedError
+
+    def table(self) -> torch.Tensor:
+        raise NotImplementedError
+
+
+class OutputHead(Part):
+    """From normalised rows of the residual stream to float32 logits.  params always hold
+    ``vocab_size``; ``tied`` (default False) says that the head owns no matrix and multiplies
+    by the embedding's, which the model hands over with ``bind_embedding``."""
+
+    def bind_embedding(self, embedding: Embedding) -> None:
+        """Called once after the weights are loaded."""
+
+    def forward(self, normed: torch.Tensor) -> torch.Tensor:
+        """``normed`` is ``[rows, hidden]`` in the run dtype; returns float32 ``[rows, vocab]``."""
+        raise NotImplementedError
+
+
+class Block(Part):
+    """Arrangement of norms, a mixer and (usually) a feed-forward around the residual.
+
+    ``norm_roles`` names the norms the arrangement uses; the layer's spec must bring a norm
+    for each of them and no other (``norms`` maps role -> built norm).  ``needs_feed_forward``
+    says whether a layer without a feed-forward is acceptable."""
+
+    norm_roles: tuple[str, ...] = ()
+    needs_feed_forward: bool = True
+
+    def __init__(self, params: Mapping[str, Any], env: PartEnv, *, mixer: Mixer,
+                 feed_forward: FeedForward | None, norms: Mapping[str, Norm]) -> None:
         super().__init__(params, env)
-        self.mixer, self.mixer_norm = mixer, mixer_norm
-        self.feed_forward, self.feed_forward_norm = feed_forward, feed_forward_norm
+        if set(norms) != set(self.norm_roles):
+            raise ValueError(f"block at {env.prefix!r} arranges norms {sorted(self.norm_roles)}, "
+                             f"the layer brings {sorted(norms)}")
+        if feed_forward is None and self.needs_feed_forward:
+            raise ValueError(f"block at {env.prefix!r} needs a feed-forward, the layer has none")
+        self.mixer, self.feed_forward, self.norms = mixer, feed_forward, dict(norms)
 
     def forward(self, x: torch.Tensor | None, residual: torch.Tensor, ctx: StepContext,
                 cache: CacheView) -> torch.Tensor:
@@ -213,3 +260,5 @@ FEED_FORWARDS = Registry("feed-forward")
 NORMS = Registry("norm")
 POSITION_ENCODINGS = Registry("position encoding")
 BLOCKS = Registry("block")
+EMBEDDINGS = Registry("embedding")
+OUTPUT_HEADS = Registry("output head")

@@ -13,9 +13,12 @@ from .base import BLOCKS, Block, CacheView, StepContext
 
 @BLOCKS.register("pre_norm")
 class PreNormBlock(Block):
+    norm_roles = ("mixer", "feed_forward")
+    graph_safe = True
+
     def forward(self, x: torch.Tensor | None, residual: torch.Tensor, ctx: StepContext,
                 cache: CacheView) -> torch.Tensor:
-        normed = self.mixer_norm.forward(x, residual)
+        normed = self.norms["mixer"].forward(x, residual)
         mixed = self.mixer.forward(normed, ctx, cache)
-        normed = self.feed_forward_norm.forward(mixed, residual)
+        normed = self.norms["feed_forward"].forward(mixed, residual)
         return self.feed_forward.forward(normed, ctx)

@@ -17,6 +17,8 @@ from .base import FEED_FORWARDS, FeedForward, PartEnv, StepContext, WeightInfo
 class GatedSiluFeedForward(FeedForward):
     """params: ``intermediate_size``."""
 
+    graph_safe = True
+
     def __init__(self, params: Mapping[str, Any], env: PartEnv) -> None:
         super().__init__(params, env)
         self.intermediate_size = int(params["intermediate_size"])

@@ -15,8 +15,8 @@ from typing import Mapping
 import torch
 
 from .. import kernels
-from .base import (BLOCKS, FEED_FORWARDS, MIXERS, NORMS, POSITION_ENCODINGS, Block, CacheView,
-                   KVPagesNeed, PartEnv, StateNeed, StepContext, WeightInfo)
+from .base import (BLOCKS, EMBEDDINGS, FEED_FORWARDS, MIXERS, NORMS, OUTPUT_HEADS, POSITION_ENCODINGS, Block,
+                   CacheView, KVPagesNeed, PartEnv, StateNeed, StepContext, WeightInfo)
 from .spec import LayerSpec, ModelSpec
 
 
@@ -36,9 +36,11 @@ class DecoderModel:
         self.layers: list[Block] = [self._build_layer(layer) for layer in spec.layers]
         self.final_norm = NORMS.get(spec.final_norm.kind)(
             spec.final_norm.params, self._env(spec.final_norm.name))
-        self.tied_output = bool(spec.output_head.params.get("tied", False))
-        self.embedding: torch.Tensor | None = None
-        self.output_weight: torch.Tensor | None = None
+        sizes = {"vocab_size": spec.vocab_size}
+        self.embedding = EMBEDDINGS.get(spec.embedding.kind)(
+            {**sizes, **spec.embedding.params}, self._env(spec.embedding.name))
+        self.output_head = OUTPUT_HEADS.get(spec.output_head.kind)(
+            {**sizes, **spec.output_head.params}, self._env(spec.output_head.name))
         self._token_error = torch.zeros(1, dtype=torch.int32, device=self.device)
 
     # ---------------------------------------------------------------- assembly
@@ -50,28 +52,29 @@ class DecoderModel:
             return self._env(_join(layer.name, part.name))
         position = POSITION_ENCODINGS.get(layer.position.kind)(layer.position.params, env(layer.position))
         mixer = MIXERS.get(layer.mixer.kind)(layer.mixer.params, env(layer.mixer), position)
-        mixer_norm = NORMS.get(layer.mixer_norm.kind)(layer.mixer_norm.params, env(layer.mixer_norm))
-        feed_forward = FEED_FORWARDS.get(layer.feed_forward.kind)(
-            layer.feed_forward.params, env(layer.feed_forward))
-        feed_forward_norm = NORMS.get(layer.feed_forward_norm.kind)(
-            layer.feed_forward_norm.params, env(layer.feed_forward_norm))
+        norms = {role: NORMS.get(part.kind)(part.params, env(part)) for role, part in layer.norms.items()}
+        feed_forward = None
+        if layer.feed_forward is not None:
+            feed_forward = FEED_FORWARDS.get(layer.feed_forward.kind)(
+                layer.feed_forward.params, env(layer.feed_forward))
         return BLOCKS.get(layer.block.kind)(
-            layer.block.params, env(layer.block), mixer=mixer, mixer_norm=mixer_norm,
-            feed_forward=feed_forward, feed_forward_norm=feed_forward_norm)
+            layer.block.params, env(layer.block), mixer=mixer, feed_forward=feed_forward, norms=norms)
 
     def _parts(self):
+        yield self.embedding
         for block in self.layers:
-            yield from (block, block.mixer_norm, block.mixer, block.feed_forward_norm, block.feed_forward)
-        yield self.final_norm
+            yield from (block, block.mixer, block.mixer.position, *block.norms.values())
+            if block.feed_forward is not None:
+                yield block.feed_forward
+        yield from (self.final_norm, self.output_head)
+
+    def graph_safe(self) -> bool:
+        """Whether every part says that steps through it may be replayed as CUDA graphs."""
+        return all(part.graph_safe for part in self._parts())
 
     # ----------------------------------------------------------------- weights
     def expected_weights(self) -> dict[str, WeightInfo]:
-        names: dict[str, WeightInfo] = {
-            _join(self.spec.embedding.name, "weight"): WeightInfo((self.vocab_size, self.hidden_size)),
-        }
-        if not self.tied_output:
-            names[_join(self.spec.output_head.name, "weight")] = WeightInfo(
-                (self.vocab_size, self.hidden_size))
+        names: dict[str, WeightInfo] = {}
         for part in self._parts():
             for name, info in part.expected_weights().items():
                 names[_join(part.env.prefix, name)] = info
@@ -79,7 +82,7 @@ class DecoderModel:
 
     def ignored_weights(self) -> set[str]:
         ignored = set(self.spec.ignored_weights)
-        if self.tied_output:
+        if getattr(self.output_head, "tied", False):
             # A tied checkpoint may still carry the output matrix; it is not read
             # (minivllm/models/qwen3.py:427-430).
             ignored.add(_join(self.spec.output_head.name, "weight"))
@@ -88,25 +91,20 @@ class DecoderModel:
     def load_weights(self, tensors: Mapping[str, torch.Tensor]) -> None:
         """``tensors``: full checkpoint name -> tensor on the device in the dtype
         its kind asks for (see ``weights.loader``)."""
-        self.embedding = tensors[_join(self.spec.embedding.name, "weight")].contiguous()
-        self.output_weight = (self.embedding if self.tied_output else
-                              tensors[_join(self.spec.output_head.name, "weight")].contiguous())
         for part in self._parts():
             wanted = part.expected_weights()
             if wanted:
                 part.load_weights({name: tensors[_join(part.env.prefix, name)] for name in wanted})
+        self.output_head.bind_embedding(self.embedding)
 
     def num_weight_bytes(self) -> int:
+        """Bytes of all distinct weight tensors the parts hold (a tied matrix counts once)."""
         seen, total = set(), 0
         for part in self._parts():
             for value in vars(part).values():
                 if isinstance(value, torch.Tensor) and value.data_ptr() not in seen:
                     seen.add(value.data_ptr())
                     total += value.numel() * value.element_size()
-        for value in (self.embedding, self.output_weight):
-            if value is not None and value.data_ptr() not in seen:
-                seen.add(value.data_ptr())
-                total += value.numel() * value.element_size()
         return total
 
     # ------------------------------------------------------------------- cache
@@ -126,7 +124,7 @@ class DecoderModel:
         not-yet-added output and the float32 residual stream."""
         tokens = token_ids.shape[0]
         residual = torch.empty((tokens, self.hidden_size), dtype=torch.float32, device=token_ids.device)
-        kernels.embedding(self.embedding, token_ids, residual, self._token_error)
+        self.embedding.forward(token_ids, ctx, residual, self._token_error)
         x: torch.Tensor | None = None
         for entry, cache in zip(self.spec.schedule, caches):
             x = self.layers[entry.layer].forward(x, residual, ctx, cache)
@@ -134,10 +132,7 @@ class DecoderModel:
 
     def logits(self, x: torch.Tensor | None, residual: torch.Tensor, rows: torch.Tensor) -> torch.Tensor:
         """float32 logits ``[len(rows), vocab]`` at the given token rows."""
-        normed = self.final_norm.forward(x, residual, rows=rows)
-        out = torch.empty((rows.shape[0], self.vocab_size), dtype=torch.float32, device=residual.device)
-        kernels.gemm(normed, self.output_weight, out)
-        return out
+        return self.output_head.forward(self.final_norm.forward(x, residual, rows=rows))
 
     def check_token_ids(self) -> None:
         """Raise if a step since the last check met a token id outside the vocabulary."""

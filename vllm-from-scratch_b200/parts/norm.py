@@ -19,6 +19,8 @@ from .base import NORMS, Norm, PartEnv, WeightInfo
 class RMSNorm(Norm):
     """params: ``eps`` (inside the root), ``size`` (defaults to the residual width)."""
 
+    graph_safe = True
+
     def __init__(self, params: Mapping[str, Any], env: PartEnv) -> None:
         super().__init__(params, env)
         self.eps = float(params["eps"])

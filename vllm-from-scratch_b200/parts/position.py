@@ -25,6 +25,8 @@ class RotaryPositionEncoding(PositionEncoding):
     """params: ``theta`` (base), ``rotary_dim`` (channels rotated, even),
     ``scaling_factor`` (positions are divided by it; 1.0 = plain)."""
 
+    graph_safe = True
+
     def __init__(self, params: Mapping[str, Any], env: PartEnv) -> None:
         super().__init__(params, env)
         self.theta = float(params["theta"])
@@ -45,3 +47,4 @@ class RotaryPositionEncoding(PositionEncoding):
 @POSITION_ENCODINGS.register("none")
 class NoPositionEncoding(PositionEncoding):
     rotary_dim = 0
+    graph_safe = True

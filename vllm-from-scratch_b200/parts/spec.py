@@ -33,15 +33,29 @@ class PartSpec:
 
 @dataclass(frozen=True)
 class LayerSpec:
-    """One layer's parts.  ``name`` is the prefix of its tensors in the checkpoint."""
+    """One layer's parts.  ``name`` is the prefix of its tensors in the checkpoint.
+
+    ``norms`` maps the role a norm plays in the block's arrangement to its part: the
+    pre-norm arrangement asks for ``"mixer"`` and ``"feed_forward"`` (the norms in front
+    of each), an arrangement with norms behind them as well would ask for four names.
+    Which roles there are is the block kind's business (``Block.norm_roles``); the model
+    checks that the layer brings exactly those.  ``feed_forward`` may be None for an
+    arrangement that has none.
+    """
 
     name: str
-    block: PartSpec                   # how norm, mixer and feed-forward are arranged
+    block: PartSpec                   # how norms, mixer and feed-forward are arranged
     mixer: PartSpec                   # token mixing (attention here)
-    mixer_norm: PartSpec              # norm in front of the mixer
-    feed_forward: PartSpec            # dense or experts
-    feed_forward_norm: PartSpec       # norm in front of the feed-forward
+    feed_forward: PartSpec | None     # dense or experts
     position: PartSpec                # position encoding handed to the mixer
+    norms: Mapping[str, PartSpec] = field(default_factory=dict)
+
+    def __post_init__(self) -> None:
+        object.__setattr__(self, "norms", MappingProxyType(dict(self.norms)))
+
+    def __hash__(self) -> int:
+        return hash((self.name, self.block, self.mixer, self.feed_forward, self.position,
+                     tuple(sorted(self.norms.items()))))
 
 
 @dataclass(frozen=True)

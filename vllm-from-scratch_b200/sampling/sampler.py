@@ -37,11 +37,14 @@ class Sampler:
         tokens = self.sample_device(logits, params, seeds, prompts, outputs)
         return tokens.tolist()
 
-    def sample_device(self, logits, params, seeds, prompts, outputs, ahead: int = 0) -> torch.Tensor:
+    def sample_device(self, logits, params, seeds, prompts, outputs, ahead: int = 0,
+                      extra: int = 0) -> torch.Tensor:
         """The sampled ids as an int32 tensor on the device, without waiting for them.
         ``ahead``: how many output tokens of every row are still on their way to the
         host and so missing from ``outputs`` (they count for the draw index and for
-        ``min_tokens``; rows with penalties cannot be sampled ahead)."""
+        ``min_tokens``; rows with penalties cannot be sampled ahead).  ``extra``: that
+        many more int32 words are allocated behind the ids for the caller to fill (the
+        step's status words, so that one copy brings both to the host)."""
         rows = logits.shape[0]
         if rows != len(params):
             raise ValueError(f"{rows} rows of logits for {len(params)} requests")
@@ -55,10 +58,10 @@ class Sampler:
         min_p = np.array([p.min_p for p in params], dtype=np.float32)
         seed = np.array([s & 0x7FFFFFFFFFFFFFFF for s in seeds], dtype=np.int64)
         draw = np.array([len(o) + ahead for o in outputs], dtype=np.int64)
-        tokens = torch.empty(rows, dtype=torch.int32, device=logits.device)
+        tokens = torch.empty(rows + extra, dtype=torch.int32, device=logits.device)
         kernels.sample(logits, self._to_device(temperature), self._to_device(top_k),
                        self._to_device(top_p), self._to_device(min_p), self._to_device(seed),
-                       self._to_device(draw), tokens, GREEDY_EPS)
+                       self._to_device(draw), tokens[:rows], GREEDY_EPS)
         return tokens
 
     def _penalties(self, logits, params, prompts, outputs) -> None:
