@@ -67,6 +67,14 @@ class CacheStorage:
             else:
                 self.views.append(owner_view.get(index, CacheView("none")))
 
+    @staticmethod
+    def bytes_per_page(needs: list[KVPagesNeed | StateNeed | None], page_size: int, dtype: torch.dtype) -> int:
+        """Memory one page number costs over all executions that own a cache of pages (every
+        group's pool has the same number of pages, so a page number exists once in each)."""
+        element = torch.empty((), dtype=dtype).element_size()
+        return sum(2 * need.num_kv_heads * page_size * need.head_dim * element
+                   for need in needs if isinstance(need, KVPagesNeed))
+
     @property
     def group_windows(self) -> list[int | None]:
         return [group.need.window for group in self.groups]

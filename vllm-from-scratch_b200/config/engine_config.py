@@ -43,14 +43,19 @@ class ModelConfig:
 @dataclass(frozen=True)
 class CacheConfig:
     block_size: int = 16            # tokens per page
-    num_gpu_blocks: int = 64        # pages in each group's pool (no memory profiling)
+    # Pages in each group's pool.  None: as many as fit into ``gpu_memory_utilization`` of the
+    # device memory that is free once the weights are loaded (the reference always takes a number).
+    num_gpu_blocks: int | None = 64
     enable_prefix_caching: bool = False
+    gpu_memory_utilization: float = 0.9
 
     def __post_init__(self) -> None:
         if self.block_size <= 0:
             raise ValueError(f"block_size must be positive, got {self.block_size}")
-        if self.num_gpu_blocks <= 0:
+        if self.num_gpu_blocks is not None and self.num_gpu_blocks <= 0:
             raise ValueError(f"num_gpu_blocks must be positive, got {self.num_gpu_blocks}")
+        if not 0.0 < self.gpu_memory_utilization <= 1.0:
+            raise ValueError(f"gpu_memory_utilization must be in (0, 1], got {self.gpu_memory_utilization}")
 
 
 @dataclass(frozen=True)
@@ -60,8 +65,11 @@ class SchedulerConfig:
     policy: str = "fcfs"                # or "priority"
     # Queue the next decode step on the GPU before the tokens of the running one have
     # come back to the host (they are fed on the device); what a stopped request
-    # computed one step too far is thrown away.  The reference has no such mode.
-    async_scheduling: bool = False
+    # computed one step too far is thrown away.  On by default: the same tokens, a fifth
+    # more of them a second at batch 8 (the host's part of a step hides behind the GPU's).
+    # It takes effect where decode steps are graph replays on a CUDA device and falls back
+    # step by step otherwise.  The reference has no such mode.
+    async_scheduling: bool = True
 
     def __post_init__(self) -> None:
         if self.max_num_seqs <= 0:

@@ -39,8 +39,9 @@ def build_parser() -> argparse.ArgumentParser:
     parser.add_argument("--max-num-seqs", type=int, default=2)
     parser.add_argument("--max-num-batched-tokens", type=int, default=64)
     parser.add_argument("--enforce-eager", action="store_true", help="no CUDA-graph replay of decode steps")
-    parser.add_argument("--async-scheduling", action="store_true",
-                        help="queue the next decode step before the running one's tokens are back (not in the reference)")
+    parser.add_argument("--no-async-scheduling", action="store_true",
+                        help="wait for a step's tokens before the next step is queued (the reference's only "
+                             "mode; by default the next decode step is queued ahead)")
     parser.add_argument("--block-size", type=int, default=16)
     parser.add_argument("--num-kv-blocks", type=int, default=64)
     parser.add_argument("--no-prefix-caching", action="store_true")
@@ -105,7 +106,7 @@ def main(argv=None) -> int:
         engine.ModelConfig(str(model_dir), args.dtype, args.max_model_len, args.enforce_eager),
         engine.CacheConfig(args.block_size, args.num_kv_blocks, not args.no_prefix_caching),
         engine.SchedulerConfig(args.max_num_seqs, args.max_num_batched_tokens,
-                               async_scheduling=args.async_scheduling), "cuda"))
+                               async_scheduling=not args.no_async_scheduling), "cuda"))
     load_seconds = time.perf_counter() - started
     runner = llm.runner
     config = runner.model_config

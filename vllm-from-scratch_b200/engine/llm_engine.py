@@ -68,7 +68,8 @@ class LLMEngine:
         model, cache, sched = config.model_config, config.cache_config, config.scheduler_config
         self.runner = runner or ModelRunner.from_folder(
             model.model, model.dtype, cache.block_size, cache.num_gpu_blocks, sched.max_num_seqs,
-            device=config.device, enable_prefix_caching=cache.enable_prefix_caching)
+            device=config.device, enable_prefix_caching=cache.enable_prefix_caching,
+            gpu_memory_utilization=cache.gpu_memory_utilization)
         trained = getattr(self.runner.model_config, "max_position_embeddings", None)
         if trained is not None and model.max_model_len > trained:
             # minivllm/worker/worker.py:140: positions past the range the position encoding was
@@ -256,7 +257,7 @@ class LLM:
                  block_size: int = 16, num_gpu_blocks: int | None = None, max_num_seqs: int = 8,
                  max_num_batched_tokens: int = 2048, enable_prefix_caching: bool = False,
                  enforce_eager: bool = False, seed: int = 0, device: str = "cuda",
-                 async_scheduling: bool = False) -> None:
+                 async_scheduling: bool = True) -> None:
         if num_gpu_blocks is None:
             num_gpu_blocks = max_num_seqs * -(-max_model_len // block_size)
         self.engine = LLMEngine(EngineConfig(

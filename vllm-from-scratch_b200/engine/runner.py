@@ -31,9 +31,15 @@ def require_device(device: str | torch.device) -> torch.device:
 
 
 class ModelRunner:
+    """``num_pages=None`` sizes the pool from the device memory that is free once the weights are
+    loaded: ``gpu_memory_utilization`` of it, less ``reserve_bytes`` for the activations and graphs
+    of the steps to come, divided by what a page costs over all layers (the reference takes the
+    number from its caller, ``--num-kv-blocks``, minivllm/demo.py:110; it profiles nothing)."""
+
     def __init__(self, spec: ModelSpec, weights: str | Path | Mapping[str, torch.Tensor], dtype: str,
-                 page_size: int, num_pages: int, max_requests: int, device: str | torch.device = "cuda",
-                 enable_prefix_caching: bool = False, model_config=None) -> None:
+                 page_size: int, num_pages: int | None, max_requests: int, device: str | torch.device = "cuda",
+                 enable_prefix_caching: bool = False, model_config=None, gpu_memory_utilization: float = 0.9,
+                 reserve_bytes: int = 4 << 30) -> None:
         self.device = require_device(device)
         self.dtype = _TORCH_DTYPE[dtype]
         self.model_config = model_config
@@ -47,21 +53,53 @@ class ModelRunner:
             load_weights_from_tensors(self.model, weights)
         else:
             load_weights(self.model, weights)
-        cache_from = [entry.cache_from for entry in spec.schedule]
+        self.spec = spec
+        self.max_requests = max_requests
+        self.enable_prefix_caching = enable_prefix_caching
+        if num_pages is None:
+            num_pages = self.pages_that_fit(page_size, gpu_memory_utilization, reserve_bytes)
+        self.rebuild_cache(page_size, num_pages)
+
+    def rebuild_cache(self, page_size: int, num_pages: int) -> None:
+        """A new, empty cache of ``num_pages`` pages (memory, books and step function); what the
+        old one held is gone.  For a caller that sizes the pool after it has let go of memory
+        of its own: ``runner.rebuild_cache(page, runner.pages_that_fit(page))``."""
+        self.storage = self.manager = self.step_function = None
+        cache_from = [entry.cache_from for entry in self.spec.schedule]
         self.storage = CacheStorage(self.model.cache_needs(), cache_from, page_size, num_pages,
-                                    max_requests, self.dtype, self.device)
-        self.manager = CacheManager(self.storage.group_windows, page_size, num_pages, max_requests,
-                                    enable_prefix_caching, has_state=self.storage.has_state)
+                                    self.max_requests, self.dtype, self.device)
+        self.manager = CacheManager(self.storage.group_windows, page_size, num_pages, self.max_requests,
+                                    self.enable_prefix_caching, has_state=self.storage.has_state)
         self.step_function = StepFunction(self.model, self.storage, self.manager)
 
+    def pages_that_fit(self, page_size: int, gpu_memory_utilization: float = 0.9,
+                       reserve_bytes: int = 4 << 30) -> int:
+        """How many pages the free memory of the device holds now (call it after the weights are
+        loaded and whatever else must stay has been allocated)."""
+        if self.device.type != "cuda":
+            raise ValueError("the pool can be sized from free memory on a CUDA device only: give num_pages")
+        if not 0.0 < gpu_memory_utilization <= 1.0:
+            raise ValueError(f"gpu_memory_utilization must be in (0, 1], got {gpu_memory_utilization}")
+        torch.cuda.synchronize(self.device)
+        torch.cuda.empty_cache()
+        free, _ = torch.cuda.mem_get_info(self.device)
+        per_page = CacheStorage.bytes_per_page(self.model.cache_needs(), page_size, self.dtype)
+        if per_page == 0:
+            return 1
+        pages = int((free * gpu_memory_utilization - reserve_bytes) // per_page)
+        if pages < 1:
+            raise RuntimeError(f"{free / 2**30:.1f} GiB are free on {self.device}: no room for a cache page of "
+                               f"{per_page / 2**20:.2f} MiB beside the reserve of {reserve_bytes / 2**30:.1f} GiB")
+        return pages
+
     @classmethod
-    def from_folder(cls, folder: str | Path, dtype: str, page_size: int, num_pages: int,
+    def from_folder(cls, folder: str | Path, dtype: str, page_size: int, num_pages: int | None,
                     max_requests: int, device: str | torch.device = "cuda",
-                    enable_prefix_caching: bool = False) -> "ModelRunner":
+                    enable_prefix_caching: bool = False, gpu_memory_utilization: float = 0.9) -> "ModelRunner":
         require_device(device)
         entry, config = load_model_config(folder)
         return cls(entry.build_spec(config), folder, dtype, page_size, num_pages, max_requests, device,
-                   enable_prefix_caching, model_config=config)
+                   enable_prefix_caching, model_config=config, gpu_memory_utilization=gpu_memory_utilization)
 
     def step(self, entries: list[StepEntry]) -> torch.Tensor | None:
         return self.step_function.run(entries)
