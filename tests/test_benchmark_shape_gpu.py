@@ -5,7 +5,8 @@ query heads on 8 key/value heads of 128, a feed-forward of 6144, a vocabulary of
 (the output product over it, the resident-rows products at K = 6144, the library's
 products from 17 rows on, the tcgen05 attention inside a graph planned for a longer
 context, decode graphs of 16 and 64 requests).  Here the model has these widths and 2 of
-the 28 layers (fewer layers, not smaller ones), random weights drawn on the GPU, and
+the 28 layers (fewer layers, not smaller ones; the two wider shapes the benchmark also
+measures run one layer of their 36 and 64), random weights drawn on the GPU, and
 every comparison is with ``plain_qwen3`` run on the GPU in float32 with the reduced-
 precision matrix modes off: full against portions against token by token against the
 oracle, as the reference's own check does (benchmarks/check_step57_model_logits.py:
@@ -41,10 +42,11 @@ SHAPES = {
 SHAPE = SHAPES["1.7b"][0]
 PAGE = 16
 LENGTHS = {"a": 600, "b": 330, "c": 131, "d": 70, "e": 520}
-# Bounds as fractions of the largest logit of the sequence.  float32: sums taken in another
-# order over K = 2048 and 6144.  bfloat16: activations carry 8 bits.
-F32_REL = 1e-4
-BF16_REL = 0.03
+# Bounds as fractions of the largest logit of the sequence, twice the worst seen over all shapes and
+# cuts.  float32 (sums taken in another order over K of 2048 to 25600): worst 5.4e-6.  bfloat16
+# (activations carry 8 bits): worst 1.19e-2.
+F32_REL = 1.2e-5
+BF16_REL = 0.024
 
 
 def build_world(name):

@@ -86,7 +86,7 @@ def test_bfloat16_greedy_generation_matches_plain(folders, name, page, eager):
             top = torch.topk(logits, 2)
             if got != int(top.indices[0]):
                 margin = float(top.values[0] - top.values[1])
-                assert margin < 2 * 0.03 * float(logits.abs().max()), (
+                assert margin < 2 * tiny_configs.BF16_REL[name] * float(logits.abs().max()), (
                     f"{name} prompt of {len(prompt)}: token {place} is {got}, plain says {int(top.indices[0])} "
                     f"(margin {margin:.3e})")
                 flipped = True
@@ -208,7 +208,7 @@ def test_long_decoding_and_first_tokens(folders):
         steps = [[("r", 1)] for _ in range(len(tokens))]
         result = helpers.run_schedule(runner, {"r": tokens}, steps)["r"]
         diff = (result - reference).abs().max(dim=1).values
-        bound = 2e-5 if dtype == "float32" else 0.03 * float(reference.abs().max())
+        bound = tiny_configs.F32_ATOL if dtype == "float32" else tiny_configs.BF16_REL["B"] * float(reference.abs().max())
         assert float(diff.max()) <= bound, (dtype, int(diff.argmax()), float(diff.max()))
         assert float(diff[:4].max()) <= bound
 

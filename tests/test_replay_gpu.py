@@ -28,14 +28,9 @@ LENGTHS = {
     "D": {"a": 70, "b": 145, "c": 100, "d": 37, "e": 64, "f": 2, "g": 410},
     "E": {"a": 70, "b": 145, "c": 100, "d": 37, "e": 64, "f": 2, "g": 330},
 }
-# float32: rounding of sums taken in another order.  bfloat16: activations carry
-# 8 bits; the bound is a fraction of the largest logit of the sequence.
-F32_ATOL = 2e-5
-BF16_REL = 0.03
-
-
-def tolerance(dtype: str, reference: torch.Tensor) -> float:
-    return F32_ATOL if dtype == "float32" else BF16_REL * float(reference.abs().max())
+# The bounds (tiny_configs.F32_ATOL, BF16_REL) are twice the worst difference seen.
+def tolerance(dtype: str, reference: torch.Tensor, name: str) -> float:
+    return tiny_configs.F32_ATOL if dtype == "float32" else tiny_configs.BF16_REL[name] * float(reference.abs().max())
 
 
 @pytest.fixture(scope="module")
@@ -70,7 +65,7 @@ def compare(results, expected, dtype, what):
         reference = expected[rid]
         assert logits.shape == reference.shape, (what, rid, logits.shape, reference.shape)
         diff = (logits - reference).abs()
-        bound = tolerance(dtype, reference)
+        bound = tolerance(dtype, reference, what[0])
         if float(diff.max()) > bound:
             position = int(diff.max(dim=1).values.gt(bound).nonzero()[0])
             raise AssertionError(
@@ -210,7 +205,7 @@ def test_trace_run_program(folders, references, tmp_path, dtype):
             n = len(entry["tokens"])
             reference = expected[dtype][entry["id"]][done[entry["id"]]:done[entry["id"]] + n]
             diff = (torch.from_numpy(data[at:at + n].copy()) - reference).abs().max()
-            assert float(diff) <= tolerance(dtype, reference), (line["step"], entry["id"], float(diff))
+            assert float(diff) <= tolerance(dtype, reference, name), (line["step"], entry["id"], float(diff))
             at += n
             done[entry["id"]] += n
         assert at == data.shape[0]

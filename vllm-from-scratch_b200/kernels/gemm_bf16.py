@@ -28,12 +28,27 @@ SKINNY_MAX_ROWS = 8
 # to 16 token rows: a decode step at batch 12 takes 1.89 against 2.08 ms, at batch 16 2.05 against 2.22.
 RESIDENT_MAX_ROWS = 16
 SKINNY_MAX_WEIGHT_ROWS = 8192
+# The engine's own few-rows kernels win on the short products of a small model's layer, where
+# the wait for the first bytes is most of the time and their copies start before the kernel ahead
+# has finished.  A matrix of tens of megabytes streams long enough for that not to matter, and
+# there the library's kernels are ahead (8 token rows, cold weights, microseconds own / library):
+# 6144 x 4096 14.7 / 11.1, 4096 x 12288 37.6 / 30.3, 10240 x 5120 29.5 / 20.6, 5120 x 8192
+# 32.4 / 17.4, 5120 x 25600 113 / 47, gated 24576 x 4096 60.7 / 36.9 (plus the activation
+# kernel); the output product over 151936 x 2048 takes the library 105.6 us, 0.90 of the copy
+# bandwidth.  Matrices above these sizes go to the library.
+OWN_MAX_WEIGHT_BYTES = 40 << 20
+OWN_MAX_GATED_WEIGHT_BYTES = 64 << 20
 _P, _I = ctypes.c_void_p, ctypes.c_int
 
 
 def _skinny_ok(m: int, n: int, k: int, *tensors: torch.Tensor) -> bool:
     return (1 <= m <= SKINNY_MAX_ROWS and n <= SKINNY_MAX_WEIGHT_ROWS and k >= 32 and k % 32 == 0
             and all(t.data_ptr() % 16 == 0 for t in tensors))
+
+
+def _small_enough(w: torch.Tensor, gated: bool) -> bool:
+    limit = OWN_MAX_GATED_WEIGHT_BYTES if gated else OWN_MAX_WEIGHT_BYTES
+    return w.numel() * w.element_size() <= limit
 
 
 def _resident_ok(m: int, k: int, gated: bool, *tensors: torch.Tensor) -> bool:
@@ -57,7 +72,8 @@ def _skinny(x, w, out, gated_inter: int) -> None:
 
 
 def gemm_bf16(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor) -> None:
-    if (_skinny_ok(x.shape[0], w.shape[0], x.shape[1], x, w, out)
+    if _small_enough(w, False) and (
+            _skinny_ok(x.shape[0], w.shape[0], x.shape[1], x, w, out)
             or (w.shape[0] <= SKINNY_MAX_WEIGHT_ROWS and _resident_ok(x.shape[0], x.shape[1], False, x, w, out))):
         _skinny(x, w, out, 0)
     elif out.dtype == torch.bfloat16:
@@ -70,7 +86,8 @@ def gemm_bf16(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor) -> None:
 def gated_silu_gemm_bf16(x: torch.Tensor, w_gate_up: torch.Tensor, out: torch.Tensor) -> bool:
     """``out = silu(x w[:I]^T) * (x w[I:]^T)`` in one kernel; False if the shape is
     not one the fused kernel takes (the caller then does it in two steps)."""
-    if not (_skinny_ok(x.shape[0], w_gate_up.shape[0], x.shape[1], x, w_gate_up, out)
+    if not _small_enough(w_gate_up, True) or not (
+            _skinny_ok(x.shape[0], w_gate_up.shape[0], x.shape[1], x, w_gate_up, out)
             or _resident_ok(x.shape[0], x.shape[1], True, x, w_gate_up, out)):
         return False
     _skinny(x, w_gate_up, out, out.shape[1])
