@@ -436,6 +436,10 @@ TENSOR_MEMORY_ATTENTION_SHAPES = [
     (2, 1, 128, 16, [384, 100], [2500, 1100], 700),
     (16, 8, 128, 16, [512], [8192], None),
     (1, 1, 128, 16, [64, 300], [3000, 300], None),
+    # a whole prompt: the row blocks far from its beginning are divided, the first ones are not
+    (16, 8, 128, 16, [2048], [2048], None),
+    (8, 4, 128, 16, [1000, 700], [1000, 2000], None),
+    (4, 2, 128, 32, [1300], [1300], 500),
 ]
 
 

@@ -90,6 +90,14 @@ def main(argv=None) -> int:
     parser.add_argument("--fused", action="store_true",
                         help="decode_attention: the kernel that takes the packed projection and also normalises "
                              "and rotates the heads and stores the new key and value")
+    parser.add_argument("--past", type=int, default=0,
+                        help="prefill_attention: positions the request has in the cache ahead of its --tokens")
+    parser.add_argument("--no-key-split", action="store_true",
+                        help="prefill_attention: never divide a row block's keys over several blocks")
+    parser.add_argument("--no-tensor-memory", action="store_true",
+                        help="prefill_attention: the mma.sync kernel instead of the tcgen05 one")
+    parser.add_argument("--no-tma-decode", action="store_true",
+                        help="decode_attention: the kernel with per-thread copies instead of tensor copies")
     parser.add_argument("--kernel", default="default", choices=("default", "library"),
                         help="gemm: the engine's choice or the vendor library")
     args = parser.parse_args(argv)
@@ -99,10 +107,14 @@ def main(argv=None) -> int:
     record: dict = {"op": args.op, "dtype": args.dtype}
 
     if args.op in ("decode_attention", "prefill_attention"):
+        from . import attention_bf16
+        attention_bf16.USE_TC_KEY_SPLIT = not args.no_key_split
+        attention_bf16.USE_TC_ATTENTION = not args.no_tensor_memory
+        attention_bf16.USE_TMA_DECODE = not args.no_tma_decode
         decode = args.op == "decode_attention"
         batch = args.batch if decode else 1
         q_len = 1 if decode else args.tokens
-        context = args.context if decode else args.tokens
+        context = args.context if decode else args.tokens + args.past
         q, kp, vp, start, seq, table = _paged_case(batch, q_len, context, nq, nkv, d, args.page, dtype)
         out = torch.empty_like(q)
         planned = args.planned_context or context
@@ -131,7 +143,7 @@ def main(argv=None) -> int:
             moved = batch * context * nkv * d * 2 * size
             record.update(bytes=moved, gb_s=round(moved / ms / 1e6, 1))
         else:
-            flops = 2 * 2 * nq * d * context * context / 2
+            flops = 2 * 2 * nq * d * q_len * (args.past + q_len / 2)
             record.update(flops=flops, tflop_s=round(flops / ms / 1e9, 1))
     elif args.op == "gemm":
         x = torch.randn(args.m, args.k, device="cuda").to(dtype)
