@@ -26,7 +26,9 @@ def close(actual, expected, dtype, scale=1.0, what=""):
 
 
 @pytest.mark.parametrize("dtype", DTYPES)
-@pytest.mark.parametrize("tokens,hidden", [(1, 64), (7, 1000), (33, 2048), (5, 5120), (3, 8192 + 24)])
+@pytest.mark.parametrize("tokens,hidden", [(1, 64), (7, 1000), (33, 2048), (5, 5120), (3, 8192 + 24),
+                                           # many rows, as a portion of a prompt brings
+                                           (300, 2048), (777, 1000), (260, 8192 + 24), (2050, 160)])
 def test_add_rmsnorm(dtype, tokens, hidden):
     k = kernels()
     g = torch.Generator(device="cuda").manual_seed(tokens * hidden)
