@@ -5,11 +5,19 @@
     python -m vllm_from_scratch_b200.kernels.microbench prefill_attention --tokens 2048
     python -m vllm_from_scratch_b200.kernels.microbench gemm --m 8 --n 12288 --k 2048
     python -m vllm_from_scratch_b200.kernels.microbench norm | silu_mul | rope --tokens 2048
+    python -m vllm_from_scratch_b200.kernels.microbench step --layers 4 --tokens 2048          (a prompt step)
+    python -m vllm_from_scratch_b200.kernels.microbench step --layers 4 --batch 8 --context 2048 --tokens 1
 
 CUDA events around ``--iters`` launches after ``--warmup``; between launches a
 buffer larger than L2 is written unless ``--keep-l2`` is given.  Prints one JSON
 line with the time per launch and the achieved bytes/s or flop/s for the
 algorithmic minimum of traffic or work.
+
+``step`` runs whole steps of a model of the Qwen3-1.7B widths (``--hidden``, ``--heads``, ...)
+with ``--layers`` layers and random weights through the step function, without graphs: one
+prompt of ``--tokens`` tokens, or with ``--tokens 1`` a decode step of ``--batch`` requests at
+``--context`` positions.  The last of its steps runs between ``cudaProfilerStart`` and
+``cudaProfilerStop``, so that ``ncu --profile-from-start off`` lists that step's launches.
 """
 
 from __future__ import annotations
@@ -62,9 +70,69 @@ def _paged_case(batch, q_len, context, nq, nkv, d, page, dtype):
     return q, kp, vp, start, seq, table
 
 
+def _step(args) -> int:
+    """Whole steps of a small-in-depth model through the step function (see the module's text)."""
+    import time
+
+    from ..config.registry import load_model_config
+    from ..engine.runner import ModelRunner
+    from ..engine.step import StepEntry
+    raw = {
+        "architectures": ["Qwen3ForCausalLM"], "model_type": "qwen3", "num_hidden_layers": args.layers,
+        "hidden_size": args.hidden, "num_attention_heads": args.heads, "num_key_value_heads": args.kv_heads,
+        "head_dim": args.head_dim, "intermediate_size": args.inter, "vocab_size": args.vocab,
+        "rope_theta": 1000000.0, "rms_norm_eps": 1e-6, "tie_word_embeddings": True,
+        "max_position_embeddings": 40960, "hidden_act": "silu", "attention_bias": False, "initializer_range": 0.02,
+    }
+    entry, config = load_model_config(raw)
+    dtype = torch.bfloat16 if args.dtype == "bfloat16" else torch.float32
+    weights = entry.random_weights(config, seed=0, dtype=dtype, device="cuda")
+    decode = args.tokens == 1
+    requests = args.batch if decode else 1
+    positions = (args.context + 8) if decode else args.tokens
+    runner = ModelRunner(entry.build_spec(config), weights, args.dtype, args.page,
+                         requests * (-(-positions // args.page)) + 4, requests, device="cuda", model_config=config)
+    del weights
+    generator = torch.Generator().manual_seed(0)
+    ids = [f"r{i}" for i in range(requests)]
+    for request_id in ids:
+        runner.manager.admit(request_id)
+    steps = 3
+    milliseconds = 0.0
+    for number in range(steps):
+        entries = []
+        for request_id in ids:
+            if decode:
+                start = args.context + number
+                tokens = torch.randint(0, args.vocab, (1,), generator=generator).tolist()
+            else:
+                start = 0
+                tokens = torch.randint(0, args.vocab, (args.tokens,), generator=generator).tolist()
+            assert runner.manager.allocate(request_id, start + len(tokens))
+            entries.append(StepEntry(request_id, tokens, start, [len(tokens) - 1]))
+        last = number == steps - 1
+        torch.cuda.synchronize()
+        if last:
+            torch.cuda.profiler.start()
+        started = time.perf_counter()
+        runner.step(entries)
+        torch.cuda.synchronize()
+        milliseconds = 1000 * (time.perf_counter() - started)
+        if last:
+            torch.cuda.profiler.stop()
+    print(json.dumps({"op": "step", "dtype": args.dtype, "layers": args.layers, "requests": requests,
+                      "tokens_per_request": 1 if decode else args.tokens,
+                      "context": args.context if decode else args.tokens,
+                      "host_ms_of_the_last_step_without_graphs": round(milliseconds, 3)}))
+    return 0
+
+
 def main(argv=None) -> int:
     parser = argparse.ArgumentParser(description=__doc__, formatter_class=argparse.RawTextHelpFormatter)
-    parser.add_argument("op", choices=("decode_attention", "prefill_attention", "gemm", "norm", "silu_mul", "rope"))
+    parser.add_argument("op", choices=("decode_attention", "prefill_attention", "gemm", "norm", "silu_mul", "rope",
+                                       "step"))
+    parser.add_argument("--layers", type=int, default=4, help="step: layers of the model")
+    parser.add_argument("--vocab", type=int, default=151936, help="step: rows of the embedding")
     parser.add_argument("--batch", type=int, default=8)
     parser.add_argument("--context", type=int, default=2048)
     parser.add_argument("--tokens", type=int, default=2048)
@@ -106,6 +174,8 @@ def main(argv=None) -> int:
     nq, nkv, d = args.heads, args.kv_heads, args.head_dim
     record: dict = {"op": args.op, "dtype": args.dtype}
 
+    if args.op == "step":
+        return _step(args)
     if args.op in ("decode_attention", "prefill_attention"):
         from . import attention_bf16
         attention_bf16.USE_TC_KEY_SPLIT = not args.no_key_split
