@@ -34,13 +34,31 @@ def silu_mul(gate_up, out):
     out.copy_((gate * torch.sigmoid(gate) * up).to(out.dtype))
 
 
-def gemm(x, w, out):
-    out.copy_((x.float() @ w.float().T).to(out.dtype))
+def _root(scale, width):
+    """The factor a product applies whose rows are half-normalised: rsqrt(sum of the pieces / width + eps)."""
+    squares, eps = scale
+    return torch.rsqrt(squares.float().sum(dim=-1, keepdim=True) / width + eps)
 
 
-def gated_silu_gemm(x, w_gate_up, out):
+def gemm(x, w, out, scale=None, fold=None):
+    product = x.float() @ w.float().T
+    if scale is not None:
+        product = product * _root(scale, x.shape[1])
+    if fold is None:
+        out.copy_(product.to(out.dtype))
+        return
+    # residual += rounded product; out = residual * weight; sums of squares over blocks of eight columns
+    residual, weight, squares_out = fold
+    residual += product.to(out.dtype).float()
+    out.copy_((residual * weight).to(out.dtype))
+    squares_out.copy_(residual.pow(2).reshape(residual.shape[0], -1, 8).sum(dim=-1))
+
+
+def gated_silu_gemm(x, w_gate_up, out, scale=None):
     inter = out.shape[1]
     gate_up = x.float() @ w_gate_up.float().T
+    if scale is not None:
+        gate_up = gate_up * _root(scale, x.shape[1])
     gate, up = gate_up[:, :inter], gate_up[:, inter:]
     out.copy_((gate * torch.sigmoid(gate) * up).to(out.dtype))
 

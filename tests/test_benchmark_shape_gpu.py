@@ -234,3 +234,34 @@ def test_prompt_steps_as_graph_replays_at_the_benchmark_widths(world):
     assert graphs.replays >= 2 + 8, "the second and third prompt of each kind must be replays"
     print(f"prompt steps as replays: max |diff| / max |logit| = {worst:.3e}")
     runner.check_device()
+
+
+@pytest.mark.parametrize("requests", [1, 8, 16])
+def test_steps_of_few_tokens_split_their_norms(world, requests, monkeypatch):
+    """Decode steps of up to 16 requests run no norm kernel between the first layer's and the final
+    one (the products around a norm carry its halves), the same steps with the split switched off
+    run two a layer, and both give the plain model's logits."""
+    import vllm_from_scratch_b200.kernels as kernels
+    from vllm_from_scratch_b200 import StepEntry
+    from vllm_from_scratch_b200.kernels import gemm_bf16
+    length = 40
+    prompts = {f"r{i}": helpers.random_tokens(SHAPE["vocab_size"], length, seed=1200 + i) for i in range(requests)}
+    plain = {rid: plain_qwen3.qwen3_logits(SHAPE, world["rounded"], toks)[-1:] for rid, toks in prompts.items()}
+    calls = []
+    real = kernels.add_rmsnorm
+    monkeypatch.setattr(kernels, "add_rmsnorm", lambda *a, **k: (calls.append(1), real(*a, **k))[1])
+    layers = SHAPE["num_hidden_layers"]
+    for split, norm_kernels in ((True, 2), (False, 2 * layers + 1)):
+        monkeypatch.setattr(gemm_bf16, "USE_SPLIT_NORM", split)
+        runner = make_runner(world, "bfloat16", requests * 4, max_requests=requests)
+        for rid, toks in prompts.items():
+            runner.manager.admit(rid)
+            assert runner.manager.allocate(rid, length)
+            runner.step([StepEntry(rid, toks[:-1], 0, [])])
+            runner.manager.commit(rid, length - 1)
+        calls.clear()
+        logits = runner.step([StepEntry(rid, toks[-1:], length - 1, [0]) for rid, toks in prompts.items()])
+        assert len(calls) == norm_kernels, (split, len(calls))
+        results = {rid: logits[i:i + 1].clone() for i, rid in enumerate(prompts)}
+        compare(results, plain, "bfloat16", f"decode step of {requests}, norms split: {split}", world["layers"])
+        runner.check_device()

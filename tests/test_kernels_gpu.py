@@ -332,6 +332,83 @@ def test_gated_silu_gemm(m, inter, k_, dtype):
         assert float((fused.float() - out_b.float()).abs().max()) <= bound
 
 
+# token rows, residual width, width of the rows that go into the first product, width of the gated product
+SPLIT_NORM_SHAPES = [(1, 128, 256, 24), (8, 2048, 2048, 6144), (5, 1152, 384, 1000), (12, 2048, 6144, 264),
+                     (16, 5120, 128, 512), (9, 384, 1024, 8), (3, 6144, 128, 64)]
+
+
+@pytest.mark.parametrize("shape", SPLIT_NORM_SHAPES)
+def test_rmsnorm_split_over_two_products(shape):
+    """A product that adds into the residual and hands on half-normalised rows, then a gated and a
+    plain product that apply the root: each against its plain version, the pair against the
+    unsplit sequence (product, add + RMSNorm, product), and a token's results must not depend on
+    the other tokens of the launch."""
+    k = kernels()
+    m, hidden, first_k, inter = shape
+    g = torch.Generator(device="cuda").manual_seed(sum(shape))
+    rand = lambda *dims, scale=1.0: torch.randn(*dims, device="cuda", generator=g) * scale
+    x = rand(m, first_k).bfloat16()
+    w_first = rand(hidden, first_k, scale=first_k ** -0.5).bfloat16()
+    w_gate_up = rand(2 * inter, hidden, scale=hidden ** -0.5).bfloat16()
+    w_plain = rand(inter, hidden, scale=hidden ** -0.5).bfloat16()
+    weight = 1 + 0.1 * rand(hidden)
+    residual = rand(m, hidden, scale=3.0)
+    residual[m - 1, 7] = 300.0                       # one large element: the sums of squares must carry it
+    eps = 1e-5
+    for w in (w_first, w_plain):
+        assert k.split_norm_ok(m, w, fold=True) and k.split_norm_ok(m, w, fold=False)
+    assert k.split_norm_ok(m, w_gate_up, fold=False, gated=True)
+
+    def run(ops, rows):
+        res = residual[:rows].clone()
+        half = torch.full((rows, hidden), 7.0, device="cuda", dtype=torch.bfloat16)
+        squares = torch.full((rows, hidden // 8), 7.0, device="cuda")
+        ops.gemm(x[:rows].contiguous(), w_first, half, fold=(res, weight, squares))
+        act = torch.full((rows, inter), 7.0, device="cuda", dtype=torch.bfloat16)
+        ops.gated_silu_gemm(half, w_gate_up, act, scale=(squares, eps))
+        out = torch.full((rows, inter), 7.0, device="cuda", dtype=torch.bfloat16)
+        ops.gemm(half, w_plain, out, scale=(squares, eps))
+        return res, half, squares, act, out
+
+    got, want = run(k, m), run(plain_ops, m)
+    # The residual carries the first product rounded to bfloat16: sums taken in another order may
+    # round it the other way, one unit in its last place.
+    rounding = float((x.float() @ w_first.float().T).abs().max()) * 2 ** -7
+    for name, a, b in zip(("residual", "half-normalised rows", "sums of squares", "gated product", "product"), got, want):
+        bound = float(b.float().abs().max()) * 2 ** -7 if name != "residual" else rounding
+        diff = float((a.float() - b.float()).abs().max())
+        assert diff <= bound, f"{name}: max |diff| {diff:.3e} > {bound:.3e}"
+    # the same through a norm of its own
+    res = residual.clone()
+    first = torch.empty(m, hidden, device="cuda", dtype=torch.bfloat16)
+    plain_ops.gemm(x, w_first, first)
+    normed = torch.empty_like(first)
+    plain_ops.add_rmsnorm(first, res, weight, eps, normed)
+    act, out = torch.empty_like(got[3]), torch.empty_like(got[4])
+    plain_ops.gated_silu_gemm(normed, w_gate_up, act)
+    plain_ops.gemm(normed, w_plain, out)
+    assert float((got[0] - res).abs().max()) <= rounding
+    for name, a, b in (("gated product", got[3], act), ("product", got[4], out)):
+        bound = float(b.float().abs().max()) * 2 ** -6
+        assert float((a.float() - b.float()).abs().max()) <= bound, name
+    fewer = 1 if m <= 8 else 9                       # up to 8 rows and from 9 rows on are different kernels
+    if m > fewer:
+        alone = run(k, fewer)
+        for a, b in zip(alone, got):
+            assert torch.equal(a[fewer - 1], b[fewer - 1])
+
+
+def test_split_norm_refusals():
+    k = kernels()
+    bf = lambda *dims: torch.zeros(*dims, device="cuda", dtype=torch.bfloat16)
+    assert not k.split_norm_ok(17, bf(256, 256), fold=False)          # too many token rows
+    assert not k.split_norm_ok(4, bf(256, 192), fold=False)           # K is no multiple of 128
+    assert not k.split_norm_ok(4, bf(260, 256), fold=True)            # no whole blocks of eight columns
+    assert not k.split_norm_ok(4, torch.zeros(256, 256, device="cuda"), fold=False)      # float32
+    with pytest.raises(k.KernelError):
+        k.gemm(bf(4, 192), bf(256, 192), bf(4, 256), scale=(torch.ones(4, 24, device="cuda"), 1e-6))
+
+
 SPLIT_BATCH_SHAPES = [
     # nq, nkv, d, page, q_lens (single tokens first), seq_lens, window
     (8, 2, 64, 16, [1, 1, 1, 40, 70], [300, 64, 1, 40, 170], None),

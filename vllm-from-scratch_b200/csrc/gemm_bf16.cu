@@ -214,7 +214,8 @@ inline int* stream_error_flag() {
 // 1 = launched, 0 = not a shape for the kernel with resident weight rows, < 0 = error.
 // gated_inter > 0: w is [2 * gated_inter, K], the result [M, gated_inter].
 template <typename OutT>
-int launch_slab(const bf16* x, const bf16* w, OutT* y, int M, int N, int K, int gated_inter, cudaStream_t stream) {
+int launch_slab(const bf16* x, const bf16* w, OutT* y, int M, int N, int K, int gated_inter, cudaStream_t stream,
+                const SlabNorm& norm = SlabNorm{}) {
     const bool gated = gated_inter > 0;
     if (M > 16 || K % 128 != 0 || slab_smem_bytes(K, gated) > 200 * 1024) return 0;
     int* error_flag = stream_error_flag();
@@ -234,7 +235,7 @@ int launch_slab(const bf16* x, const bf16* w, OutT* y, int M, int N, int K, int 
             if (status != cudaSuccess) return fail("slab_gemm", cudaGetErrorString(status));
             *configured = true;
         }
-        launch_overlapped(kernel, blocks, threads, smem, stream, x, w, y, M, rows, K, error_flag);
+        launch_overlapped(kernel, blocks, threads, smem, stream, x, w, y, M, rows, K, error_flag, norm);
         return 0;
     };
     static bool configured[7] = {};
@@ -266,6 +267,41 @@ B200_EXPORT int b200_stream_gemm_error() {
         cudaMemcpyToSymbol(b200::g_stream_error, &zero, sizeof(int));
     }
     return code;
+}
+
+// Whether the resident-rows kernel takes the product, in the forms that carry half of an RMSNorm.
+B200_EXPORT int b200_split_norm_gemm_supports(int M, int N, int K, int gated_inter) {
+    const int rows = gated_inter > 0 ? gated_inter : N;
+    return (M >= 1 && M <= 16 && K >= 128 && K % 128 == 0 && rows >= 8 && rows % 8 == 0 &&
+            b200::slab_smem_bytes(K, gated_inter > 0) <= 200 * 1024) ? 1 : 0;
+}
+
+// The resident-rows product with half of an RMSNorm on either side (slab_gemm.cuh), bfloat16 in and out.
+//   squares_in != null: x holds rows v * g; the result is multiplied by rsqrt(sum of the row's `pieces`
+//   pieces of squares_in[row][...] / K + eps).
+//   residual != null (not gated): residual[M][N] += bfloat16(result) in float32, y = residual * weight[N],
+//   squares_out[row][N / 8] = sums of the new residual's squares over blocks of eight columns.
+B200_EXPORT int b200_split_norm_gemm_bf16(const void* x, const void* w, void* y, int M, int N, int K, int gated_inter,
+                                          const void* squares_in, int pieces, float eps, void* residual,
+                                          const void* weight, void* squares_out, cudaStream_t stream) {
+    using namespace b200;
+    if (M == 0 || N == 0) return 0;
+    if (!b200_split_norm_gemm_supports(M, N, K, gated_inter)) return fail("split_norm_gemm", "not a shape for the resident-rows kernel");
+    if (((uintptr_t)x | (uintptr_t)w | (uintptr_t)y | (uintptr_t)residual | (uintptr_t)weight) & 15)
+        return fail("split_norm_gemm", "operands must be 16-byte aligned");
+    if (gated_inter > 0 && N != 2 * gated_inter) return fail("split_norm_gemm", "gated product needs N = 2 * inter");
+    if (squares_in != nullptr && pieces < 1) return fail("split_norm_gemm", "no pieces of the sums of squares");
+    if (residual != nullptr && (gated_inter > 0 || weight == nullptr || squares_out == nullptr))
+        return fail("split_norm_gemm", "a residual sum needs the norm's weights and room for the sums of squares, and is not gated");
+    SlabNorm norm = {};
+    norm.squares_in = static_cast<const float*>(squares_in);
+    norm.pieces = pieces;
+    norm.eps = eps;
+    norm.residual = static_cast<float*>(residual);
+    norm.weight = static_cast<const float*>(weight);
+    norm.squares_out = static_cast<float*>(squares_out);
+    const int rc = launch_slab<bf16>((const bf16*)x, (const bf16*)w, (bf16*)y, M, N, K, gated_inter, stream, norm);
+    return rc == 1 ? 0 : (rc < 0 ? rc : fail("split_norm_gemm", "not launched"));
 }
 
 // Largest M and the divisibility of K the few-rows kernel takes.

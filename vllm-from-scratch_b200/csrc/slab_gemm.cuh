@@ -16,6 +16,14 @@
 // order.  GATED: w is [2 N, K] with N gate rows followed by N up rows; a block holds eight
 // of each and stores silu(gate) * up, the feed-forward's first product and activation in one.
 // Waits are bounded; a block that gives up sets `error_flag` and stores nothing.
+//
+// RMSNorm between two such products is split over them, so that no kernel of its own has to read
+// and write the rows: rmsnorm(v) g W^T = rsqrt(mean v^2 + eps) * ((v g) W^T) for the norm's
+// weights g.  The product ahead of the norm (`SlabNorm::residual` given) adds its rounded result
+// into the float32 residual rows v in place (every element has one owner), stores v g instead of
+// the result, and the sum of v^2 over its eight columns for every token row to
+// squares_out[row][block].  The product behind it (`SlabNorm::squares_in` given) adds these
+// pieces up in a fixed order and multiplies its own sums by the root.
 #pragma once
 
 #include "async_copy.cuh"
@@ -40,13 +48,24 @@ inline size_t slab_smem_bytes(int K, bool gated) {
 // DEEP: more of them in flight.  Plain form: rows so long (K of 4096 and more) that two blocks
 // fill an SM's shared memory, so a block may have the registers of the blocks that do not fit
 // (twelve fragments in flight, six for WIDE).  Gated form: eight instead of four.
+// The two halves of a split RMSNorm (all null: a plain product).
+struct SlabNorm {
+    const float* squares_in;        // [rows][pieces]: this product's rows are v g, to be scaled by the root
+    int pieces;
+    float eps;
+    float* residual;                // [M][N] float32, updated in place: this product's result is added to it
+    const float* weight;            // [N]: the norm's weights g
+    float* squares_out;             // [rows][N / 8]
+};
+
 template <typename OutT, bool GATED, bool WIDE, bool DEEP>
 __global__ void __launch_bounds__(kSlabWarps * 32, GATED ? 3 : (DEEP ? 2 : 4)) slab_gemm_kernel(
     const __nv_bfloat16* __restrict__ x, const __nv_bfloat16* __restrict__ w, OutT* __restrict__ y, int M, int N,
-    int K, int* __restrict__ error_flag) {
+    int K, int* __restrict__ error_flag, const SlabNorm norm) {
     extern __shared__ __align__(128) unsigned char slab_smem[];
     constexpr int kSets = GATED ? 2 : 1;            // sets of eight rows: gate and up, or one
     __shared__ float partial[kSlabWarps][kSets][32][4];
+    __shared__ float row_scale[16];
     overlap_trigger();
     const int pitch = K * 2 + 16;
     unsigned char* rows = slab_smem;
@@ -79,6 +98,30 @@ __global__ void __launch_bounds__(kSlabWarps * 32, GATED ? 3 : (DEEP ? 2 : 4)) s
         }
     }
     overlap_wait();                                 // the token rows come from the kernel before this one
+
+    // The pieces of a token row's sum of squares (warp r: row r), asked for now and added up after
+    // the products.
+    constexpr int kPieces = 8;                      // a lane's share of 256 pieces
+    float piece[kPieces];
+    const bool scaled = norm.squares_in != nullptr;
+    if (scaled) {
+        const float* mine = norm.squares_in + (size_t)(warp < M ? warp : 0) * norm.pieces;
+#pragma unroll
+        for (int j = 0; j < kPieces; ++j) {
+            const int i = j * 32 + lane;
+            piece[j] = __ldcg(mine + (i < norm.pieces ? i : 0));
+        }
+    }
+
+    // What the warp that stores will add to, asked for ahead of the products.
+    float2 before[2] = {make_float2(0.0f, 0.0f), make_float2(0.0f, 0.0f)}, gain = make_float2(0.0f, 0.0f);
+    if (warp == 0 && norm.residual != nullptr) {
+#pragma unroll
+        for (int half = 0; half < (WIDE ? 2 : 1); ++half)
+            if (g + half * 8 < M)
+                before[half] = __ldcg(reinterpret_cast<const float2*>(norm.residual + (size_t)(g + half * 8) * N + n0 + 2 * t));
+        gain = *reinterpret_cast<const float2*>(norm.weight + n0 + 2 * t);
+    }
 
     const bool x_ok = g < M, x_hi_ok = WIDE && g + 8 < M;   // rows g and g + 8 of the 16-row operand
     const __nv_bfloat16* x_row = x + (size_t)(x_ok ? g : 0) * K + 8 * t;
@@ -130,6 +173,20 @@ __global__ void __launch_bounds__(kSlabWarps * 32, GATED ? 3 : (DEEP ? 2 : 4)) s
     for (int set = 0; set < kSets; ++set)
 #pragma unroll
         for (int e = 0; e < 4; ++e) partial[warp][set][lane][e] = acc[set][e];
+    for (int row = warp; row < 16; row += kSlabWarps) {
+        float scale = 1.0f;
+        if (scaled && row < M) {
+            const float* mine = norm.squares_in + (size_t)row * norm.pieces;
+            float sum = 0.0f;
+            if (row == warp) {
+#pragma unroll
+                for (int j = 0; j < kPieces; ++j) sum += j * 32 + lane < norm.pieces ? piece[j] : 0.0f;
+            }
+            for (int i = (row == warp ? kPieces * 32 : 0) + lane; i < norm.pieces; i += 32) sum += __ldcg(mine + i);
+            scale = rsqrtf(warp_sum(sum) / (float)K + norm.eps);
+        }
+        if (lane == 0) row_scale[row] = scale;
+    }
     __syncthreads();
     if (warp != 0 || !ok) return;
     // accumulator layout: c0, c1 = (token g, weight rows 2t, 2t + 1), c2, c3 = (token g + 8, same rows)
@@ -148,9 +205,26 @@ __global__ void __launch_bounds__(kSlabWarps * 32, GATED ? 3 : (DEEP ? 2 : 4)) s
                 for (int wi = 1; wi < kSlabWarps; ++wi) sum += partial[wi][set][lane][half * 2 + e];
                 sums[set] = sum;
             }
-            total[e] = GATED ? sums[0] / (1.0f + expf(-sums[0])) * sums[kSets - 1] : sums[0];
+            const float scale = row_scale[g + half * 8];
+            const float first = sums[0] * scale;
+            total[e] = GATED ? first / (1.0f + expf(-first)) * (sums[kSets - 1] * scale) : first;
         }
         const int token = g + half * 8;
+        if (norm.residual != nullptr) {
+            // (the launcher gives this form whole blocks of eight columns and an even N)
+            float squares = 0.0f;
+            if (token < M) {
+                const float2 v = make_float2(before[half].x + to_float(from_float<OutT>(total[0])),
+                                             before[half].y + to_float(from_float<OutT>(total[1])));
+                *reinterpret_cast<float2*>(norm.residual + (size_t)token * N + n) = v;
+                total[0] = v.x * gain.x;
+                total[1] = v.y * gain.y;
+                squares = v.x * v.x + v.y * v.y;
+            }
+            squares += __shfl_xor_sync(0xffffffffu, squares, 1);
+            squares += __shfl_xor_sync(0xffffffffu, squares, 2);
+            if (t == 0 && token < M) norm.squares_out[(size_t)token * gridDim.x + blockIdx.x] = squares;
+        }
         if (token >= M) continue;
         OutT* dst = y + (size_t)token * N + n;
         if (n + 1 < N && (N & 1) == 0) store_pair<OutT>(dst, total[0], total[1]);

@@ -207,12 +207,38 @@ def silu_mul(gate_up: torch.Tensor, out: torch.Tensor) -> None:
 
 
 # --------------------------------------------------------------- matrix product
-def gemm(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor) -> None:
+def split_norm_ok(tokens: int, w: torch.Tensor, fold: bool, gated: bool = False) -> bool:
+    """Whether the product of ``tokens`` rows with ``w`` can carry half of an RMSNorm: scale its
+    result by the root of :class:`~..parts.base.HalfNormedRows`, or, with ``fold``, add its result
+    into the residual and write such rows (``gemm`` with ``scale`` / ``fold``).  True for the few
+    rows and the bfloat16 matrices that the resident-rows kernel takes."""
+    if w.dtype != torch.bfloat16 or not w.is_cuda:
+        return False
+    from . import gemm_bf16
+    return gemm_bf16.split_norm_ok(tokens, w, fold, gated)
+
+
+def gemm(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor,
+         scale: tuple[torch.Tensor, float] | None = None,
+         fold: tuple[torch.Tensor, torch.Tensor, torch.Tensor] | None = None) -> None:
     """``out[M, N] = x[M, K] @ w[N, K]^T``.  float32 operands: the engine's own
     fused-multiply-add kernel (no tensor-core mode).  bfloat16 operands: float32
-    accumulation on the tensor cores; ``out`` may be bfloat16 or float32."""
+    accumulation on the tensor cores; ``out`` may be bfloat16 or float32.
+
+    The halves of a split RMSNorm, where :func:`split_norm_ok` says so: ``scale = (squares, eps)``
+    multiplies row ``m`` of the result by ``rsqrt(squares[m].sum() / K + eps)``; ``fold = (residual,
+    weight, squares_out)`` adds the rounded result into the float32 ``residual`` ``[M, N]`` in place,
+    writes ``residual * weight`` to ``out`` instead, and the sums of the new residual's squares over
+    blocks of eight columns to ``squares_out`` ``[M, N / 8]``."""
     m, k = x.shape
     n = w.shape[0]
+    if scale is not None or fold is not None:
+        _check("gemm input", x, torch.bfloat16)
+        _check("gemm weight", w, torch.bfloat16, (n, k))
+        _check("gemm output", out, torch.bfloat16, (m, n))
+        from . import gemm_bf16
+        gemm_bf16.split_norm_gemm(x, w, out, 0, scale, fold)
+        return
     if x.dtype == torch.float32:
         _run("gemm_f32", "b200_gemm_f32",
              _P(_check("gemm input", x, torch.float32)), _P(_check("gemm weight", w, torch.float32, (n, k))),
@@ -225,15 +251,21 @@ def gemm(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor) -> None:
     gemm_bf16.gemm_bf16(x, w, out)
 
 
-def gated_silu_gemm(x: torch.Tensor, w_gate_up: torch.Tensor, out: torch.Tensor) -> None:
+def gated_silu_gemm(x: torch.Tensor, w_gate_up: torch.Tensor, out: torch.Tensor,
+                    scale: tuple[torch.Tensor, float] | None = None) -> None:
     """``out[M, I] = silu(x @ w[:I]^T) * (x @ w[I:]^T)`` for ``w_gate_up`` of shape
     ``[2 I, K]`` (gate rows first).  One fused kernel where the shape allows it,
-    otherwise the product followed by the activation kernel."""
+    otherwise the product followed by the activation kernel.  ``scale``: as for :func:`gemm`
+    (both products are scaled before the activation)."""
     m, k = x.shape
     inter = out.shape[1]
     _check("gated input", x, (torch.float32, torch.bfloat16))
     _check("gate_up weight", w_gate_up, x.dtype, (2 * inter, k))
     _check("gated output", out, x.dtype, (m, inter))
+    if scale is not None:
+        from . import gemm_bf16
+        gemm_bf16.split_norm_gemm(x, w_gate_up, out, inter, scale, None)
+        return
     if x.dtype == torch.bfloat16:
         from . import gemm_bf16
         if gemm_bf16.gated_silu_gemm_bf16(x, w_gate_up, out):

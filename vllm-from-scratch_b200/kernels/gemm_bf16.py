@@ -94,6 +94,45 @@ def gated_silu_gemm_bf16(x: torch.Tensor, w_gate_up: torch.Tensor, out: torch.Te
     return True
 
 
+# Tests switch the split of the norms off to run the same steps with norm kernels of their own.
+USE_SPLIT_NORM = True
+
+
+def split_norm_ok(tokens: int, w: torch.Tensor, fold: bool, gated: bool = False) -> bool:
+    """Whether ``split_norm_gemm`` takes the product: a shape for the resident-rows kernel, where the
+    engine would use that kernel anyway, and whole blocks of eight result columns."""
+    rows = w.shape[0] // 2 if gated else w.shape[0]
+    return (USE_SPLIT_NORM and rows % 8 == 0 and _small_enough(w, gated)
+            and (gated or w.shape[0] <= SKINNY_MAX_WEIGHT_ROWS) and _resident_ok(tokens, w.shape[1], gated, w))
+
+
+def split_norm_gemm(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, gated_inter: int,
+                    scale: tuple[torch.Tensor, float] | None,
+                    fold: tuple[torch.Tensor, torch.Tensor, torch.Tensor] | None) -> None:
+    """The resident-rows product with half of an RMSNorm on either side (see ``kernels.gemm``)."""
+    from . import KernelError, _check, _stream, count_launch
+    m, k = x.shape
+    n = w.shape[0]
+    squares_in = pieces = 0
+    eps = 0.0
+    if scale is not None:
+        squares, eps = scale
+        squares_in = _check("sums of squares", squares, torch.float32, (m, None))
+        pieces = squares.shape[1]
+    residual = weight = squares_out = 0
+    if fold is not None:
+        residual = _check("residual", fold[0], torch.float32, (m, n))
+        weight = _check("norm weight", fold[1], torch.float32, (n,))
+        squares_out = _check("sums of squares out", fold[2], torch.float32, (m, n // 8))
+    lib = load_library("gemm_bf16")
+    status = lib.b200_split_norm_gemm_bf16(
+        _P(x.data_ptr()), _P(w.data_ptr()), _P(out.data_ptr()), _I(m), _I(n), _I(k), _I(gated_inter),
+        _P(squares_in), _I(pieces), ctypes.c_float(eps), _P(residual), _P(weight), _P(squares_out), _stream())
+    if status != 0:
+        raise KernelError(lib.b200_last_error().decode())
+    count_launch()
+
+
 def device_error_code() -> int:
     """0, or the code left by a kernel whose bounded wait ran out (synchronises)."""
     lib = load_library("gemm_bf16")

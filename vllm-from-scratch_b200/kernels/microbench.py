@@ -5,6 +5,7 @@
     python -m vllm_from_scratch_b200.kernels.microbench prefill_attention --tokens 2048
     python -m vllm_from_scratch_b200.kernels.microbench gemm --m 8 --n 12288 --k 2048
     python -m vllm_from_scratch_b200.kernels.microbench norm | silu_mul | rope --tokens 2048
+    python -m vllm_from_scratch_b200.kernels.microbench layer_products --m 8 [--no-split-norm]
     python -m vllm_from_scratch_b200.kernels.microbench step --layers 4 --tokens 2048          (a prompt step)
     python -m vllm_from_scratch_b200.kernels.microbench step --layers 4 --batch 8 --context 2048 --tokens 1
 
@@ -12,6 +13,13 @@ CUDA events around ``--iters`` launches after ``--warmup``; between launches a
 buffer larger than L2 is written unless ``--keep-l2`` is given.  Prints one JSON
 line with the time per launch and the achieved bytes/s or flop/s for the
 algorithmic minimum of traffic or work.
+
+``layer_products`` times what lies between two attention kernels of a decode step (output product,
+sum and norm, gate and up with the activation, down product, sum and norm, the next layer's q/k/v
+product) for ``--m`` token rows at the widths ``--hidden``, ``--heads`` x ``--head-dim``, ``--inter``,
+with the norms split over the products around them or (``--no-split-norm``) as kernels of their own;
+the time printed is per layer, over several layers' worth of weights, so that every launch reads
+cold weights.
 
 ``step`` runs whole steps of a model of the Qwen3-1.7B widths (``--hidden``, ``--heads``, ...)
 with ``--layers`` layers and random weights through the step function, without graphs: one
@@ -130,7 +138,9 @@ def _step(args) -> int:
 def main(argv=None) -> int:
     parser = argparse.ArgumentParser(description=__doc__, formatter_class=argparse.RawTextHelpFormatter)
     parser.add_argument("op", choices=("decode_attention", "prefill_attention", "gemm", "norm", "silu_mul", "rope",
-                                       "step"))
+                                       "layer_products", "step"))
+    parser.add_argument("--no-split-norm", action="store_true",
+                        help="layer_products: the two norms as kernels of their own")
     parser.add_argument("--layers", type=int, default=4, help="step: layers of the model")
     parser.add_argument("--vocab", type=int, default=151936, help="step: rows of the embedding")
     parser.add_argument("--batch", type=int, default=8)
@@ -237,6 +247,38 @@ def main(argv=None) -> int:
         flops = 2 * args.m * args.n * args.k
         record.update(m=args.m, n=args.n, k=args.k, gb_s=round(moved / ms / 1e6, 1),
                       tflop_s=round(flops / ms / 1e9, 2))
+    elif args.op == "layer_products":
+        m, hidden, inter = args.m, args.hidden, args.inter
+        attended, qkv_width = nq * d, (nq + 2 * nkv) * d
+        layer_bytes = (hidden * attended + 3 * inter * hidden + qkv_width * hidden) * 2
+        copies = max(2, min(16, (768 * 1024 * 1024) // layer_bytes))
+        rand = lambda *shape: (torch.randn(*shape, device="cuda") * shape[-1] ** -0.5).bfloat16()
+        layers = [(rand(hidden, attended), rand(2 * inter, hidden), rand(hidden, inter), rand(qkv_width, hidden))
+                  for _ in range(copies)]
+        gain = torch.ones(hidden, device="cuda")
+        x = torch.randn(m, attended, device="cuda").bfloat16()
+        res = torch.randn(m, hidden, device="cuda")
+        bf = lambda width: torch.empty(m, width, device="cuda", dtype=torch.bfloat16)
+        out, normed, act, down, qkv = bf(hidden), bf(hidden), bf(inter), bf(hidden), bf(qkv_width)
+        squares = [torch.empty(m, hidden // 8, device="cuda") for _ in range(2)]
+
+        def sweep():
+            for w_out, w_gate_up, w_down, w_qkv in layers:
+                if args.no_split_norm:
+                    kernels.gemm(x, w_out, out)
+                    kernels.add_rmsnorm(out, res, gain, 1e-6, normed)
+                    kernels.gated_silu_gemm(normed, w_gate_up, act)
+                    kernels.gemm(act, w_down, down)
+                    kernels.add_rmsnorm(down, res, gain, 1e-6, normed)
+                    kernels.gemm(normed, w_qkv, qkv)
+                else:
+                    kernels.gemm(x, w_out, out, fold=(res, gain, squares[0]))
+                    kernels.gated_silu_gemm(out, w_gate_up, act, scale=(squares[0], 1e-6))
+                    kernels.gemm(act, w_down, down, fold=(res, gain, squares[1]))
+                    kernels.gemm(down, w_qkv, qkv, scale=(squares[1], 1e-6))
+        ms = _time(sweep, args.warmup, args.iters, False) / copies
+        record.update(m=m, hidden=hidden, inter=inter, attended=attended, qkv=qkv_width,
+                      split_norm=not args.no_split_norm, gb_s=round(layer_bytes / ms / 1e6, 1))
     elif args.op == "norm":
         x = torch.randn(args.tokens, args.hidden, device="cuda").to(dtype)
         residual = torch.randn(args.tokens, args.hidden, device="cuda")

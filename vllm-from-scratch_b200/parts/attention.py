@@ -16,8 +16,8 @@ from typing import Any, Mapping
 import torch
 
 from .. import kernels
-from .base import (MIXERS, CacheView, KVPagesNeed, Mixer, PartEnv, PositionEncoding, StepContext,
-                   WeightInfo)
+from .base import (MIXERS, CacheView, HalfNormedRows, KVPagesNeed, Mixer, Norm, PartEnv, PositionEncoding,
+                   StepContext, WeightInfo)
 
 
 @MIXERS.register("paged_attention")
@@ -77,14 +77,21 @@ class PagedAttention(Mixer):
         return KVPagesNeed(self.num_kv_heads, self.head_dim, self.window)
 
     # ------------------------------------------------------------------ forward
-    def forward(self, x: torch.Tensor, ctx: StepContext, cache: CacheView) -> torch.Tensor:
+    def splits_norms(self, tokens: int) -> bool:
+        return (kernels.split_norm_ok(tokens, self.qkv, fold=False)
+                and kernels.split_norm_ok(tokens, self.out_proj, fold=True))
+
+    def forward(self, x: torch.Tensor | HalfNormedRows, ctx: StepContext, cache: CacheView,
+                fold: tuple[torch.Tensor, Norm] | None = None) -> torch.Tensor | HalfNormedRows:
         if cache.kind != "pages":
             raise ValueError("paged attention needs a cache of pages")
         group = ctx.groups[cache.group]
+        scale = (x.squares, x.eps) if isinstance(x, HalfNormedRows) else None
+        x = x.rows if isinstance(x, HalfNormedRows) else x
         tokens = x.shape[0]
         nq, nkv, d = self.num_heads, self.num_kv_heads, self.head_dim
         qkv = torch.empty((tokens, (nq + 2 * nkv) * d), dtype=x.dtype, device=x.device)
-        kernels.gemm(x, self.qkv, qkv)
+        kernels.gemm(x, self.qkv, qkv, scale=scale)
         store = cache.writable
         eps = self.qk_norm_eps if self.qk_norm_eps is not None else 0.0
         rope = (self.q_norm, self.k_norm, self.position.inverse_frequencies(), self.position.rotary_dim, eps)
@@ -109,5 +116,11 @@ class PagedAttention(Mixer):
                 nq, nkv, d, group.page_size, self.scale, self.window, ctx.max_query_len, ctx.max_seq_len,
                 ctx.num_decode, decode_done=fused > 0)
         out = torch.empty((tokens, self.env.hidden_size), dtype=x.dtype, device=x.device)
-        kernels.gemm(attended, self.out_proj, out)
-        return out
+        if fold is None:
+            kernels.gemm(attended, self.out_proj, out)
+            return out
+        residual, norm = fold
+        weight, eps = norm.split()
+        squares = torch.empty((tokens, self.env.hidden_size // 8), dtype=torch.float32, device=x.device)
+        kernels.gemm(attended, self.out_proj, out, fold=(residual, weight, squares))
+        return HalfNormedRows(out, squares, eps)

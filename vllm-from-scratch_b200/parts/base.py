@@ -110,6 +110,21 @@ class CacheView:
     writable: bool = True
 
 
+@dataclass
+class HalfNormedRows:
+    """Rows half-way through an RMSNorm that is split over the two products around it.
+
+    For float32 residual rows ``v`` and the norm's weights ``g``: ``rows = v * g`` in the run
+    dtype and ``squares`` (float32 ``[T, pieces]``) the pieces of every row's sum of ``v**2``.
+    ``rmsnorm(v) g W^T = rsqrt(sum / width + eps) * ((v g) W^T)``: the product that takes these
+    rows multiplies its result by the root, and no kernel of its own reads and writes the rows
+    to normalise them."""
+
+    rows: torch.Tensor
+    squares: torch.Tensor
+    eps: float
+
+
 # ----------------------------------------------------------------------- parts
 class Part:
     # Whether a step that runs this part may be captured into a CUDA graph and replayed with
@@ -141,6 +156,12 @@ class Norm(Part):
         unchanged."""
         raise NotImplementedError
 
+    def split(self) -> tuple[torch.Tensor, float] | None:
+        """``(weight, eps)`` if the norm is ``v * rsqrt(mean(v**2) + eps) * weight`` over the whole
+        residual width, so that it can be split over the products around it
+        (:class:`HalfNormedRows`); None otherwise."""
+        return None
+
 
 class PositionEncoding(Part):
     """Rotary family: the mixer's fused kernel applies it to queries and keys."""
@@ -164,10 +185,22 @@ class Mixer(Part):
         """``x`` is ``[T, hidden]`` in the run dtype; returns the same shape."""
         raise NotImplementedError
 
+    def splits_norms(self, tokens: int) -> bool:
+        """Whether, for a step of so many tokens, ``forward`` also takes
+        :class:`HalfNormedRows` for ``x`` and a keyword ``fold=(residual, norm)``, with which
+        it adds its result into the float32 ``residual`` itself and returns the
+        :class:`HalfNormedRows` of the sum under ``norm``.  A block only asks a part that
+        says True."""
+        return False
+
 
 class FeedForward(Part):
     def forward(self, x: torch.Tensor, ctx: StepContext) -> torch.Tensor:
         raise NotImplementedError
+
+    def splits_norms(self, tokens: int) -> bool:
+        """As :meth:`Mixer.splits_norms`."""
+        return False
 
 
 class Embedding(Part):
@@ -225,6 +258,22 @@ class Block(Part):
         whose input already sits in ``residual``) and the float32 residual
         stream, updated in place; returns this layer's not-yet-added output."""
         raise NotImplementedError
+
+    # A block may hand its output over already added into the residual and half-normalised
+    # under the *next* block's first norm (:class:`HalfNormedRows`), if both sides say so for
+    # the step's number of tokens; the model then calls ``forward(..., next_norm=norm)`` and
+    # passes what comes back to the next block as its ``x``.  The default is neither.
+    def first_norm(self) -> Norm | None:
+        """The norm this block applies to what it is handed, if it starts with one."""
+        return None
+
+    def takes_half_normed(self, tokens: int) -> bool:
+        """Whether ``x`` may be :class:`HalfNormedRows` under :meth:`first_norm`."""
+        return False
+
+    def folds_into(self, norm: Norm, tokens: int) -> bool:
+        """Whether ``forward`` takes ``next_norm=norm`` and then returns :class:`HalfNormedRows`."""
+        return False
 
 
 # ------------------------------------------------------------------ registries

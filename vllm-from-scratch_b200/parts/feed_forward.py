@@ -10,7 +10,7 @@ from typing import Any, Mapping
 import torch
 
 from .. import kernels
-from .base import FEED_FORWARDS, FeedForward, PartEnv, StepContext, WeightInfo
+from .base import FEED_FORWARDS, FeedForward, HalfNormedRows, Norm, PartEnv, StepContext, WeightInfo
 
 
 @FEED_FORWARDS.register("gated_silu")
@@ -37,10 +37,23 @@ class GatedSiluFeedForward(FeedForward):
         self.gate_up = torch.cat([tensors["gate_proj.weight"], tensors["up_proj.weight"]], dim=0).contiguous()
         self.down = tensors["down_proj.weight"].contiguous()
 
-    def forward(self, x: torch.Tensor, ctx: StepContext) -> torch.Tensor:
+    def splits_norms(self, tokens: int) -> bool:
+        return (kernels.split_norm_ok(tokens, self.gate_up, fold=False, gated=True)
+                and kernels.split_norm_ok(tokens, self.down, fold=True))
+
+    def forward(self, x: torch.Tensor | HalfNormedRows, ctx: StepContext,
+                fold: tuple[torch.Tensor, Norm] | None = None) -> torch.Tensor | HalfNormedRows:
+        scale = (x.squares, x.eps) if isinstance(x, HalfNormedRows) else None
+        x = x.rows if isinstance(x, HalfNormedRows) else x
         tokens = x.shape[0]
         hidden = torch.empty((tokens, self.intermediate_size), dtype=x.dtype, device=x.device)
-        kernels.gated_silu_gemm(x, self.gate_up, hidden)
+        kernels.gated_silu_gemm(x, self.gate_up, hidden, scale=scale)
         out = torch.empty((tokens, self.env.hidden_size), dtype=x.dtype, device=x.device)
-        kernels.gemm(hidden, self.down, out)
-        return out
+        if fold is None:
+            kernels.gemm(hidden, self.down, out)
+            return out
+        residual, norm = fold
+        weight, eps = norm.split()
+        squares = torch.empty((tokens, self.env.hidden_size // 8), dtype=torch.float32, device=x.device)
+        kernels.gemm(hidden, self.down, out, fold=(residual, weight, squares))
+        return HalfNormedRows(out, squares, eps)

@@ -125,9 +125,18 @@ class DecoderModel:
         tokens = token_ids.shape[0]
         residual = torch.empty((tokens, self.hidden_size), dtype=torch.float32, device=token_ids.device)
         self.embedding.forward(token_ids, ctx, residual, self._token_error)
-        x: torch.Tensor | None = None
-        for entry, cache in zip(self.spec.schedule, caches):
-            x = self.layers[entry.layer].forward(x, residual, ctx, cache)
+        x = None
+        blocks = [self.layers[entry.layer] for entry in self.spec.schedule]
+        for number, (block, cache) in enumerate(zip(blocks, caches)):
+            # Two blocks that both say so for this many tokens split the norm between them: the
+            # first adds its output into the residual itself and hands on rows half-normalised
+            # under the second's first norm.
+            after = blocks[number + 1] if number + 1 < len(blocks) else None
+            norm = after.first_norm() if after is not None and after.takes_half_normed(tokens) else None
+            if norm is not None and block.folds_into(norm, tokens):
+                x = block.forward(x, residual, ctx, cache, next_norm=norm)
+            else:
+                x = block.forward(x, residual, ctx, cache)
         return x, residual
 
     def logits(self, x: torch.Tensor | None, residual: torch.Tensor, rows: torch.Tensor) -> torch.Tensor:

@@ -33,6 +33,9 @@ class RMSNorm(Norm):
     def load_weights(self, tensors: Mapping[str, torch.Tensor]) -> None:
         self.weight = tensors["weight"]
 
+    def split(self) -> tuple[torch.Tensor, float] | None:
+        return (self.weight, self.eps) if self.size == self.env.hidden_size else None
+
     def forward(self, x: torch.Tensor | None, residual: torch.Tensor, out: torch.Tensor | None = None,
                 rows: torch.Tensor | None = None) -> torch.Tensor:
         if out is None:
