@@ -409,6 +409,36 @@ def test_split_norm_refusals():
         k.gemm(bf(4, 192), bf(256, 192), bf(4, 256), scale=(torch.ones(4, 24, device="cuda"), 1e-6))
 
 
+# token rows, intermediate width, K: tiles of 2 x 96 and 2 x 128 rows, one block of token rows and many,
+# a last block that is partly empty, the benchmark's prompt through the dispatch
+TENSOR_MEMORY_GATED_SHAPES = [(1, 96, 64), (130, 384, 320), (300, 192, 128), (128, 6144, 2048), (2048, 6144, 2048),
+                              (2304, 1280, 4096), (2048, 480, 192)]
+
+
+@pytest.mark.parametrize("shape", TENSOR_MEMORY_GATED_SHAPES)
+def test_tensor_memory_gated_product(shape):
+    """The feed-forward's first product with its activation on the 5th-generation tensor cores,
+    against the plain version; where the engine's dispatch uses it (whole blocks of 128 token
+    rows from 2048 on) also through ``kernels.gated_silu_gemm``."""
+    from vllm_from_scratch_b200.kernels import gemm_bf16
+    k = kernels()
+    m, inter, width = shape
+    g = torch.Generator(device="cuda").manual_seed(sum(shape))
+    x = torch.randn(m, width, device="cuda", generator=g).bfloat16()
+    w = (torch.randn(2 * inter, width, device="cuda", generator=g) * width ** -0.5).bfloat16()
+    want = torch.empty(m, inter, device="cuda", dtype=torch.bfloat16)
+    plain_ops.gated_silu_gemm(x, w, want)
+    bound = float(want.float().abs().max()) * 2 ** -7
+    got = torch.full_like(want, 7.0)
+    gemm_bf16.tc_gated_gemm(x, w, got)
+    assert float((got.float() - want.float()).abs().max()) <= bound
+    if gemm_bf16.tc_gated_ok(m, inter, width, x, w, got):
+        through = torch.full_like(want, 7.0)
+        k.gated_silu_gemm(x, w, through)
+        assert torch.equal(through, got)
+    assert k.device_error() is None
+
+
 SPLIT_BATCH_SHAPES = [
     # nq, nkv, d, page, q_lens (single tokens first), seq_lens, window
     (8, 2, 64, 16, [1, 1, 1, 40, 70], [300, 64, 1, 40, 170], None),

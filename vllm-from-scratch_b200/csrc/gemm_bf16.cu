@@ -269,6 +269,69 @@ B200_EXPORT int b200_stream_gemm_error() {
     return code;
 }
 
+#include "tensor_map.cuh"
+#include "tc_gemm.cuh"
+namespace b200 {
+
+template <int BN>
+int launch_tc_gated_gemm(const bf16* x, const bf16* w, bf16* y, int M, int inter, int K, cudaStream_t stream) {
+    int* error_flag = stream_error_flag();
+    if (error_flag == nullptr) return fail("tc_gated_gemm", "no error flag");
+    CUtensorMap map_x, map_w;
+    if (!tensor_map_for(x, M, K, kTgRows, &map_x) || !tensor_map_for(w, 2 * inter, K, BN / 2, &map_w))
+        return fail("tc_gated_gemm", "could not encode a tensor map");
+    auto kernel = tc_gated_gemm_kernel<BN>;
+    static bool configured = false;
+    if (!configured) {
+        cudaError_t status = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, TcGemmShape<BN>::kSmem);
+        if (status != cudaSuccess) return fail("tc_gated_gemm", cudaGetErrorString(status));
+        configured = true;
+    }
+    const int tiles = ((M + kTgRows - 1) / kTgRows) * (inter / (BN / 2));
+    const int blocks = tiles < sm_count() ? tiles : sm_count();
+    launch_overlapped(kernel, blocks, kTgThreads, TcGemmShape<BN>::kSmem, stream, map_x, map_w, y, M, inter, K, error_flag);
+    return check_launch("tc_gated_gemm");
+}
+
+// Weight rows per tile (gate and up together) that the tensor-memory gated product would use, 0 if it
+// does not take the shape: the tile with the fewer rounds over the SMs, weighted by its width.
+inline int tc_gated_gemm_tile(int M, int inter, int K) {
+    if (M < 1 || K < kTgK || K % kTgK != 0) return 0;
+    const int sms = sm_count();
+    if (sms <= 0) return 0;
+    int best = 0;
+    long long best_cost = 0;
+    const int candidates[2] = {256, 192};
+    for (int i = 0; i < 2; ++i) {
+        const int tile = candidates[i];
+        if (inter % (tile / 2) != 0) continue;
+        const long long tiles = (long long)((M + kTgRows - 1) / kTgRows) * (inter / (tile / 2));
+        const long long cost = ((tiles + sms - 1) / sms) * tile;
+        if (best == 0 || cost < best_cost) {
+            best = tile;
+            best_cost = cost;
+        }
+    }
+    return best;
+}
+
+}  // namespace b200
+
+// Weight rows per tile of the tensor-memory gated product (tc_gemm.cuh) for M token rows and a
+// [2 * inter, K] matrix, or 0 if the kernel does not take the shape.
+B200_EXPORT int b200_tc_gated_gemm_tile(int M, int inter, int K) { return b200::tc_gated_gemm_tile(M, inter, K); }
+
+// y[M, inter] = silu(x w[:inter]^T) * (x w[inter:]^T), bfloat16, on the 5th-generation tensor cores.
+B200_EXPORT int b200_tc_gated_gemm_bf16(const void* x, const void* w, void* y, int M, int inter, int K, cudaStream_t stream) {
+    using namespace b200;
+    if (M == 0 || inter == 0) return 0;
+    const int tile = tc_gated_gemm_tile(M, inter, K);
+    if (tile == 0) return fail("tc_gated_gemm", "not a shape for the tensor-memory product");
+    if (((uintptr_t)x | (uintptr_t)w | (uintptr_t)y) & 15) return fail("tc_gated_gemm", "operands must be 16-byte aligned");
+    if (tile == 256) return launch_tc_gated_gemm<256>((const bf16*)x, (const bf16*)w, (bf16*)y, M, inter, K, stream);
+    return launch_tc_gated_gemm<192>((const bf16*)x, (const bf16*)w, (bf16*)y, M, inter, K, stream);
+}
+
 // Whether the resident-rows kernel takes the product, in the forms that carry half of an RMSNorm.
 B200_EXPORT int b200_split_norm_gemm_supports(int M, int N, int K, int gated_inter) {
     const int rows = gated_inter > 0 ? gated_inter : N;

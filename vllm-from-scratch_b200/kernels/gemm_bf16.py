@@ -86,6 +86,9 @@ def gemm_bf16(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor) -> None:
 def gated_silu_gemm_bf16(x: torch.Tensor, w_gate_up: torch.Tensor, out: torch.Tensor) -> bool:
     """``out = silu(x w[:I]^T) * (x w[I:]^T)`` in one kernel; False if the shape is
     not one the fused kernel takes (the caller then does it in two steps)."""
+    if tc_gated_ok(x.shape[0], out.shape[1], x.shape[1], x, w_gate_up, out):
+        tc_gated_gemm(x, w_gate_up, out)
+        return True
     if not _small_enough(w_gate_up, True) or not (
             _skinny_ok(x.shape[0], w_gate_up.shape[0], x.shape[1], x, w_gate_up, out)
             or _resident_ok(x.shape[0], x.shape[1], True, x, w_gate_up, out)):
@@ -128,6 +131,34 @@ def split_norm_gemm(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, gated_i
     status = lib.b200_split_norm_gemm_bf16(
         _P(x.data_ptr()), _P(w.data_ptr()), _P(out.data_ptr()), _I(m), _I(n), _I(k), _I(gated_inter),
         _P(squares_in), _I(pieces), ctypes.c_float(eps), _P(residual), _P(weight), _P(squares_out), _stream())
+    if status != 0:
+        raise KernelError(lib.b200_last_error().decode())
+    count_launch()
+
+
+# The gated product on the 5th-generation tensor cores (csrc/tc_gemm.cuh) is ahead of the library's
+# product followed by the activation kernel for whole blocks of 128 token rows from 2048 rows on
+# (microseconds own / library + activation: 12288 x 2048 at 2048 rows 80.3 / 83.3, 4096 rows 159 /
+# 166, 8192 rows 281 / 317; 24576 x 4096 at 2048 rows 301 / 326, 8192 rows 1287 / 1527; 51200 x 5120 at
+# 2048 rows 723 / 857) and level or behind below that and where the last block of rows is partly
+# empty (2112 rows: 92.9 / 86.8), so that is where it is used.
+USE_TC_GATED = True
+TC_GATED_MIN_ROWS = 2048
+
+
+def tc_gated_ok(m: int, inter: int, k: int, *tensors: torch.Tensor) -> bool:
+    if not (USE_TC_GATED and m >= TC_GATED_MIN_ROWS and m % 128 == 0 and all(t.data_ptr() % 16 == 0 for t in tensors)):
+        return False
+    return int(load_library("gemm_bf16").b200_tc_gated_gemm_tile(_I(m), _I(inter), _I(k))) != 0
+
+
+def tc_gated_gemm(x: torch.Tensor, w_gate_up: torch.Tensor, out: torch.Tensor) -> None:
+    """``out = silu(x w[:I]^T) * (x w[I:]^T)`` by the tensor-memory kernel (any number of token rows;
+    K a multiple of 64, I a multiple of 96 or 128)."""
+    from . import KernelError, _stream, count_launch
+    lib = load_library("gemm_bf16")
+    status = lib.b200_tc_gated_gemm_bf16(_P(x.data_ptr()), _P(w_gate_up.data_ptr()), _P(out.data_ptr()), _I(x.shape[0]),
+                                         _I(out.shape[1]), _I(x.shape[1]), _stream())
     if status != 0:
         raise KernelError(lib.b200_last_error().decode())
     count_launch()
