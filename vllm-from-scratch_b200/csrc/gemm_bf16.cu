@@ -238,15 +238,20 @@ int launch_slab(const bf16* x, const bf16* w, OutT* y, int M, int N, int K, int 
         launch_overlapped(kernel, blocks, threads, smem, stream, x, w, y, M, rows, K, error_flag, norm);
         return 0;
     };
-    static bool configured[7] = {};
+    static bool configured[14] = {};
+    const bool normed = norm.squares_in != nullptr || norm.residual != nullptr;
     int rc;
-    if (gated && wide) rc = launch(slab_gemm_kernel<OutT, true, true, false>, configured + 0);
-    else if (gated && deep) rc = launch(slab_gemm_kernel<OutT, true, false, true>, configured + 1);
-    else if (gated) rc = launch(slab_gemm_kernel<OutT, true, false, false>, configured + 6);
-    else if (wide && deep) rc = launch(slab_gemm_kernel<OutT, false, true, true>, configured + 2);
-    else if (wide) rc = launch(slab_gemm_kernel<OutT, false, true, false>, configured + 3);
-    else if (deep) rc = launch(slab_gemm_kernel<OutT, false, false, true>, configured + 4);
-    else rc = launch(slab_gemm_kernel<OutT, false, false, false>, configured + 5);
+#define B200_SLAB(G, W, D, slot)                                                                                   \
+    rc = normed ? launch(slab_gemm_kernel<OutT, G, W, D, true>, configured + 7 + slot)                             \
+                : launch(slab_gemm_kernel<OutT, G, W, D, false>, configured + slot)
+    if (gated && wide) B200_SLAB(true, true, false, 0);
+    else if (gated && deep) B200_SLAB(true, false, true, 1);
+    else if (gated) B200_SLAB(true, false, false, 6);
+    else if (wide && deep) B200_SLAB(false, true, true, 2);
+    else if (wide) B200_SLAB(false, true, false, 3);
+    else if (deep) B200_SLAB(false, false, true, 4);
+    else B200_SLAB(false, false, false, 5);
+#undef B200_SLAB
     if (rc != 0) return -1;
     return check_launch("slab_gemm") == 0 ? 1 : -1;
 }

@@ -58,14 +58,16 @@ struct SlabNorm {
     float* squares_out;             // [rows][N / 8]
 };
 
-template <typename OutT, bool GATED, bool WIDE, bool DEEP>
+// NORM: the launch carries one or both halves of a norm (`norm` is looked at); the plain product
+// is compiled without any of it.
+template <typename OutT, bool GATED, bool WIDE, bool DEEP, bool NORM>
 __global__ void __launch_bounds__(kSlabWarps * 32, GATED ? 3 : (DEEP ? 2 : 4)) slab_gemm_kernel(
     const __nv_bfloat16* __restrict__ x, const __nv_bfloat16* __restrict__ w, OutT* __restrict__ y, int M, int N,
     int K, int* __restrict__ error_flag, const SlabNorm norm) {
     extern __shared__ __align__(128) unsigned char slab_smem[];
     constexpr int kSets = GATED ? 2 : 1;            // sets of eight rows: gate and up, or one
     __shared__ float partial[kSlabWarps][kSets][32][4];
-    __shared__ float row_scale[16];
+    __shared__ float row_scale[NORM ? 16 : 1];
     overlap_trigger();
     const int pitch = K * 2 + 16;
     unsigned char* rows = slab_smem;
@@ -99,23 +101,11 @@ __global__ void __launch_bounds__(kSlabWarps * 32, GATED ? 3 : (DEEP ? 2 : 4)) s
     }
     overlap_wait();                                 // the token rows come from the kernel before this one
 
-    // The pieces of a token row's sum of squares (warp r: row r), asked for now and added up after
-    // the products.
-    constexpr int kPieces = 8;                      // a lane's share of 256 pieces
-    float piece[kPieces];
-    const bool scaled = norm.squares_in != nullptr;
-    if (scaled) {
-        const float* mine = norm.squares_in + (size_t)(warp < M ? warp : 0) * norm.pieces;
-#pragma unroll
-        for (int j = 0; j < kPieces; ++j) {
-            const int i = j * 32 + lane;
-            piece[j] = __ldcg(mine + (i < norm.pieces ? i : 0));
-        }
-    }
+    const bool scaled = NORM && norm.squares_in != nullptr;
 
     // What the warp that stores will add to, asked for ahead of the products.
     float2 before[2] = {make_float2(0.0f, 0.0f), make_float2(0.0f, 0.0f)}, gain = make_float2(0.0f, 0.0f);
-    if (warp == 0 && norm.residual != nullptr) {
+    if (NORM && warp == 0 && norm.residual != nullptr) {
 #pragma unroll
         for (int half = 0; half < (WIDE ? 2 : 1); ++half)
             if (g + half * 8 < M)
@@ -173,16 +163,15 @@ __global__ void __launch_bounds__(kSlabWarps * 32, GATED ? 3 : (DEEP ? 2 : 4)) s
     for (int set = 0; set < kSets; ++set)
 #pragma unroll
         for (int e = 0; e < 4; ++e) partial[warp][set][lane][e] = acc[set][e];
-    for (int row = warp; row < 16; row += kSlabWarps) {
+    // The root of the norm ahead: warp r adds the pieces of token row r's sum of squares, a lane
+    // every 32nd piece, then the lanes' sums in the order of the shuffles.  (Asked for here, after
+    // the products: held in registers across them, the pieces cost more than their round trip.)
+    for (int row = warp; NORM && row < 16; row += kSlabWarps) {
         float scale = 1.0f;
         if (scaled && row < M) {
             const float* mine = norm.squares_in + (size_t)row * norm.pieces;
             float sum = 0.0f;
-            if (row == warp) {
-#pragma unroll
-                for (int j = 0; j < kPieces; ++j) sum += j * 32 + lane < norm.pieces ? piece[j] : 0.0f;
-            }
-            for (int i = (row == warp ? kPieces * 32 : 0) + lane; i < norm.pieces; i += 32) sum += __ldcg(mine + i);
+            for (int i = lane; i < norm.pieces; i += 32) sum += __ldcg(mine + i);
             scale = rsqrtf(warp_sum(sum) / (float)K + norm.eps);
         }
         if (lane == 0) row_scale[row] = scale;
@@ -205,12 +194,12 @@ __global__ void __launch_bounds__(kSlabWarps * 32, GATED ? 3 : (DEEP ? 2 : 4)) s
                 for (int wi = 1; wi < kSlabWarps; ++wi) sum += partial[wi][set][lane][half * 2 + e];
                 sums[set] = sum;
             }
-            const float scale = row_scale[g + half * 8];
+            const float scale = NORM ? row_scale[g + half * 8] : 1.0f;
             const float first = sums[0] * scale;
             total[e] = GATED ? first / (1.0f + expf(-first)) * (sums[kSets - 1] * scale) : first;
         }
         const int token = g + half * 8;
-        if (norm.residual != nullptr) {
+        if (NORM && norm.residual != nullptr) {
             // (the launcher gives this form whole blocks of eight columns and an even N)
             float squares = 0.0f;
             if (token < M) {
