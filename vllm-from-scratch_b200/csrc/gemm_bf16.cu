@@ -238,20 +238,28 @@ int launch_slab(const bf16* x, const bf16* w, OutT* y, int M, int N, int K, int 
         launch_overlapped(kernel, blocks, threads, smem, stream, x, w, y, M, rows, K, error_flag, norm);
         return 0;
     };
-    static bool configured[14] = {};
-    const bool normed = norm.squares_in != nullptr || norm.residual != nullptr;
+    static bool configured[4 * 7] = {};
+    const int halves = (norm.squares_in != nullptr ? 1 : 0) | (norm.residual != nullptr ? 2 : 0);
     int rc;
 #define B200_SLAB(G, W, D, slot)                                                                                   \
-    rc = normed ? launch(slab_gemm_kernel<OutT, G, W, D, true>, configured + 7 + slot)                             \
-                : launch(slab_gemm_kernel<OutT, G, W, D, false>, configured + slot)
-    if (gated && wide) B200_SLAB(true, true, false, 0);
-    else if (gated && deep) B200_SLAB(true, false, true, 1);
-    else if (gated) B200_SLAB(true, false, false, 6);
+    rc = halves == 0   ? launch(slab_gemm_kernel<OutT, G, W, D, 0>, configured + slot)                             \
+         : halves == 1 ? launch(slab_gemm_kernel<OutT, G, W, D, 1>, configured + 7 + slot)                         \
+         : halves == 2 ? launch(slab_gemm_kernel<OutT, G, W, D, 2>, configured + 14 + slot)                        \
+                       : launch(slab_gemm_kernel<OutT, G, W, D, 3>, configured + 21 + slot)
+    // (a gated product never carries the sum: two instantiations each)
+#define B200_SLAB_GATED(W, D, slot)                                                                                \
+    rc = halves == 0 ? launch(slab_gemm_kernel<OutT, true, W, D, 0>, configured + slot)                            \
+                     : launch(slab_gemm_kernel<OutT, true, W, D, 1>, configured + 7 + slot)
+    if (gated && (halves & 2)) return fail("slab_gemm", "a gated product cannot add into the residual");
+    if (gated && wide) B200_SLAB_GATED(true, false, 0);
+    else if (gated && deep) B200_SLAB_GATED(false, true, 1);
+    else if (gated) B200_SLAB_GATED(false, false, 6);
     else if (wide && deep) B200_SLAB(false, true, true, 2);
     else if (wide) B200_SLAB(false, true, false, 3);
     else if (deep) B200_SLAB(false, false, true, 4);
     else B200_SLAB(false, false, false, 5);
 #undef B200_SLAB
+#undef B200_SLAB_GATED
     if (rc != 0) return -1;
     return check_launch("slab_gemm") == 0 ? 1 : -1;
 }

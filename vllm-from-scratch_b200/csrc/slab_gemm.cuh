@@ -58,16 +58,17 @@ struct SlabNorm {
     float* squares_out;             // [rows][N / 8]
 };
 
-// NORM: the launch carries one or both halves of a norm (`norm` is looked at); the plain product
-// is compiled without any of it.
-template <typename OutT, bool GATED, bool WIDE, bool DEEP, bool NORM>
+// NORM: which halves of a norm the launch carries (1: squares_in, the root of the norm ahead; 2:
+// residual, the sum and the first half of the norm behind; 3: both).  Each is an instantiation of
+// its own: the halves cost registers, and these kernels are short enough for that to show.
+template <typename OutT, bool GATED, bool WIDE, bool DEEP, int NORM>
 __global__ void __launch_bounds__(kSlabWarps * 32, GATED ? 3 : (DEEP ? 2 : 4)) slab_gemm_kernel(
     const __nv_bfloat16* __restrict__ x, const __nv_bfloat16* __restrict__ w, OutT* __restrict__ y, int M, int N,
     int K, int* __restrict__ error_flag, const SlabNorm norm) {
     extern __shared__ __align__(128) unsigned char slab_smem[];
     constexpr int kSets = GATED ? 2 : 1;            // sets of eight rows: gate and up, or one
     __shared__ float partial[kSlabWarps][kSets][32][4];
-    __shared__ float row_scale[NORM ? 16 : 1];
+    __shared__ float row_scale[(NORM & 1) ? 16 : 1];
     overlap_trigger();
     const int pitch = K * 2 + 16;
     unsigned char* rows = slab_smem;
@@ -101,11 +102,11 @@ __global__ void __launch_bounds__(kSlabWarps * 32, GATED ? 3 : (DEEP ? 2 : 4)) s
     }
     overlap_wait();                                 // the token rows come from the kernel before this one
 
-    const bool scaled = NORM && norm.squares_in != nullptr;
+    constexpr bool kScaled = (NORM & 1) != 0, kFolded = (NORM & 2) != 0;
 
     // What the warp that stores will add to, asked for ahead of the products.
     float2 before[2] = {make_float2(0.0f, 0.0f), make_float2(0.0f, 0.0f)}, gain = make_float2(0.0f, 0.0f);
-    if (NORM && warp == 0 && norm.residual != nullptr) {
+    if (kFolded && warp == 0) {
 #pragma unroll
         for (int half = 0; half < (WIDE ? 2 : 1); ++half)
             if (g + half * 8 < M)
@@ -166,9 +167,9 @@ __global__ void __launch_bounds__(kSlabWarps * 32, GATED ? 3 : (DEEP ? 2 : 4)) s
     // The root of the norm ahead: warp r adds the pieces of token row r's sum of squares, a lane
     // every 32nd piece, then the lanes' sums in the order of the shuffles.  (Asked for here, after
     // the products: held in registers across them, the pieces cost more than their round trip.)
-    for (int row = warp; NORM && row < 16; row += kSlabWarps) {
+    for (int row = warp; kScaled && row < 16; row += kSlabWarps) {
         float scale = 1.0f;
-        if (scaled && row < M) {
+        if (row < M) {
             const float* mine = norm.squares_in + (size_t)row * norm.pieces;
             float sum = 0.0f;
             for (int i = lane; i < norm.pieces; i += 32) sum += __ldcg(mine + i);
@@ -194,12 +195,12 @@ __global__ void __launch_bounds__(kSlabWarps * 32, GATED ? 3 : (DEEP ? 2 : 4)) s
                 for (int wi = 1; wi < kSlabWarps; ++wi) sum += partial[wi][set][lane][half * 2 + e];
                 sums[set] = sum;
             }
-            const float scale = NORM ? row_scale[g + half * 8] : 1.0f;
+            const float scale = kScaled ? row_scale[g + half * 8] : 1.0f;
             const float first = sums[0] * scale;
             total[e] = GATED ? first / (1.0f + expf(-first)) * (sums[kSets - 1] * scale) : first;
         }
         const int token = g + half * 8;
-        if (NORM && norm.residual != nullptr) {
+        if (kFolded) {
             // (the launcher gives this form whole blocks of eight columns and an even N)
             float squares = 0.0f;
             if (token < M) {
