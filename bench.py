@@ -606,17 +606,27 @@ def write_reference_model(raw: dict, folder: Path) -> None:
     save_file(tensors, str(folder / "model.safetensors"))
 
 
+def ensure_reference_copy() -> bool:
+    """``baseline/_ref/minivllm``, a plain copy of the reference's source tree (it needs no
+    installation): made, if it is missing, from ``$REFERENCE_SOURCE`` or from a folder ``reference``
+    beside this repository.  False if there is neither."""
+    if (REFERENCE_ROOT / "minivllm" / "__init__.py").is_file():
+        return True
+    source = Path(os.environ.get("REFERENCE_SOURCE", str(ROOT.parent / "reference"))) / "minivllm"
+    if not source.is_dir():
+        return False
+    REFERENCE_ROOT.mkdir(parents=True, exist_ok=True)
+    shutil.copytree(source, REFERENCE_ROOT / "minivllm")
+    return True
+
+
 def run_reference(args) -> dict:
     """The unmodified reference (``baseline/_ref/minivllm``, a copy of its source tree) through its
     own entry point: stock ``LLMEngine`` + ``UniProcExecutor`` + ``Worker`` on CUDA in bfloat16, the
     same shape, batch, prompt length, steps and warm-up."""
-    if not (REFERENCE_ROOT / "minivllm" / "__init__.py").is_file():
-        source = Path("/root/reference/minivllm")
-        if not source.is_dir():
-            return {"impl": "reference", "unavailable": "baseline/_ref/minivllm is missing and there is no "
-                                                        "reference source tree to copy it from"}
-        REFERENCE_ROOT.mkdir(parents=True, exist_ok=True)
-        shutil.copytree(source, REFERENCE_ROOT / "minivllm")
+    if not ensure_reference_copy():
+        return {"impl": "reference", "unavailable": "baseline/_ref/minivllm is missing and there is no "
+                                                    "reference source tree to copy it from"}
     import torch
     if not torch.cuda.is_available():
         return {"impl": "reference", "unavailable": "no CUDA device"}
