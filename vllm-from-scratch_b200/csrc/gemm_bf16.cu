@@ -16,6 +16,8 @@
 // [0, I) and [I, 2I) of one matrix (minivllm/models/qwen3.py:44-65 as one kernel).
 #include <stdlib.h>
 
+#include <type_traits>
+
 #include "common.cuh"
 #include "async_copy.cuh"
 
@@ -241,15 +243,18 @@ int launch_slab(const bf16* x, const bf16* w, OutT* y, int M, int N, int K, int 
     static bool configured[4 * 7] = {};
     const int halves = (norm.squares_in != nullptr ? 1 : 0) | (norm.residual != nullptr ? 2 : 0);
     int rc;
+    // (the halves of a norm are for bfloat16 results only: the float32 result has the plain form alone)
+    constexpr int kOne = std::is_same<OutT, bf16>::value ? 1 : 0, kTwo = kOne * 2, kBoth = kOne * 3;
+    if (halves != 0 && kOne == 0) return fail("slab_gemm", "the halves of a norm need a bfloat16 result");
 #define B200_SLAB(G, W, D, slot)                                                                                   \
     rc = halves == 0   ? launch(slab_gemm_kernel<OutT, G, W, D, 0>, configured + slot)                             \
-         : halves == 1 ? launch(slab_gemm_kernel<OutT, G, W, D, 1>, configured + 7 + slot)                         \
-         : halves == 2 ? launch(slab_gemm_kernel<OutT, G, W, D, 2>, configured + 14 + slot)                        \
-                       : launch(slab_gemm_kernel<OutT, G, W, D, 3>, configured + 21 + slot)
+         : halves == 1 ? launch(slab_gemm_kernel<OutT, G, W, D, kOne>, configured + 7 + slot)                      \
+         : halves == 2 ? launch(slab_gemm_kernel<OutT, G, W, D, kTwo>, configured + 14 + slot)                     \
+                       : launch(slab_gemm_kernel<OutT, G, W, D, kBoth>, configured + 21 + slot)
     // (a gated product never carries the sum: two instantiations each)
 #define B200_SLAB_GATED(W, D, slot)                                                                                \
     rc = halves == 0 ? launch(slab_gemm_kernel<OutT, true, W, D, 0>, configured + slot)                            \
-                     : launch(slab_gemm_kernel<OutT, true, W, D, 1>, configured + 7 + slot)
+                     : launch(slab_gemm_kernel<OutT, true, W, D, kOne>, configured + 7 + slot)
     if (gated && (halves & 2)) return fail("slab_gemm", "a gated product cannot add into the residual");
     if (gated && wide) B200_SLAB_GATED(true, false, 0);
     else if (gated && deep) B200_SLAB_GATED(false, true, 1);
