@@ -50,11 +50,32 @@ def tensor_map_cache_self_check(count: int = 5000) -> int:
 
 def decode_splits(num_requests: int, num_kv_heads: int, max_seq_len: int) -> int:
     """Over how many blocks the keys of one (request, key/value head) are split.
-    Three blocks fit on an SM at a time; the split is chosen so that the blocks fill
-    whole rounds of the GPU (a last round with few blocks would leave it idle), with
-    at least 512 keys per block at the planned length (256 for one or two requests)."""
+    Three blocks fit on an SM at a time.  Few pairs: the split is chosen so that the blocks fill
+    whole rounds of the GPU (a last round with few blocks would leave it idle), with at least 512
+    keys per block at the planned length (256 for one or two requests).  Pairs that fill half of
+    the GPU by themselves stream at the memory's rate without any split: there the split only has
+    to keep the last round from being a few lone blocks, and every split more costs its set-up and
+    the merge, which a count of rounds does not see."""
     pairs = max(1, num_requests * num_kv_heads)
     slots = 3 * sm_count()
+    most = max(1, min(16, max_seq_len // 512))
+    if 2 * pairs >= slots:
+        # Time in steps of a lone block's tile of 64 keys: a round of blocks that fills the GPU is
+        # bound by the memory and takes three such steps a tile, a round of few blocks one; a block
+        # costs seven steps beside its tiles, the merge four (measured at 32, 64 and 128 requests of
+        # 2100 keys: no split 51 us against 56 with five at 32; three to five 95 to 98 against 113
+        # without at 64).
+        tiles_whole = -(-max_seq_len // 64)
+        best, best_cost = 1, None
+        for splits in range(1, most + 1):
+            tiles = -(-tiles_whole // splits)
+            blocks = pairs * splits
+            full, last = divmod(blocks, slots)
+            cost = full * tiles * 3.0 + (tiles * max(3.0 * last / slots, 1.0) if last else 0.0) + 7.0
+            cost += 4.0 if splits > 1 else 0.0
+            if best_cost is None or cost < best_cost:
+                best, best_cost = splits, cost
+        return best
     best, best_fill = 1, 0.0
     # One or two requests cannot fill half of the GPU with 512 keys a block: they get 256
     # (a step at batch 1 takes 1.21 against 1.29 ms, at batch 2 1.27 against 1.31; from batch 4
