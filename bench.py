@@ -172,33 +172,44 @@ def prefill_all(runner, ids: list[str], prompts: list[list[int]]) -> None:
 
 
 def measure_prefill(runner, config, tokens: int) -> dict:
-    """One prompt of ``tokens`` tokens in one step (one row of logits), as a graph replay: the
-    median of CUDA-event times of single steps, at least three and at least 200 ms of them."""
+    """One prompt of ``tokens`` tokens in one step (one row of logits), as a graph replay: steps of
+    different requests queued one behind the other the way the engine queues steps that sample
+    nothing (the host packs the next while the device runs the last), timed by CUDA events around
+    regions of them: the median per step over at least three regions of at least 200 ms."""
     import torch
     from vllm_from_scratch_b200 import StepEntry
     from vllm_from_scratch_b200.engine.decode_graph import MixedGraphs
     steps = MixedGraphs(runner, tokens)
-    times: list[float] = []
-    number = 0
+    counter = [0]
+
+    def one_step() -> None:
+        request_id = f"prefill-{counter[0]}"
+        prompt = random_prompt(config.vocab_size, tokens, seed=5000 + counter[0] % 7)
+        counter[0] += 1
+        runner.manager.admit(request_id)
+        assert runner.manager.allocate(request_id, tokens)
+        steps.run([StepEntry(request_id, prompt, 0, [tokens - 1])])
+        runner.manager.release(request_id)
+
+    def region(count: int) -> float:
+        begin, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        torch.cuda.synchronize()
+        begin.record()
+        for _ in range(count):
+            one_step()
+        end.record()
+        torch.cuda.synchronize()
+        return begin.elapsed_time(end) / count
+
+    for _ in range(3):                      # the first goes the ordinary way, the second is the capture
+        one_step()
+    torch.cuda.synchronize()
     with ClockSampler() as clocks:
-        while len(times) < MIN_REPEATS or sum(times) < MIN_REGION_MS:
-            request_id = f"prefill-{number}"
-            prompt = random_prompt(config.vocab_size, tokens, seed=5000 + number)
-            runner.manager.admit(request_id)
-            assert runner.manager.allocate(request_id, tokens)
-            begin, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-            torch.cuda.synchronize()
-            begin.record()
-            steps.run([StepEntry(request_id, prompt, 0, [tokens - 1])])
-            end.record()
-            torch.cuda.synchronize()
-            if number >= 2:                 # the first goes the ordinary way, the second is the capture
-                times.append(begin.elapsed_time(end))
-            runner.manager.release(request_id)
-            number += 1
-            if number > 400:
-                break
-    return {"ms": statistics.median(times), "repeats": len(times), "spread": spread(times), "clocks": clocks.summary()}
+        estimate = region(3)
+        count = max(3, math.ceil(MIN_REGION_MS / estimate))
+        times = [region(count) for _ in range(MIN_REPEATS)]
+    return {"ms": statistics.median(times), "repeats": len(times), "steps_timed": count, "spread": spread(times),
+            "clocks": clocks.summary()}
 
 
 class DecodeLoop:
@@ -403,8 +414,8 @@ def run_small(args, measured, peak_kind) -> dict:
     prefill_ms = prefill_point["ms"]
     prefill = {"value": round(tokens * 1000.0 / prefill_ms, 1), "tokens": tokens, "ms": round(prefill_ms, 3),
                "frac": round(flops / (prefill_ms * 1e-3) / (measured["bf16_tflops"] * 1e12), 4),
-               "repeats": prefill_point["repeats"], "spread": prefill_point["spread"],
-               "clocks": prefill_point["clocks"]}
+               "repeats": prefill_point["repeats"], "steps_timed": prefill_point["steps_timed"],
+               "spread": prefill_point["spread"], "clocks": prefill_point["clocks"]}
     return {
         "metric": "decode tokens/s (Qwen3-1.7B shape, bf16, random weights)",
         "value": round(main_point["tok_s"], 1), "unit": "tokens/s", "n_gpus": 1, "steps": args.steps,
