@@ -246,7 +246,7 @@ class DecodeLoop:
                 entries.append(StepEntry(request_id, [feed[index][row]], self.position, [0]))
             logits = self.graphs.run(entries)
             kernels.sample(logits, self.temperature, self.zeros_i, self.ones_f, self.zeros_f, self.keys, self.keys,
-                           self.picked, 1e-5)
+                           self.picked, 1e-5, 1)        # every row is greedy: the kernel for rows without a filter alone
             self.position += 1
         end.record()
         torch.cuda.synchronize()

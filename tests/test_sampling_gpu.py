@@ -91,6 +91,38 @@ def test_same_key_same_token_and_large_vocabulary():
     assert bool(keep[a].all())
 
 
+@pytest.mark.parametrize("vocab", [503, 4096, 151936])
+def test_rows_with_and_without_filters_draw_alike(vocab):
+    """Rows without a filter and rows with one run in different kernels.  A filter that keeps
+    every token (top-k of the whole vocabulary) must give the token of the row without it, in
+    one call with rows of both kinds and in calls that launch one kernel only."""
+    import vllm_from_scratch_b200.kernels as k
+    g = torch.Generator().manual_seed(vocab)
+    n = 12
+    logits = (torch.randn(n, vocab, generator=g) * 2).cuda()
+    logits[5] = float("-inf")                            # nothing to draw from: the first token
+    seeds = torch.arange(100, 100 + n, dtype=torch.int64, device="cuda")
+    index = torch.arange(n, dtype=torch.int64, device="cuda") % 5
+    temperature = torch.full((n,), 0.8, device="cuda")
+    temperature[3] = 0.0                                 # a greedy row among them
+    ones, zeros = torch.ones(n, device="cuda"), torch.zeros(n, device="cuda")
+    none = torch.zeros(n, dtype=torch.int32, device="cuda")
+    whole = torch.full((n,), vocab, dtype=torch.int32, device="cuda")
+    mixed = torch.where(torch.arange(n, device="cuda") % 2 == 0, none, whole)
+
+    def run(top_k, kinds):
+        out = torch.full((n,), -1, dtype=torch.int32, device="cuda")
+        k.sample(logits, temperature, top_k, ones, zeros, seeds, index, out, 1e-5, kinds)
+        return out.cpu().tolist()
+
+    plain, filtered = run(none, 1), run(whole, 3)
+    assert plain == filtered == run(mixed, 3) == run(none, 3)
+    assert plain[3] == int(logits[3].argmax()) and plain[5] == 0
+    assert len(set(plain)) > 3
+    with pytest.raises(k.KernelError):
+        run(none, 0)
+
+
 def _large_rows():
     g = torch.Generator().manual_seed(21)
     vocab = 151936

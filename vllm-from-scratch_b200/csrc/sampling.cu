@@ -1,5 +1,5 @@
-// Sampling on the device: penalties, the mask of stop tokens, and one kernel that
-// turns a row of float32 logits into a token: greedy argmax, or temperature ->
+// Sampling on the device: penalties, the mask of stop tokens, and two kernels (one for rows
+// without a filter, one for rows with) that turn a row of float32 logits into a token: greedy argmax, or temperature ->
 // min-p -> top-k -> top-p -> a draw, as the reference orders them
 // (minivllm/sample/sampler.py:243-288, minivllm/sample/ops/topk_topp_sampler.py:48-90).
 //
@@ -18,7 +18,6 @@
 // keyed by (seed, index of the generated token, token id), equal in distribution
 // to the reference's argmax(p_i / E_i); the keying follows minivllm/worker/gpu/
 // sample/gumbel.py:94-131 (the stream depends on the position, not on call order).
-#include <curand_kernel.h>
 
 #include "common.cuh"
 
@@ -197,6 +196,114 @@ __device__ unsigned select_mass_from_below(Each&& each, unsigned cut, unsigned l
     return prefix;
 }
 
+// Four uniform numbers in (0, 1] for tokens 4 c .. 4 c + 3 of the draw-th generated token of a
+// request with this seed: Philox-4x32 with ten rounds (Salmon et al., "Parallel random numbers: as
+// easy as 1, 2, 3"), the key the seed, the counter (c, 0, draw).  A function of its arguments
+// alone: no state is set up or skipped ahead, which is most of what a generator object costs when
+// every group of four tokens has a counter of its own.
+__device__ __forceinline__ void philox_uniform4(unsigned long long seed, unsigned long long draw, unsigned c, float (&u)[4]) {
+    unsigned k0 = (unsigned)seed, k1 = (unsigned)(seed >> 32);
+    unsigned x0 = c, x1 = 0u, x2 = (unsigned)draw, x3 = (unsigned)(draw >> 32);
+#pragma unroll
+    for (int round = 0; round < 10; ++round) {
+        const unsigned hi0 = __umulhi(0xD2511F53u, x0), lo0 = 0xD2511F53u * x0;
+        const unsigned hi1 = __umulhi(0xCD9E8D57u, x2), lo1 = 0xCD9E8D57u * x2;
+        x0 = hi1 ^ x1 ^ k0;
+        x1 = lo1;
+        x2 = hi0 ^ x3 ^ k1;
+        x3 = lo0;
+        k0 += 0x9E3779B9u;
+        k1 += 0xBB67AE85u;
+    }
+    const unsigned x[4] = {x0, x1, x2, x3};
+#pragma unroll
+    for (int j = 0; j < 4; ++j) u[j] = (float)(x[j] >> 8) * 5.9604644775390625e-8f + 2.98023223876953125e-8f;    // (n + 1/2) / 2^24
+}
+
+// A row that needs no filter: the argmax, or temperature and a draw with every token kept.
+// The host states the same rule when it decides which of the two kernels to launch.
+__device__ __forceinline__ bool plain_row(float temp, int k, float p, float mp, float greedy_eps) {
+    return temp < greedy_eps || (k <= 0 && p >= 1.0f && mp <= 0.0f);
+}
+
+// Plain rows, a cluster of blocks to a row: one pass over the logits (the argmax of x, or of
+// x / T - log(E) with the argmax of x / T beside it for a row that holds no finite number), each
+// block over every kPlainCluster-th stretch of the row; the blocks' results meet in the shared
+// memory of the cluster's first block.  The draw costs a few hundred instructions per four tokens,
+// so a row is bound by the instruction rate of the SMs it runs on, not by memory.
+constexpr int kPlainCluster = 8;
+constexpr int kPlainThreads = 512;
+
+__global__ void __cluster_dims__(kPlainCluster, 1, 1) __launch_bounds__(kPlainThreads) sample_plain_kernel(
+    const float* __restrict__ logits, int vocab, const float* __restrict__ temperature,
+    const int* __restrict__ top_k, const float* __restrict__ top_p, const float* __restrict__ min_p,
+    const unsigned long long* __restrict__ seeds, const unsigned long long* __restrict__ draw_index,
+    int* __restrict__ tokens, float greedy_eps) {
+    __shared__ ArgMax scratch[33];
+    __shared__ ArgMax shares[2 * kPlainCluster];        // of the cluster's first block: every block's best and top
+    const int row = blockIdx.x / kPlainCluster, tid = threadIdx.x;
+    unsigned rank;
+    asm volatile("mov.u32 %0, %%cluster_ctarank;\n" : "=r"(rank));
+    const float temp = temperature[row];
+    if (!plain_row(temp, top_k[row], top_p[row], min_p[row], greedy_eps)) return;      // the whole cluster leaves
+    const bool greedy = temp < greedy_eps;
+    const float* x = logits + (size_t)row * vocab;
+    const unsigned long long seed = seeds[row], draw = draw_index[row];
+    ArgMax best{-INFINITY, 0x7fffffff}, top{-INFINITY, 0x7fffffff};
+    const int chunks = (vocab + 3) >> 2;
+    const bool vec = (vocab & 3) == 0 && ((uintptr_t)x & 15) == 0;
+    for (int c = (int)rank * kPlainThreads + tid; c < chunks; c += kPlainCluster * kPlainThreads) {
+        float xs[4];
+        if (vec) {
+            const float4 v = reinterpret_cast<const float4*>(x)[c];
+            xs[0] = v.x; xs[1] = v.y; xs[2] = v.z; xs[3] = v.w;
+        } else {
+#pragma unroll
+            for (int j = 0; j < 4; ++j) xs[j] = 4 * c + j < vocab ? x[4 * c + j] : -INFINITY;
+        }
+        if (greedy) {
+#pragma unroll
+            for (int j = 0; j < 4; ++j)
+                if (4 * c + j < vocab) best = better(best, ArgMax{xs[j], 4 * c + j});
+            continue;
+        }
+        float us[4];
+        philox_uniform4(seed, draw, (unsigned)c, us);
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+            const int i = 4 * c + j;
+            if (i >= vocab) break;
+            const float y = xs[j] / temp;
+            top = better(top, ArgMax{y, i});
+            const float e = fmaxf(-logf(us[j]), 1e-30f);
+            best = better(best, ArgMax{y - logf(e), i});
+        }
+    }
+    best = block_argmax(best, scratch);
+    if (!greedy) top = block_argmax(top, scratch);
+    if (tid == 0) {
+        unsigned mine = (unsigned)__cvta_generic_to_shared(shares + rank), first;
+        asm volatile("mapa.shared::cluster.u32 %0, %1, 0;\n" : "=r"(first) : "r"(mine));
+        asm volatile("st.shared::cluster.b32 [%0], %1;\n" ::"r"(first), "r"(__float_as_uint(best.value)) : "memory");
+        asm volatile("st.shared::cluster.b32 [%0], %1;\n" ::"r"(first + 4u), "r"((unsigned)best.index) : "memory");
+        asm volatile("st.shared::cluster.b32 [%0], %1;\n" ::"r"(first + 8u * kPlainCluster), "r"(__float_as_uint(top.value)) : "memory");
+        asm volatile("st.shared::cluster.b32 [%0], %1;\n" ::"r"(first + 8u * kPlainCluster + 4u), "r"((unsigned)top.index) : "memory");
+    }
+    asm volatile("barrier.cluster.arrive.release.aligned;\n" ::: "memory");
+    asm volatile("barrier.cluster.wait.acquire.aligned;\n" ::: "memory");
+    if (rank == 0 && tid < 32) {
+        ArgMax b = tid < kPlainCluster ? shares[tid] : ArgMax{-INFINITY, 0x7fffffff};
+        ArgMax t = tid < kPlainCluster ? shares[kPlainCluster + tid] : ArgMax{-INFINITY, 0x7fffffff};
+#pragma unroll
+        for (int offset = kPlainCluster / 2; offset > 0; offset >>= 1) {
+            b = better(b, ArgMax{__shfl_xor_sync(0xffffffffu, b.value, offset), __shfl_xor_sync(0xffffffffu, b.index, offset)});
+            t = better(t, ArgMax{__shfl_xor_sync(0xffffffffu, t.value, offset), __shfl_xor_sync(0xffffffffu, t.index, offset)});
+        }
+        if (tid == 0) tokens[row] = b.index == 0x7fffffff ? t.index : b.index;
+    }
+}
+
+// The other rows, one block per row.
 __global__ void __launch_bounds__(kSampleThreads, 1) sample_kernel(
     const float* __restrict__ logits, int vocab, const float* __restrict__ temperature,
     const int* __restrict__ top_k, const float* __restrict__ top_p, const float* __restrict__ min_p,
@@ -209,13 +316,7 @@ __global__ void __launch_bounds__(kSampleThreads, 1) sample_kernel(
     const int tid = threadIdx.x;
     const float temp = temperature[row];
 
-    if (temp < greedy_eps) {
-        ArgMax mine{-INFINITY, 0x7fffffff};
-        for_each_logit(x, vocab, [&](float v, int i) { mine = better(mine, ArgMax{v, i}); });
-        mine = block_argmax(mine, sh.arg_scratch);
-        if (tid == 0) tokens[row] = mine.index;
-        return;
-    }
+    if (plain_row(temp, top_k[row], top_p[row], min_p[row], greedy_eps)) return;       // the other kernel's
 
     // Scaled logits y = x / T; maximum and normaliser.
     ArgMax top{-INFINITY, 0x7fffffff};
@@ -375,10 +476,8 @@ __global__ void __launch_bounds__(kSampleThreads, 1) sample_kernel(
 #pragma unroll
         for (int j = 0; j < 4; ++j) any = any || (4 * c + j < vocab && ordered_key(xs[j] / temp) >= cut);
         if (!any) continue;                        // no kept token here: its random numbers are not needed
-        curandStatePhilox4_32_10_t state;
-        curand_init(seed, draw, 4ull * (unsigned long long)c, &state);
-        const float4 u = curand_uniform4(&state);
-        const float us[4] = {u.x, u.y, u.z, u.w};
+        float us[4];
+        philox_uniform4(seed, draw, (unsigned)c, us);
 #pragma unroll
         for (int j = 0; j < 4; ++j) {
             const int i = 4 * c + j;
@@ -431,12 +530,22 @@ __global__ void mask_tokens_kernel(float* __restrict__ logits, int vocab, const 
 B200_EXPORT int b200_sample(const float* logits, int rows, int vocab, const float* temperature,
                             const int* top_k, const float* top_p, const float* min_p,
                             const unsigned long long* seeds, const unsigned long long* draw_index,
-                            int* tokens, float greedy_eps, cudaStream_t stream) {
+                            int* tokens, float greedy_eps, int kinds, cudaStream_t stream) {
+    // kinds: bit 0 = some row may be plain (greedy, or temperature alone), bit 1 = some row may
+    // have a filter; a kernel none of whose rows can be there is not launched.
     using namespace b200;
     if (rows == 0) return 0;
     if (vocab <= 0) return fail("sample", "vocabulary must be positive");
-    sample_kernel<<<rows, kSampleThreads, 0, stream>>>(logits, vocab, temperature, top_k, top_p, min_p,
-                                                       seeds, draw_index, tokens, greedy_eps);
+    if ((kinds & 3) == 0) return fail("sample", "neither kind of row is said to be there");
+    if (kinds & 1) {
+        sample_plain_kernel<<<rows * kPlainCluster, kPlainThreads, 0, stream>>>(logits, vocab, temperature, top_k, top_p, min_p,
+                                                                                seeds, draw_index, tokens, greedy_eps);
+        const int status = check_launch("sample (plain rows)");
+        if (status) return status;
+    }
+    if (kinds & 2)
+        sample_kernel<<<rows, kSampleThreads, 0, stream>>>(logits, vocab, temperature, top_k, top_p, min_p,
+                                                           seeds, draw_index, tokens, greedy_eps);
     return check_launch("sample");
 }
 

@@ -380,10 +380,13 @@ _U64 = ctypes.c_uint64
 
 def sample(logits: torch.Tensor, temperature: torch.Tensor, top_k: torch.Tensor, top_p: torch.Tensor,
            min_p: torch.Tensor, seeds: torch.Tensor, draw_index: torch.Tensor, tokens: torch.Tensor,
-           greedy_eps: float) -> None:
+           greedy_eps: float, kinds: int = 3) -> None:
     """One token per row of float32 ``logits``: argmax where ``temperature`` is
     below ``greedy_eps``, otherwise temperature, min-p, top-k, top-p and a seeded
-    draw keyed by ``(seeds[r], draw_index[r], token id)``."""
+    draw keyed by ``(seeds[r], draw_index[r], token id)``.  Rows without a filter
+    (greedy, or ``top_k <= 0``, ``top_p >= 1`` and ``min_p <= 0``) and rows with one
+    have a kernel each; a caller that knows the values may say in ``kinds`` which
+    are there (bit 0: rows without a filter, bit 1: rows with) and save a launch."""
     rows, vocab = logits.shape
     _run("sampling", "b200_sample",
          _P(_check("logits", logits, torch.float32)), _I(rows), _I(vocab),
@@ -393,7 +396,7 @@ def sample(logits: torch.Tensor, temperature: torch.Tensor, top_k: torch.Tensor,
          _P(_check("min_p", min_p, torch.float32, (rows,))),
          _P(_check("seeds", seeds, torch.int64, (rows,))),
          _P(_check("draw index", draw_index, torch.int64, (rows,))),
-         _P(_check("sampled tokens", tokens, torch.int32, (rows,))), _F(greedy_eps), _stream())
+         _P(_check("sampled tokens", tokens, torch.int32, (rows,))), _F(greedy_eps), _I(kinds), _stream())
 
 
 def apply_penalties(logits: torch.Tensor, offsets: torch.Tensor, seen_tokens: torch.Tensor,

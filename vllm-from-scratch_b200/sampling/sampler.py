@@ -59,9 +59,11 @@ class Sampler:
         seed = np.array([s & 0x7FFFFFFFFFFFFFFF for s in seeds], dtype=np.int64)
         draw = np.array([len(o) + ahead for o in outputs], dtype=np.int64)
         tokens = torch.empty(rows + extra, dtype=torch.int32, device=logits.device)
+        filtered = (temperature >= GREEDY_EPS) & ((top_k > 0) | ~(top_p >= 1.0) | ~(min_p <= 0.0))
+        kinds = (1 if not filtered.all() else 0) | (2 if filtered.any() else 0)
         kernels.sample(logits, self._to_device(temperature), self._to_device(top_k),
                        self._to_device(top_p), self._to_device(min_p), self._to_device(seed),
-                       self._to_device(draw), tokens[:rows], GREEDY_EPS)
+                       self._to_device(draw), tokens[:rows], GREEDY_EPS, kinds)
         return tokens
 
     def _penalties(self, logits, params, prompts, outputs) -> None:
