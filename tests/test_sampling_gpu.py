@@ -132,7 +132,10 @@ def _large_rows():
     tail[torch.randperm(vocab, generator=g)[:100]] = torch.randn(100, generator=g)
     peaked = torch.randn(vocab, generator=g)
     peaked[torch.randperm(vocab, generator=g)[:6]] += torch.tensor([9.0, 8.5, 8.0, 7.5, 7.0, 6.5])
-    return {"spread": spread, "crowd": crowd, "tail": tail, "peaked": peaked}
+    flat = torch.randn(vocab, generator=g)                       # thousands of tokens in the bin of a top-p threshold
+    ties = torch.zeros(vocab)                                    # no division of a bin tells these apart
+    ties[torch.randperm(vocab, generator=g)[:3]] = torch.tensor([0.5, 0.25, 0.125])
+    return {"spread": spread, "crowd": crowd, "tail": tail, "peaked": peaked, "flat": flat, "ties": ties}
 
 
 @pytest.mark.parametrize("name,temperature,top_k,top_p,min_p", [
@@ -140,11 +143,14 @@ def _large_rows():
     ("crowd", 1.0, 6, 1.0, 0.0), ("crowd", 1.0, 70000, 1.0, 0.0), ("crowd", 1.0, 0, 0.5, 0.0),
     ("crowd", 1.0, 50000, 0.7, 0.0), ("tail", 1.0, 500, 1.0, 0.0), ("tail", 1.0, 40, 0.9, 0.0),
     ("tail", 1.0, 0, 0.999999, 0.0), ("peaked", 1.0, 0, 0.6, 0.0), ("peaked", 1.3, 4, 0.95, 0.001),
+    ("flat", 0.8, 0, 0.9, 0.0), ("flat", 0.8, 20000, 0.5, 0.0), ("flat", 1.0, 0, 0.999, 0.02),
+    ("ties", 1.0, 3, 1.0, 0.0), ("ties", 1.0, 10, 1.0, 0.0), ("ties", 1.0, 0, 1.0, 0.9),
 ])
 def test_filters_on_a_large_vocabulary(name, temperature, top_k, top_p, min_p):
-    """The threshold search looks at the row coarsely first and then selects inside one
-    bin held in shared memory; thresholds in a crowded bin or in the far tail take the
-    path over the whole row.  All of them must keep the reference's set."""
+    """The threshold search looks at the row coarsely first, divides a crowded bin again and
+    then selects among the keys of one bin held in shared memory; a threshold in the far tail
+    or among thousands of equal logits takes the path over the whole row.  All of them must
+    keep the reference's set."""
     row = _large_rows()[name]
     keep = plain_keep_mask(row, temperature, top_k, top_p, min_p)
     tokens = draw(row, 2048, temperature, top_k, top_p, min_p)

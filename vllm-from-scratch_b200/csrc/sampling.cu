@@ -4,15 +4,16 @@
 // (minivllm/sample/sampler.py:243-288, minivllm/sample/ops/topk_topp_sampler.py:48-90).
 //
 // Instead of sorting the vocabulary, each filter is a threshold on the scaled
-// logit found by radix selection over the order-preserving integer image of the
-// float (four passes of 256 bins): top-k by counts, top-p by probability mass in
+// logit found by selection: top-k by counts, top-p by probability mass in
 // 2^-40 fixed point, so that the sums do not depend on the order of the atomics
-// and a seed always reproduces its tokens.  The selection does not run over the
-// whole row: one pass sorts the kept tokens into coarse bins by their distance
-// below the maximum, the bin that holds the threshold is copied into shared memory
-// (a few thousand keys at most) and the radix selection runs there; only a
-// threshold in the far tail, or a bin too crowded for the list, falls back to
-// selecting over the row.  Ties at a threshold are all kept (the
+// and a seed always reproduces its tokens.  A row is shared by a cluster of eight
+// blocks.  One pass sorts the kept tokens into coarse bins by their distance
+// below the maximum; the bin that holds the threshold is divided again while it
+// holds more tokens than fit into shared memory, then its keys are copied there and
+// a radix selection over the order-preserving integer image of the float (four
+// passes of 256 bins) runs on them.  Only a threshold in the far tail, or thousands
+// of tokens within a few units in the last place of each other, fall back to radix
+// selection over the row.  Ties at a threshold are all kept (the
 // reference keeps ties at the k-th value too, and breaks top-p ties by sort order).
 // The draw is Gumbel-max: argmax(x_i - log(E_i)), E_i exponential from Philox
 // keyed by (seed, index of the generated token, token id), equal in distribution
@@ -22,8 +23,6 @@
 #include "common.cuh"
 
 namespace b200 {
-
-constexpr int kSampleThreads = 1024;
 
 __device__ __forceinline__ unsigned ordered_key(float v) {
     const unsigned u = __float_as_uint(v);
@@ -68,28 +67,6 @@ __device__ ArgMax block_argmax(ArgMax mine, ArgMax* scratch) {
     return result;
 }
 
-// One block per row.
-// Calls f(value, index) for every logit of a row, this thread's share.  A block has a whole
-// row to itself, so each thread keeps four 16-byte loads in flight where the row allows it.
-template <typename F>
-__device__ __forceinline__ void for_each_logit(const float* __restrict__ x, int vocab, F&& f) {
-    const int tid = threadIdx.x, step = blockDim.x;
-    if ((vocab & 3) == 0 && ((uintptr_t)x & 15) == 0) {
-        const float4* x4 = reinterpret_cast<const float4*>(x);
-        const int quads = vocab >> 2;
-#pragma unroll 4
-        for (int i = tid; i < quads; i += step) {
-            const float4 v = x4[i];
-            f(v.x, 4 * i);
-            f(v.y, 4 * i + 1);
-            f(v.z, 4 * i + 2);
-            f(v.w, 4 * i + 3);
-        }
-    } else {
-        for (int i = tid; i < vocab; i += step) f(x[i], i);
-    }
-}
-
 __device__ __forceinline__ float key_value(unsigned key) {
     return __uint_as_float((key & 0x80000000u) ? (key & 0x7fffffffu) : ~key);
 }
@@ -100,100 +77,55 @@ __device__ __forceinline__ unsigned long long fixed_mass(float y, float y_max) {
     return __float2ull_rz(expf(y - y_max) * 1099511627776.0f);
 }
 
-// A first, coarse look at a row: kept tokens by how far they lie below the maximum, eight
-// bins per unit, the last bin for everything 31.875 and more below.  Bin indices fall as
-// the logit rises, so bins are ranges of the key order.  Random-looking logits spread
-// over many bins, which keeps the shared-memory atomics apart; the crowded far bin is
-// counted in registers.
-constexpr int kCoarseBins = 256;
-constexpr float kCoarsePerUnit = 8.0f;
-constexpr int kListCapacity = 6144;             // candidates of one coarse bin held in shared memory
+// ---- a cluster of blocks to a row ------------------------------------------------------------
+// The blocks of a cluster share a row: each walks over every kRowCluster-th stretch of it, adds
+// what it finds to tables in its own shared memory, and after a barrier of the cluster every block
+// sums the tables of all (through distributed shared memory) and takes the same decision from the
+// same numbers, so that all blocks follow one path and meet at the same barriers.
+constexpr int kRowCluster = 8;
 
-__device__ __forceinline__ int coarse_bin(float y, float y_max) {
-    const float d = (y_max - y) * kCoarsePerUnit;
-    return d >= (float)(kCoarseBins - 1) ? kCoarseBins - 1 : (int)d;
+__device__ __forceinline__ unsigned cluster_rank() {
+    unsigned rank;
+    asm volatile("mov.u32 %0, %%cluster_ctarank;\n" : "=r"(rank));
+    return rank;
 }
 
-struct SampleShared {
-    ArgMax arg_scratch[33];
-    unsigned long long bins[256];               // one radix pass: counts or masses per byte value
-    unsigned coarse_mass_lo[kCoarseBins], coarse_mass_hi[kCoarseBins];     // 64-bit sums kept as two words
-    unsigned coarse_count[kCoarseBins];
-    unsigned list[kListCapacity];               // keys of the kept tokens of one coarse bin
-    unsigned list_size;
-    unsigned prefix_key;
-    unsigned long long carry;
-    int chosen_bin;
-    unsigned long long chosen_before;           // count above / mass below the chosen bin
-};
-
-// The k-th largest key among the keys >= cut that `each` visits (`each(f)` calls f(key) for
-// this thread's share).  Fewer than k such keys: the smallest possible prefix, which cuts nothing.
-template <typename Each>
-__device__ unsigned select_kth_largest(Each&& each, unsigned cut, int k, SampleShared& sh) {
-    const int tid = threadIdx.x;
-    unsigned prefix = 0;
-    int remaining = k;
-    for (int pass = 0; pass < 4; ++pass) {
-        const int shift = 24 - 8 * pass;
-        const unsigned mask = pass == 0 ? 0u : (0xffffffffu << (shift + 8));
-        for (int b = tid; b < 256; b += blockDim.x) sh.bins[b] = 0ull;
-        __syncthreads();
-        each([&](unsigned key) {
-            if (key >= cut && (key & mask) == prefix) atomicAdd(&sh.bins[(key >> shift) & 255u], 1ull);
-        });
-        __syncthreads();
-        if (tid == 0) {
-            int b = 255;
-            unsigned long long above = 0;
-            for (; b > 0; --b) {
-                if (above + sh.bins[b] >= (unsigned long long)remaining) break;
-                above += sh.bins[b];
-            }
-            sh.prefix_key = prefix | ((unsigned)b << shift);
-            sh.carry = above;
-        }
-        __syncthreads();
-        prefix = sh.prefix_key;
-        remaining -= (int)sh.carry;
-        __syncthreads();
-    }
-    return prefix;
+__device__ __forceinline__ void cluster_sync() {
+    asm volatile("barrier.cluster.arrive.release.aligned;\n" ::: "memory");
+    asm volatile("barrier.cluster.wait.acquire.aligned;\n" ::: "memory");
 }
 
-// The smallest key at which the mass of the visited keys >= cut, summed from the smallest
-// key up and starting from `below`, first exceeds `target`.
-template <typename Each>
-__device__ unsigned select_mass_from_below(Each&& each, unsigned cut, unsigned long long target,
-                                           unsigned long long below, float y_max, SampleShared& sh) {
-    const int tid = threadIdx.x;
-    unsigned prefix = 0;
-    for (int pass = 0; pass < 4; ++pass) {
-        const int shift = 24 - 8 * pass;
-        const unsigned mask = pass == 0 ? 0u : (0xffffffffu << (shift + 8));
-        for (int b = tid; b < 256; b += blockDim.x) sh.bins[b] = 0ull;
-        __syncthreads();
-        each([&](unsigned key) {
-            if (key >= cut && (key & mask) == prefix)
-                atomicAdd(&sh.bins[(key >> shift) & 255u], fixed_mass(key_value(key), y_max));
-        });
-        __syncthreads();
-        if (tid == 0) {
-            int b = 0;
-            unsigned long long mass = below;
-            for (; b < 255; ++b) {
-                if (mass + sh.bins[b] > target) break;       // this bin holds the first kept token
-                mass += sh.bins[b];
-            }
-            sh.prefix_key = prefix | ((unsigned)b << shift);
-            sh.carry = mass;
-        }
-        __syncthreads();
-        prefix = sh.prefix_key;
-        below = sh.carry;
-        __syncthreads();
+__device__ __forceinline__ unsigned peer_address(const void* mine, unsigned rank) {
+    unsigned there;
+    asm volatile("mapa.shared::cluster.u32 %0, %1, %2;\n" : "=r"(there) : "r"((unsigned)__cvta_generic_to_shared(mine)), "r"(rank));
+    return there;
+}
+
+__device__ __forceinline__ unsigned peer_u32(const void* mine, unsigned rank) {
+    unsigned v;
+    asm volatile("ld.shared::cluster.u32 %0, [%1];\n" : "=r"(v) : "r"(peer_address(mine, rank)) : "memory");
+    return v;
+}
+
+__device__ __forceinline__ unsigned long long peer_u64(const void* mine, unsigned rank) {
+    unsigned long long v;
+    asm volatile("ld.shared::cluster.u64 %0, [%1];\n" : "=l"(v) : "r"(peer_address(mine, rank)) : "memory");
+    return v;
+}
+
+// The best of the blocks' results: every block has written its own into `mine` (the same place
+// in each block's shared memory) before a barrier of the cluster; the first 32 threads call this.
+__device__ __forceinline__ ArgMax cluster_best(const ArgMax* mine) {
+    const int lane = threadIdx.x & 31;
+    ArgMax v{-INFINITY, 0x7fffffff};
+    if (lane < kRowCluster) {
+        v.value = __uint_as_float(peer_u32(&mine->value, (unsigned)lane));
+        v.index = (int)peer_u32(&mine->index, (unsigned)lane);
     }
-    return prefix;
+#pragma unroll
+    for (int offset = kRowCluster / 2; offset > 0; offset >>= 1)
+        v = better(v, ArgMax{__shfl_xor_sync(0xffffffffu, v.value, offset), __shfl_xor_sync(0xffffffffu, v.index, offset)});
+    return v;
 }
 
 // Four uniform numbers in (0, 1] for tokens 4 c .. 4 c + 3 of the draw-th generated token of a
@@ -231,7 +163,7 @@ __device__ __forceinline__ bool plain_row(float temp, int k, float p, float mp, 
 // block over every kPlainCluster-th stretch of the row; the blocks' results meet in the shared
 // memory of the cluster's first block.  The draw costs a few hundred instructions per four tokens,
 // so a row is bound by the instruction rate of the SMs it runs on, not by memory.
-constexpr int kPlainCluster = 8;
+constexpr int kPlainCluster = kRowCluster;
 constexpr int kPlainThreads = 512;
 
 __global__ void __cluster_dims__(kPlainCluster, 1, 1) __launch_bounds__(kPlainThreads) sample_plain_kernel(
@@ -303,156 +235,451 @@ __global__ void __cluster_dims__(kPlainCluster, 1, 1) __launch_bounds__(kPlainTh
     }
 }
 
-// The other rows, one block per row.
-__global__ void __launch_bounds__(kSampleThreads, 1) sample_kernel(
+// ---- rows with a filter ------------------------------------------------------------------------
+constexpr int kFilterThreads = 1024;         // four threads to each of 256 bins when columns are summed
+constexpr int kCoarseBins = 256;
+constexpr float kCoarsePerUnit = 8.0f;
+constexpr int kListCapacity = 6144;             // candidates of one bin held in a block's shared memory
+constexpr int kLevels = 3;                      // a crowded bin is divided again, this often at most
+
+struct Tables {                                 // what a block found in its share of the row
+    unsigned long long mass[256];
+    unsigned count[256];
+    ArgMax arg;
+};
+
+// While a block walks over its share of the row, each lane of a warp adds to a column of its own:
+// tokens crowd into a few bins, and 32 lanes adding to one word would queue up; 32 columns are 32
+// banks, so the lanes of a warp never meet.  A mass (below 2^41) is added as its low 20 bits and
+// the rest: a lane meets fewer than 2^11 tokens of a row (the launcher sees to that), so neither
+// sum leaves 32 bits.
+struct Columns {
+    unsigned count[256][32];
+    unsigned low[256][32];
+    unsigned high[256][32];
+};
+constexpr int kMassLowBits = 20;
+constexpr int kFilterMaxVocab = (1 << 11) * 32 * kRowCluster;
+
+struct FilterShared {
+    Columns columns;
+    ArgMax arg_scratch[33];
+    Tables mine[2];                             // used in turn: the others may still read the last one
+    unsigned long long mass[256];               // the cluster's sums
+    unsigned count[256];
+    unsigned list[kListCapacity];               // this block's share of the keys of one bin
+    unsigned all[kListCapacity];                // those of all blocks
+    unsigned list_size, all_size;
+    int chosen;
+    unsigned long long before;
+    ArgMax best;
+};
+
+// A 64-bit sum in shared memory as two 32-bit atomics with the carry passed on by hand (32-bit
+// shared-memory atomics are the fast ones, and nearly all masses fit the low word).
+__device__ __forceinline__ void add_wide(unsigned long long* slot, unsigned long long m) {
+    unsigned* words = reinterpret_cast<unsigned*>(slot);
+    const unsigned lo = (unsigned)m, hi = (unsigned)(m >> 32);
+    const unsigned before = atomicAdd(words, lo);
+    const unsigned carry = before + lo < before ? 1u : 0u;
+    if (hi + carry) atomicAdd(words + 1, hi + carry);
+}
+
+template <bool WITH_MASS>
+__device__ __forceinline__ void column_add(Columns& columns, bool in, int bin, unsigned long long m) {
+    if (!in) return;
+    const int lane = threadIdx.x & 31;
+    atomicAdd(&columns.count[bin][lane], 1u);
+    if (WITH_MASS) {
+        atomicAdd(&columns.low[bin][lane], (unsigned)m & ((1u << kMassLowBits) - 1u));
+        const unsigned high = (unsigned)(m >> kMassLowBits);
+        if (high) atomicAdd(&columns.high[bin][lane], high);
+    }
+}
+
+// The first j of 0..255 at which v(0) + .. + v(j) reaches `need` (STRICT: exceeds it), with the sum
+// before it; j = 256 and the whole sum if none does.  The first warp works, every thread gets the result.
+template <bool STRICT, typename Get>
+__device__ void first_crossing(Get&& v, unsigned long long need, FilterShared& sh, int& j_out, unsigned long long& before_out) {
+    if (threadIdx.x < 32) {
+        const int lane = threadIdx.x;
+        unsigned long long mine[8], sum = 0;
+#pragma unroll
+        for (int i = 0; i < 8; ++i) {
+            mine[i] = v(8 * lane + i);
+            sum += mine[i];
+        }
+        unsigned long long upto = sum;
+#pragma unroll
+        for (int offset = 1; offset < 32; offset <<= 1) {
+            const unsigned long long other = __shfl_up_sync(0xffffffffu, upto, offset);
+            if (lane >= offset) upto += other;
+        }
+        const unsigned who = __ballot_sync(0xffffffffu, STRICT ? upto > need : upto >= need);
+        if (who == 0u) {
+            if (lane == 31) {
+                sh.chosen = 256;
+                sh.before = upto;
+            }
+        } else if (lane == __ffs(who) - 1) {
+            unsigned long long run = upto - sum;
+            int at = -1;
+#pragma unroll
+            for (int i = 0; i < 8; ++i) {
+                if (at < 0) {
+                    if (STRICT ? run + mine[i] > need : run + mine[i] >= need) at = i;
+                    else run += mine[i];
+                }
+            }
+            sh.chosen = 8 * lane + at;
+            sh.before = run;
+        }
+    }
+    __syncthreads();
+    j_out = sh.chosen;
+    before_out = sh.before;
+    __syncthreads();
+}
+
+__global__ void __cluster_dims__(kRowCluster, 1, 1) __launch_bounds__(kFilterThreads, 1) sample_filtered_kernel(
     const float* __restrict__ logits, int vocab, const float* __restrict__ temperature,
     const int* __restrict__ top_k, const float* __restrict__ top_p, const float* __restrict__ min_p,
     const unsigned long long* __restrict__ seeds, const unsigned long long* __restrict__ draw_index,
     int* __restrict__ tokens, float greedy_eps) {
-    __shared__ SampleShared sh;
+    extern __shared__ __align__(16) unsigned char filter_shared_raw[];
+    FilterShared& sh = *reinterpret_cast<FilterShared*>(filter_shared_raw);
 
-    const int row = blockIdx.x;
+    const int row = blockIdx.x / kRowCluster;
+    const unsigned rank = cluster_rank();
     const float* x = logits + (size_t)row * vocab;
-    const int tid = threadIdx.x;
+    const int tid = threadIdx.x, lane = tid & 31;
     const float temp = temperature[row];
+    const int k = top_k[row];
+    const float p = top_p[row], mp = min_p[row];
+    if (plain_row(temp, k, p, mp, greedy_eps)) return;             // the other kernel's; the whole cluster leaves
 
-    if (plain_row(temp, top_k[row], top_p[row], min_p[row], greedy_eps)) return;       // the other kernel's
+    const int chunks = (vocab + 3) >> 2;
+    const bool vec = (vocab & 3) == 0 && ((uintptr_t)x & 15) == 0;
+    // f(key of the scaled logit x / T, whether there is such a token) for this block's share of
+    // the row; the lanes of a warp call f together.
+    auto load_chunk = [&](int c, float (&xs)[4]) {      // tokens 4 c .. 4 c + 3, zeros past the row's end
+        if (vec) {
+            const float4 v = reinterpret_cast<const float4*>(x)[c];
+            xs[0] = v.x; xs[1] = v.y; xs[2] = v.z; xs[3] = v.w;
+        } else {
+#pragma unroll
+            for (int j = 0; j < 4; ++j) xs[j] = 4 * c + j < vocab ? x[4 * c + j] : 0.0f;
+        }
+    };
+    auto each_in_row = [&](auto&& f) {
+        for (int c0 = (int)rank * kFilterThreads + (tid & ~31); c0 < chunks; c0 += kRowCluster * kFilterThreads) {
+            const int c = c0 + lane;
+            float xs[4] = {0.0f, 0.0f, 0.0f, 0.0f};
+            if (c < chunks) load_chunk(c, xs);
+#pragma unroll
+            for (int j = 0; j < 4; ++j) f(ordered_key(xs[j] / temp), c < chunks && 4 * c + j < vocab);
+        }
+    };
+    auto each_in_all = [&](auto&& f) {              // the keys that the blocks have gathered, the same in every block
+        const int n = (int)sh.all_size;
+        for (int i = tid; i < n; i += kFilterThreads) f(sh.all[i], true);
+    };
 
-    // Scaled logits y = x / T; maximum and normaliser.
+    int turn = 0;                           // which of the two tables the next exchange uses
+    auto clear_columns = [&](bool with_mass) {
+        unsigned* words = &sh.columns.count[0][0];
+        const int n = (with_mass ? 3 : 1) * 256 * 32;               // count, low and high lie one behind the other
+        for (int i = tid; i < n; i += kFilterThreads) words[i] = 0u;
+        __syncthreads();
+    };
+    // The columns of a bin summed into this block's table: four threads to a bin, eight columns
+    // each, taken in an order that keeps the threads of a warp on different banks.
+    auto fold_columns = [&](bool with_mass) {
+        __syncthreads();
+        Tables& t = sh.mine[turn];
+        const int b = tid >> 2, q = tid & 3;
+        unsigned n = 0;
+        unsigned long long low = 0, high = 0;
+#pragma unroll
+        for (int i = 0; i < 8; ++i) {
+            const int column = (8 * q + i + b) & 31;
+            n += sh.columns.count[b][column];
+            if (with_mass) {
+                low += sh.columns.low[b][column];
+                high += sh.columns.high[b][column];
+            }
+        }
+        unsigned long long m = low + (high << kMassLowBits);
+#pragma unroll
+        for (int offset = 1; offset < 4; offset <<= 1) {
+            n += __shfl_xor_sync(0xffffffffu, n, offset);
+            m += __shfl_xor_sync(0xffffffffu, m, offset);
+        }
+        if (q == 0) {
+            t.count[b] = n;
+            t.mass[b] = m;
+        }
+    };
+    auto clear_sums = [&]() {
+        for (int b = tid; b < 256; b += kFilterThreads) {
+            sh.mass[b] = 0ull;
+            sh.count[b] = 0u;
+        }
+        __syncthreads();
+    };
+    // After the blocks have filled their tables: the sums over the cluster into sh.mass and
+    // sh.count.  A block writes into a table again two exchanges later, when every block has
+    // passed the barrier in between and so has read it.
+    auto sum_over_cluster = [&]() {
+        cluster_sync();
+        const Tables& t = sh.mine[turn];
+        for (int b = tid; b < 256; b += kFilterThreads) {
+            unsigned long long m = 0;
+            unsigned n = 0;
+#pragma unroll
+            for (unsigned r = 0; r < (unsigned)kRowCluster; ++r) {
+                m += peer_u64(&t.mass[b], r);
+                n += peer_u32(&t.count[b], r);
+            }
+            sh.mass[b] = m;
+            sh.count[b] = n;
+        }
+        __syncthreads();
+        turn ^= 1;
+    };
+    auto best_of_cluster = [&](ArgMax mine) {
+        mine = block_argmax(mine, sh.arg_scratch);
+        if (tid == 0) sh.mine[turn].arg = mine;
+        cluster_sync();
+        if (tid < 32) {
+            const ArgMax all = cluster_best(&sh.mine[turn].arg);
+            if (tid == 0) sh.best = all;
+        }
+        __syncthreads();
+        turn ^= 1;
+        return sh.best;
+    };
+
+    // Scaled logits y = x / T: the maximum.
     ArgMax top{-INFINITY, 0x7fffffff};
-    for_each_logit(x, vocab, [&](float v, int i) { top = better(top, ArgMax{v / temp, i}); });
-    top = block_argmax(top, sh.arg_scratch);
+    for (int c = (int)rank * kFilterThreads + tid; c < chunks; c += kRowCluster * kFilterThreads) {
+        float xs[4];
+        load_chunk(c, xs);
+#pragma unroll
+        for (int j = 0; j < 4; ++j)
+            if (4 * c + j < vocab) top = better(top, ArgMax{xs[j] / temp, 4 * c + j});
+    }
+    top = best_of_cluster(top);
     const float y_max = top.value;
 
     unsigned cut = 0;                       // keep tokens whose key >= cut
-    const float mp = min_p[row];
     if (mp > 0.0f) cut = ordered_key(y_max + logf(mp));
 
-    auto each_in_row = [&](auto&& f) { for_each_logit(x, vocab, [&](float v, int) { f(ordered_key(v / temp)); }); };
-    auto each_in_list = [&](auto&& f) {
-        const int n = (int)sh.list_size;
-        for (int i = tid; i < n; i += blockDim.x) f(sh.list[i]);
+    // A first, coarse look at the row sorts the kept tokens by how far they lie below the maximum:
+    // eight bins per unit, the last bin for everything 31.875 and more below.  Bin numbers fall as
+    // the logit rises, so bins are ranges of the key order.  A bin with more tokens than the list
+    // holds is divided again into 256 (level 2, and those once more, level 3): `in1`, `in2` name
+    // the bins of levels 1 and 2 that are looked into.  The differences are exact, so that a
+    // token falls into the same bins at every look.
+    auto locate = [&](float y, int level, int in1, int in2, int& bin) -> bool {
+        const float d = (y_max - y) * kCoarsePerUnit;
+        const int b1 = d >= (float)(kCoarseBins - 1) ? kCoarseBins - 1 : (int)d;
+        if (level == 1) {
+            bin = b1;
+            return true;
+        }
+        if (b1 != in1) return false;
+        const float f2 = (d - (float)in1) * 256.0f;
+        const int b2 = min(max((int)f2, 0), 255);
+        if (level == 2) {
+            bin = b2;
+            return true;
+        }
+        if (b2 != in2) return false;
+        bin = min(max((int)((f2 - (float)in2) * 256.0f), 0), 255);
+        return true;
     };
-    // Counts (and, for top-p, masses) of the kept tokens per coarse bin.
-    // (A mass is added as two 32-bit words with the carry passed on by hand: nearly all
-    // masses fit the low word, and 32-bit shared-memory atomics are the fast ones.)
-    auto add_mass = [&](int b, unsigned long long m) {
-        const unsigned lo = (unsigned)m, hi = (unsigned)(m >> 32);
-        const unsigned before = atomicAdd(&sh.coarse_mass_lo[b], lo);
-        const unsigned carry = before + lo < before ? 1u : 0u;
-        if (hi + carry) atomicAdd(&sh.coarse_mass_hi[b], hi + carry);
-    };
-    auto mass_of_bin = [&](int b) { return ((unsigned long long)sh.coarse_mass_hi[b] << 32) + sh.coarse_mass_lo[b]; };
-    auto look = [&](bool with_mass) {
-        for (int b = tid; b < kCoarseBins; b += blockDim.x) sh.coarse_count[b] = sh.coarse_mass_lo[b] = sh.coarse_mass_hi[b] = 0u;
-        __syncthreads();
-        unsigned far_count = 0;
-        unsigned long long far_mass = 0;
-        each_in_row([&](unsigned key) {
-            if (key < cut) return;
+    auto look = [&](int level, int in1, int in2, bool with_mass) {
+        clear_columns(with_mass);
+        each_in_row([&](unsigned key, bool there) {
             const float y = key_value(key);
-            const int b = coarse_bin(y, y_max);
-            if (b == kCoarseBins - 1) {
-                ++far_count;
-                if (with_mass) far_mass += fixed_mass(y, y_max);
-            } else {
-                atomicAdd(&sh.coarse_count[b], 1u);
-                if (with_mass) add_mass(b, fixed_mass(y, y_max));
-            }
+            int bin = 0;
+            const bool in = there && key >= cut && locate(y, level, in1, in2, bin);
+            if (with_mass) column_add<true>(sh.columns, in, bin, in ? fixed_mass(y, y_max) : 0ull);
+            else column_add<false>(sh.columns, in, bin, 0ull);
         });
-#pragma unroll
-        for (int offset = 16; offset > 0; offset >>= 1) {
-            far_count += __shfl_xor_sync(0xffffffffu, far_count, offset);
-            far_mass += __shfl_xor_sync(0xffffffffu, far_mass, offset);
-        }
-        if ((tid & 31) == 0 && far_count) {
-            atomicAdd(&sh.coarse_count[kCoarseBins - 1], far_count);
-            add_mass(kCoarseBins - 1, far_mass);
-        }
-        __syncthreads();
+        fold_columns(with_mass);
+        sum_over_cluster();
     };
-    // The kept tokens of coarse bin `bin` into the list (a warp appends together).
-    auto gather = [&](int bin) {
+    // The kept tokens of bin `bin`: this block's into its list (a warp appends together), then the
+    // lists of all blocks into `all`.  A block's list is written again after a later look at the row,
+    // whose barrier every block reaches after it has copied.
+    auto gather = [&](int level, int in1, int in2, int bin) {
         if (tid == 0) sh.list_size = 0u;
         __syncthreads();
-        each_in_row([&](unsigned key) {
-            const bool mine = key >= cut && coarse_bin(key_value(key), y_max) == bin;
-            const unsigned active = __activemask();
-            const unsigned who = __ballot_sync(active, mine);
+        each_in_row([&](unsigned key, bool there) {
+            int b = 0;
+            const bool mine = there && key >= cut && locate(key_value(key), level, in1, in2, b) && b == bin;
+            const unsigned who = __ballot_sync(0xffffffffu, mine);
             if (who == 0u) return;
-            const int lane = tid & 31, leader = __ffs(who) - 1;
+            const int leader = __ffs(who) - 1;
             unsigned base = 0;
             if (lane == leader) base = atomicAdd(&sh.list_size, (unsigned)__popc(who));
-            base = __shfl_sync(active, base, leader);
+            base = __shfl_sync(0xffffffffu, base, leader);
             if (mine) {
                 const unsigned at = base + __popc(who & ((1u << lane) - 1u));
                 if (at < (unsigned)kListCapacity) sh.list[at] = key;
             }
         });
+        // every block copies the lists of all: what follows runs in each block alone, alike
+        cluster_sync();
+        unsigned start = 0;
+        for (unsigned r = 0; r < (unsigned)kRowCluster; ++r) {
+            const unsigned n = peer_u32(&sh.list_size, r);
+            for (unsigned i = tid; i < n && start + i < (unsigned)kListCapacity; i += kFilterThreads)
+                sh.all[start + i] = peer_u32(&sh.list[i], r);
+            start += n;
+        }
+        if (tid == 0) sh.all_size = min(start, (unsigned)kListCapacity);
         __syncthreads();
+    };
+    // The kth largest of the kept keys: of the gathered ones (in each block alone), or OF_ROW, of
+    // the row (the blocks share it).  Fewer than that many: the smallest possible prefix, which
+    // cuts nothing.  Radix selection, a byte a pass.
+    auto select_kth_largest = [&](bool of_row, unsigned long long kth) -> unsigned {
+        unsigned prefix = 0;
+        for (int pass = 0; pass < 4; ++pass) {
+            const int shift = 24 - 8 * pass;
+            const unsigned mask = pass == 0 ? 0u : (0xffffffffu << (shift + 8));
+            if (of_row) {
+                clear_columns(false);
+                each_in_row([&](unsigned key, bool there) {
+                    column_add<false>(sh.columns, there && key >= cut && (key & mask) == prefix, (int)((key >> shift) & 255u), 0ull);
+                });
+                fold_columns(false);
+                sum_over_cluster();
+            } else {
+                clear_sums();
+                each_in_all([&](unsigned key, bool) {
+                    if (key >= cut && (key & mask) == prefix) atomicAdd(&sh.count[(key >> shift) & 255u], 1u);
+                });
+                __syncthreads();
+            }
+            int j;
+            unsigned long long above;
+            first_crossing<false>([&](int i) { return (unsigned long long)sh.count[255 - i]; }, kth, sh, j, above);
+            if (j == 256) {                 // not that many: the lowest byte, everything above it counted
+                j = 255;
+                above -= sh.count[0];
+            }
+            prefix |= (unsigned)(255 - j) << shift;
+            kth -= above;
+        }
+        return prefix;
+    };
+    // The smallest key at which the mass of the kept keys (the gathered ones, or OF_ROW the row's),
+    // summed from the smallest key up and starting from `below`, first exceeds `target`.
+    auto select_mass_from_below = [&](bool of_row, unsigned long long target, unsigned long long below) -> unsigned {
+        unsigned prefix = 0;
+        for (int pass = 0; pass < 4; ++pass) {
+            const int shift = 24 - 8 * pass;
+            const unsigned mask = pass == 0 ? 0u : (0xffffffffu << (shift + 8));
+            if (of_row) {
+                clear_columns(true);
+                each_in_row([&](unsigned key, bool there) {
+                    const bool in = there && key >= cut && (key & mask) == prefix;
+                    column_add<true>(sh.columns, in, (int)((key >> shift) & 255u), in ? fixed_mass(key_value(key), y_max) : 0ull);
+                });
+                fold_columns(true);
+                sum_over_cluster();
+            } else {
+                clear_sums();
+                each_in_all([&](unsigned key, bool) {
+                    if (key >= cut && (key & mask) == prefix) add_wide(&sh.mass[(key >> shift) & 255u], fixed_mass(key_value(key), y_max));
+                });
+                __syncthreads();
+            }
+            int j;
+            unsigned long long before;
+            first_crossing<true>([&](int i) { return sh.mass[i]; }, target - below, sh, j, before);
+            if (j == 256) {                 // the highest byte holds the first kept token at the latest
+                j = 255;
+                before -= sh.mass[255];
+            }
+            prefix |= (unsigned)j << shift;
+            below += before;
+        }
+        return prefix;
     };
 
     // ---- top-k: the k-th largest key among the kept ones -------------------
-    const int k = top_k[row];
-    const float p = top_p[row];
-    bool looked = false;                    // the coarse bins hold counts and masses under the current cut
     if (k > 0 && k < vocab) {
-        look(p < 1.0f);
-        looked = true;
-        if (tid == 0) {
-            unsigned long long above = 0;
-            int b = 0;
-            for (; b < kCoarseBins; ++b) {
-                if (above + sh.coarse_count[b] >= (unsigned long long)k) break;
-                above += sh.coarse_count[b];
+        unsigned long long need = (unsigned long long)k;        // how many from the top of the bins looked into
+        int in1 = 0, in2 = 0;
+        unsigned kth = 0;
+        bool found = false, fewer = false;
+        for (int level = 1; level <= kLevels && !found; ++level) {
+            look(level, in1, in2, false);
+            int bin;
+            unsigned long long above;
+            first_crossing<false>([&](int i) { return (unsigned long long)sh.count[i]; }, need, sh, bin, above);
+            if (bin == 256) {
+                if (level == 1) {           // fewer than k tokens are kept
+                    fewer = true;
+                    break;
+                }
+                bin = 255;
+                above -= sh.count[255];
             }
-            sh.chosen_bin = b;                  // kCoarseBins: fewer than k tokens are kept
-            sh.chosen_before = above;
-        }
-        __syncthreads();
-        const int bin = sh.chosen_bin;
-        const unsigned long long above = sh.chosen_before;
-        __syncthreads();
-        if (bin < kCoarseBins) {
-            unsigned kth;
-            if (bin < kCoarseBins - 1 && sh.coarse_count[bin] <= (unsigned)kListCapacity) {
-                gather(bin);
-                kth = select_kth_largest(each_in_list, cut, k - (int)above, sh);
+            if (level == 1 && bin == kCoarseBins - 1) break;    // the far bin is not divided
+            need -= above;
+            if (sh.count[bin] <= (unsigned)kListCapacity) {
+                gather(level, in1, in2, bin);
+                kth = select_kth_largest(false, need);
+                found = true;
+            } else if (level == 1) {
+                in1 = bin;
             } else {
-                kth = select_kth_largest(each_in_row, cut, k, sh);         // the far bin, or a crowd: the whole row
+                in2 = bin;
             }
-            if (kth > cut) { cut = kth; looked = false; }
         }
+        if (!found && !fewer) kth = select_kth_largest(true, (unsigned long long)k);     // the far bin, or a crowd of near ties
+        if (kth > cut) cut = kth;
     }
 
     // ---- top-p: drop the smallest tokens while their mass stays <= 1 - p ----
     if (p < 1.0f) {
-        if (!looked) look(true);
-        if (tid == 0) {
-            unsigned long long total = 0;
-            for (int b = 0; b < kCoarseBins; ++b) total += mass_of_bin(b);
-            const unsigned long long target = (unsigned long long)((double)total * (double)(1.0f - p));
-            unsigned long long below = 0;
-            int b = kCoarseBins - 1;
-            for (; b > 0; --b) {
-                if (below + mass_of_bin(b) > target) break;
-                below += mass_of_bin(b);
+        unsigned long long target = 0, below = 0;
+        int in1 = 0, in2 = 0;
+        unsigned edge = 0;
+        bool found = false;
+        for (int level = 1; level <= kLevels && !found; ++level) {
+            look(level, in1, in2, true);
+            int j;
+            unsigned long long before;
+            if (level == 1) {
+                first_crossing<true>([&](int i) { return sh.mass[i]; }, ~0ull, sh, j, before);   // none crosses: the whole mass
+                target = (unsigned long long)((double)before * (double)(1.0f - p));
             }
-            sh.chosen_bin = b;
-            sh.chosen_before = below;
-            sh.carry = target;
+            first_crossing<true>([&](int i) { return sh.mass[255 - i]; }, target - below, sh, j, before);   // from the smallest up
+            if (j == 256) {                 // the bin of the largest tokens holds the first kept one at the latest
+                j = 255;
+                before -= sh.mass[0];
+            }
+            const int bin = 255 - j;
+            if (level == 1 && bin == kCoarseBins - 1) break;    // the far bin is not divided
+            below += before;
+            if (sh.count[bin] <= (unsigned)kListCapacity) {
+                gather(level, in1, in2, bin);
+                edge = select_mass_from_below(false, target, below);
+                found = true;
+            } else if (level == 1) {
+                in1 = bin;
+            } else {
+                in2 = bin;
+            }
         }
-        __syncthreads();
-        const int bin = sh.chosen_bin;
-        const unsigned long long below = sh.chosen_before, target = sh.carry;
-        __syncthreads();
-        unsigned edge;
-        if (bin < kCoarseBins - 1 && sh.coarse_count[bin] <= (unsigned)kListCapacity) {
-            gather(bin);
-            edge = select_mass_from_below(each_in_list, cut, target, below, y_max, sh);
-        } else {
-            edge = select_mass_from_below(each_in_row, cut, target, 0ull, y_max, sh);
-        }
+        if (!found) edge = select_mass_from_below(true, target, 0ull);
         if (edge > cut) cut = edge;
         const unsigned top_key = ordered_key(y_max);
         if (cut > top_key) cut = top_key;          // the largest token always stays
@@ -461,17 +688,9 @@ __global__ void __launch_bounds__(kSampleThreads, 1) sample_kernel(
     // ---- the draw ------------------------------------------------------------
     const unsigned long long seed = seeds[row], draw = draw_index[row];
     ArgMax best{-INFINITY, 0x7fffffff};
-    const int chunks = (vocab + 3) >> 2;
-    const bool vec = (vocab & 3) == 0 && ((uintptr_t)x & 15) == 0;
-    for (int c = tid; c < chunks; c += blockDim.x) {
+    for (int c = (int)rank * kFilterThreads + tid; c < chunks; c += kRowCluster * kFilterThreads) {
         float xs[4];
-        if (vec) {
-            const float4 v = reinterpret_cast<const float4*>(x)[c];
-            xs[0] = v.x; xs[1] = v.y; xs[2] = v.z; xs[3] = v.w;
-        } else {
-#pragma unroll
-            for (int j = 0; j < 4; ++j) xs[j] = 4 * c + j < vocab ? x[4 * c + j] : -INFINITY;
-        }
+        load_chunk(c, xs);
         bool any = false;
 #pragma unroll
         for (int j = 0; j < 4; ++j) any = any || (4 * c + j < vocab && ordered_key(xs[j] / temp) >= cut);
@@ -488,8 +707,9 @@ __global__ void __launch_bounds__(kSampleThreads, 1) sample_kernel(
             best = better(best, ArgMax{y - logf(e), i});
         }
     }
-    best = block_argmax(best, sh.arg_scratch);
-    if (tid == 0) tokens[row] = best.index == 0x7fffffff ? top.index : best.index;
+    best = best_of_cluster(best);
+    if (rank == 0 && tid == 0) tokens[row] = best.index == 0x7fffffff ? top.index : best.index;
+    cluster_sync();                                // no block leaves while another may read its tables
 }
 
 // Penalties on the distinct tokens a request has seen, listed per row in CSR form:
@@ -543,9 +763,14 @@ B200_EXPORT int b200_sample(const float* logits, int rows, int vocab, const floa
         const int status = check_launch("sample (plain rows)");
         if (status) return status;
     }
-    if (kinds & 2)
-        sample_kernel<<<rows, kSampleThreads, 0, stream>>>(logits, vocab, temperature, top_k, top_p, min_p,
-                                                           seeds, draw_index, tokens, greedy_eps);
+    if (kinds & 2) {
+        if (vocab >= kFilterMaxVocab) return fail("sample", "filters (top-k, top-p, min-p) take a vocabulary below 524288");
+        static const cudaError_t attribute = cudaFuncSetAttribute(sample_filtered_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                                                  (int)sizeof(FilterShared));
+        if (attribute != cudaSuccess) return fail("sample", cudaGetErrorString(attribute));
+        sample_filtered_kernel<<<rows * kRowCluster, kFilterThreads, sizeof(FilterShared), stream>>>(logits, vocab, temperature, top_k, top_p, min_p,
+                                                                                  seeds, draw_index, tokens, greedy_eps);
+    }
     return check_launch("sample");
 }
 
