@@ -123,6 +123,14 @@ def test_rows_with_and_without_filters_draw_alike(vocab):
         run(none, 0)
 
 
+def test_filters_refuse_a_vocabulary_beyond_their_counters():
+    import vllm_from_scratch_b200.kernels as k
+    row = torch.zeros(1 << 19)
+    with pytest.raises(k.KernelError, match="vocabulary"):
+        draw(row, 2, temperature=1.0, top_k=5)
+    assert draw(row, 2, temperature=1.0).numel() == 2          # rows without a filter take any size
+
+
 def _large_rows():
     g = torch.Generator().manual_seed(21)
     vocab = 151936
