@@ -128,7 +128,14 @@ def test_filters_refuse_a_vocabulary_beyond_their_counters():
     row = torch.zeros(1 << 19)
     with pytest.raises(k.KernelError, match="vocabulary"):
         draw(row, 2, temperature=1.0, top_k=5)
-    assert draw(row, 2, temperature=1.0).numel() == 2          # rows without a filter take any size
+    # rows without a filter take any size, when the caller says that there are no others
+    logits = row.cuda().unsqueeze(0).contiguous()
+    logits[0, 77] = 30.0
+    one = lambda v, dt: torch.full((1,), v, dtype=dt, device="cuda")
+    out = torch.empty(1, dtype=torch.int32, device="cuda")
+    k.sample(logits, one(1.0, torch.float32), one(0, torch.int32), one(1.0, torch.float32), one(0.0, torch.float32),
+             one(5, torch.int64), one(0, torch.int64), out, 1e-5, 1)
+    assert int(out[0]) == 77
 
 
 def _large_rows():
