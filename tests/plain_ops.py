@@ -146,8 +146,9 @@ def patch(monkeypatch) -> None:
         monkeypatch.setattr(kernels, name, globals()[name])
 
 
-def sample(logits, temperature, top_k, top_p, min_p, seeds, draw_index, tokens, greedy_eps):
+def sample(logits, temperature, top_k, top_p, min_p, seeds, draw_index, tokens, greedy_eps, kinds=3):
     """Greedy rows only: enough to drive the engine on the CPU."""
+    assert kinds & 1, "greedy rows are rows without a filter"
     if bool((temperature >= greedy_eps).any()):
         raise NotImplementedError("the plain stand-in samples greedily only")
     tokens.copy_(logits.argmax(dim=-1).to(tokens.dtype))
