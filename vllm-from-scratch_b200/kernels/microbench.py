@@ -6,6 +6,7 @@
     python -m vllm_from_scratch_b200.kernels.microbench gemm --m 8 --n 12288 --k 2048
     python -m vllm_from_scratch_b200.kernels.microbench norm | silu_mul | rope --tokens 2048
     python -m vllm_from_scratch_b200.kernels.microbench layer_products --m 8 [--no-split-norm]
+    python -m vllm_from_scratch_b200.kernels.microbench sample --batch 8 --top-k 50 --top-p 0.9 --repeat 10
     python -m vllm_from_scratch_b200.kernels.microbench step --layers 4 --tokens 2048          (a prompt step)
     python -m vllm_from_scratch_b200.kernels.microbench step --layers 4 --batch 8 --context 2048 --tokens 1
 
@@ -138,7 +139,12 @@ def _step(args) -> int:
 def main(argv=None) -> int:
     parser = argparse.ArgumentParser(description=__doc__, formatter_class=argparse.RawTextHelpFormatter)
     parser.add_argument("op", choices=("decode_attention", "prefill_attention", "gemm", "norm", "silu_mul", "rope",
-                                       "layer_products", "step"))
+                                       "layer_products", "sample", "step"))
+    parser.add_argument("--temperature", type=float, default=0.8, help="sample: 0 for greedy rows")
+    parser.add_argument("--top-k", type=int, default=0, help="sample")
+    parser.add_argument("--top-p", type=float, default=1.0, help="sample")
+    parser.add_argument("--min-p", type=float, default=0.0, help="sample")
+    parser.add_argument("--spread", type=float, default=1.0, help="sample: standard deviation of the random logits")
     parser.add_argument("--no-split-norm", action="store_true",
                         help="layer_products: the two norms as kernels of their own")
     parser.add_argument("--layers", type=int, default=4, help="step: layers of the model")
@@ -279,6 +285,22 @@ def main(argv=None) -> int:
         ms = _time(sweep, args.warmup, args.iters, False) / copies
         record.update(m=m, hidden=hidden, inter=inter, attended=attended, qkv=qkv_width,
                       split_norm=not args.no_split_norm, gb_s=round(layer_bytes / ms / 1e6, 1))
+    elif args.op == "sample":
+        rows = args.batch
+        logits = torch.randn(rows, args.vocab, device="cuda") * args.spread
+        full = lambda value, kind: torch.full((rows,), value, dtype=kind, device="cuda")
+        temperature, top_k = full(args.temperature, torch.float32), full(args.top_k, torch.int32)
+        top_p, min_p = full(args.top_p, torch.float32), full(args.min_p, torch.float32)
+        seeds, draws = torch.arange(rows, dtype=torch.int64, device="cuda"), full(3, torch.int64)
+        picked = torch.empty(rows, dtype=torch.int32, device="cuda")
+        filtered = args.temperature >= 1e-5 and (args.top_k > 0 or args.top_p < 1.0 or args.min_p > 0.0)
+
+        def launches():
+            for _ in range(args.repeat):
+                kernels.sample(logits, temperature, top_k, top_p, min_p, seeds, draws, picked, 1e-5, 2 if filtered else 1)
+        ms = _time(launches, args.warmup, args.iters, not args.keep_l2) / args.repeat
+        record.update(rows=rows, vocab=args.vocab, temperature=args.temperature, top_k=args.top_k, top_p=args.top_p,
+                      min_p=args.min_p, repeat=args.repeat, gb_s=round(rows * args.vocab * 4 / ms / 1e6, 1))
     elif args.op == "norm":
         x = torch.randn(args.tokens, args.hidden, device="cuda").to(dtype)
         residual = torch.randn(args.tokens, args.hidden, device="cuda")
