@@ -20,13 +20,17 @@ pytestmark = pytest.mark.gpu
 
 ROOT = Path(__file__).resolve().parent.parent
 CONFIGS = {"A": (tiny_configs.TINY_A, 16), "B": (tiny_configs.TINY_B, 8), "C": (tiny_configs.TINY_C, 16),
-           "D": (tiny_configs.TINY_D, 16), "E": (tiny_configs.TINY_E, 16)}
+           "D": (tiny_configs.TINY_D, 16), "E": (tiny_configs.TINY_E, 16), "F": (tiny_configs.TINY_F, 16),
+           "G": (tiny_configs.TINY_G, 32), "H": (tiny_configs.TINY_H, 8)}
 LENGTHS = {
     "A": {"a": 70, "b": 45, "c": 100, "d": 37, "e": 64, "f": 3, "g": 128},
     "B": {"a": 70, "b": 145, "c": 100, "d": 37, "e": 64, "f": 2, "g": 200},
     "C": {"a": 70, "b": 145, "c": 100, "d": 37, "e": 64, "f": 5, "g": 300},
     "D": {"a": 70, "b": 145, "c": 100, "d": 37, "e": 64, "f": 2, "g": 410},
     "E": {"a": 70, "b": 145, "c": 100, "d": 37, "e": 64, "f": 2, "g": 330},
+    "F": {"a": 70, "b": 145, "c": 100, "d": 37, "e": 64, "f": 2, "g": 230},
+    "G": {"a": 70, "b": 145, "c": 100, "d": 37, "e": 64, "f": 3, "g": 310},
+    "H": {"a": 70, "b": 145, "c": 100, "d": 37, "e": 64, "f": 2, "g": 280},
 }
 # The bounds (tiny_configs.F32_ATOL, BF16_REL) are twice the worst difference seen.
 def tolerance(dtype: str, reference: torch.Tensor, name: str) -> float:
