@@ -91,14 +91,14 @@ def test_same_key_same_token_and_large_vocabulary():
     assert bool(keep[a].all())
 
 
-@pytest.mark.parametrize("vocab", [503, 4096, 151936])
-def test_rows_with_and_without_filters_draw_alike(vocab):
+@pytest.mark.parametrize("vocab,n", [(503, 12), (4096, 12), (151936, 12), (151936, 24), (50257, 70)])
+def test_rows_with_and_without_filters_draw_alike(vocab, n):
     """Rows without a filter and rows with one run in different kernels.  A filter that keeps
     every token (top-k of the whole vocabulary) must give the token of the row without it, in
-    one call with rows of both kinds and in calls that launch one kernel only."""
+    one call with rows of both kinds and in calls that launch one kernel only.  (The number of
+    rows decides how many blocks share a row with a filter: eight, four or two.)"""
     import vllm_from_scratch_b200.kernels as k
     g = torch.Generator().manual_seed(vocab)
-    n = 12
     logits = (torch.randn(n, vocab, generator=g) * 2).cuda()
     logits[5] = float("-inf")                            # nothing to draw from: the first token
     seeds = torch.arange(100, 100 + n, dtype=torch.int64, device="cuda")
@@ -125,7 +125,7 @@ def test_rows_with_and_without_filters_draw_alike(vocab):
 
 def test_filters_refuse_a_vocabulary_beyond_their_counters():
     import vllm_from_scratch_b200.kernels as k
-    row = torch.zeros(1 << 19)
+    row = torch.zeros(1 << 20)
     with pytest.raises(k.KernelError, match="vocabulary"):
         draw(row, 2, temperature=1.0, top_k=5)
     # rows without a filter take any size, when the caller says that there are no others

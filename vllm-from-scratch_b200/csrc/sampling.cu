@@ -78,11 +78,17 @@ __device__ __forceinline__ unsigned long long fixed_mass(float y, float y_max) {
 }
 
 // ---- a cluster of blocks to a row ------------------------------------------------------------
-// The blocks of a cluster share a row: each walks over every kRowCluster-th stretch of it, adds
+// The blocks of a cluster share a row: each walks over every n-th stretch of it (n blocks), adds
 // what it finds to tables in its own shared memory, and after a barrier of the cluster every block
 // sums the tables of all (through distributed shared memory) and takes the same decision from the
 // same numbers, so that all blocks follow one path and meet at the same barriers.
-constexpr int kRowCluster = 8;
+constexpr int kRowCluster = 8;             // blocks to a row at most (the portable size of a cluster)
+
+__device__ __forceinline__ unsigned cluster_blocks() {
+    unsigned n;
+    asm volatile("mov.u32 %0, %%cluster_nctarank;\n" : "=r"(n));
+    return n;
+}
 
 __device__ __forceinline__ unsigned cluster_rank() {
     unsigned rank;
@@ -115,10 +121,10 @@ __device__ __forceinline__ unsigned long long peer_u64(const void* mine, unsigne
 
 // The best of the blocks' results: every block has written its own into `mine` (the same place
 // in each block's shared memory) before a barrier of the cluster; the first 32 threads call this.
-__device__ __forceinline__ ArgMax cluster_best(const ArgMax* mine) {
+__device__ __forceinline__ ArgMax cluster_best(const ArgMax* mine, unsigned blocks) {
     const int lane = threadIdx.x & 31;
     ArgMax v{-INFINITY, 0x7fffffff};
-    if (lane < kRowCluster) {
+    if (lane < (int)blocks) {
         v.value = __uint_as_float(peer_u32(&mine->value, (unsigned)lane));
         v.index = (int)peer_u32(&mine->index, (unsigned)lane);
     }
@@ -174,8 +180,7 @@ __global__ void __cluster_dims__(kPlainCluster, 1, 1) __launch_bounds__(kPlainTh
     __shared__ ArgMax scratch[33];
     __shared__ ArgMax shares[2 * kPlainCluster];        // of the cluster's first block: every block's best and top
     const int row = blockIdx.x / kPlainCluster, tid = threadIdx.x;
-    unsigned rank;
-    asm volatile("mov.u32 %0, %%cluster_ctarank;\n" : "=r"(rank));
+    const unsigned rank = cluster_rank();
     const float temp = temperature[row];
     if (!plain_row(temp, top_k[row], top_p[row], min_p[row], greedy_eps)) return;      // the whole cluster leaves
     const bool greedy = temp < greedy_eps;
@@ -214,15 +219,13 @@ __global__ void __cluster_dims__(kPlainCluster, 1, 1) __launch_bounds__(kPlainTh
     best = block_argmax(best, scratch);
     if (!greedy) top = block_argmax(top, scratch);
     if (tid == 0) {
-        unsigned mine = (unsigned)__cvta_generic_to_shared(shares + rank), first;
-        asm volatile("mapa.shared::cluster.u32 %0, %1, 0;\n" : "=r"(first) : "r"(mine));
+        const unsigned first = peer_address(shares + rank, 0u);        // the same place in the first block
         asm volatile("st.shared::cluster.b32 [%0], %1;\n" ::"r"(first), "r"(__float_as_uint(best.value)) : "memory");
         asm volatile("st.shared::cluster.b32 [%0], %1;\n" ::"r"(first + 4u), "r"((unsigned)best.index) : "memory");
         asm volatile("st.shared::cluster.b32 [%0], %1;\n" ::"r"(first + 8u * kPlainCluster), "r"(__float_as_uint(top.value)) : "memory");
         asm volatile("st.shared::cluster.b32 [%0], %1;\n" ::"r"(first + 8u * kPlainCluster + 4u), "r"((unsigned)top.index) : "memory");
     }
-    asm volatile("barrier.cluster.arrive.release.aligned;\n" ::: "memory");
-    asm volatile("barrier.cluster.wait.acquire.aligned;\n" ::: "memory");
+    cluster_sync();
     if (rank == 0 && tid < 32) {
         ArgMax b = tid < kPlainCluster ? shares[tid] : ArgMax{-INFINITY, 0x7fffffff};
         ArgMax t = tid < kPlainCluster ? shares[kPlainCluster + tid] : ArgMax{-INFINITY, 0x7fffffff};
@@ -251,15 +254,15 @@ struct Tables {                                 // what a block found in its sha
 // While a block walks over its share of the row, each lane of a warp adds to a column of its own:
 // tokens crowd into a few bins, and 32 lanes adding to one word would queue up; 32 columns are 32
 // banks, so the lanes of a warp never meet.  A mass (below 2^41) is added as its low 20 bits and
-// the rest: a lane meets fewer than 2^11 tokens of a row (the launcher sees to that), so neither
-// sum leaves 32 bits.
+// the rest (2^20 at most): a column takes fewer than 2^12 tokens of a row (the launcher sees to
+// that with the number of blocks it gives a row), so neither sum leaves 32 bits.
 struct Columns {
     unsigned count[256][32];
     unsigned low[256][32];
     unsigned high[256][32];
 };
 constexpr int kMassLowBits = 20;
-constexpr int kFilterMaxVocab = (1 << 11) * 32 * kRowCluster;
+constexpr int kColumnMaxTokens = (1 << (32 - kMassLowBits)) - 1;       // tokens that a lane may add to a column
 
 struct FilterShared {
     Columns columns;
@@ -341,7 +344,9 @@ __device__ void first_crossing(Get&& v, unsigned long long need, FilterShared& s
     __syncthreads();
 }
 
-__global__ void __cluster_dims__(kRowCluster, 1, 1) __launch_bounds__(kFilterThreads, 1) sample_filtered_kernel(
+// Launched with clusters of 2, 4 or 8 blocks (a launch attribute): many rows get fewer blocks each, so
+// that all rows run at once.
+__global__ void __launch_bounds__(kFilterThreads, 1) sample_filtered_kernel(
     const float* __restrict__ logits, int vocab, const float* __restrict__ temperature,
     const int* __restrict__ top_k, const float* __restrict__ top_p, const float* __restrict__ min_p,
     const unsigned long long* __restrict__ seeds, const unsigned long long* __restrict__ draw_index,
@@ -349,10 +354,11 @@ __global__ void __cluster_dims__(kRowCluster, 1, 1) __launch_bounds__(kFilterThr
     extern __shared__ __align__(16) unsigned char filter_shared_raw[];
     FilterShared& sh = *reinterpret_cast<FilterShared*>(filter_shared_raw);
 
-    const int row = blockIdx.x / kRowCluster;
-    const unsigned rank = cluster_rank();
+    const unsigned rank = cluster_rank(), blocks = cluster_blocks();
+    const int row = blockIdx.x / blocks;
     const float* x = logits + (size_t)row * vocab;
     const int tid = threadIdx.x, lane = tid & 31;
+    const int stride = (int)blocks * kFilterThreads;        // chunks of four tokens from one of this thread's to its next
     const float temp = temperature[row];
     const int k = top_k[row];
     const float p = top_p[row], mp = min_p[row];
@@ -372,7 +378,7 @@ __global__ void __cluster_dims__(kRowCluster, 1, 1) __launch_bounds__(kFilterThr
         }
     };
     auto each_in_row = [&](auto&& f) {
-        for (int c0 = (int)rank * kFilterThreads + (tid & ~31); c0 < chunks; c0 += kRowCluster * kFilterThreads) {
+        for (int c0 = (int)rank * kFilterThreads + (tid & ~31); c0 < chunks; c0 += stride) {
             const int c = c0 + lane;
             float xs[4] = {0.0f, 0.0f, 0.0f, 0.0f};
             if (c < chunks) load_chunk(c, xs);
@@ -436,8 +442,7 @@ __global__ void __cluster_dims__(kRowCluster, 1, 1) __launch_bounds__(kFilterThr
         for (int b = tid; b < 256; b += kFilterThreads) {
             unsigned long long m = 0;
             unsigned n = 0;
-#pragma unroll
-            for (unsigned r = 0; r < (unsigned)kRowCluster; ++r) {
+            for (unsigned r = 0; r < blocks; ++r) {
                 m += peer_u64(&t.mass[b], r);
                 n += peer_u32(&t.count[b], r);
             }
@@ -452,7 +457,7 @@ __global__ void __cluster_dims__(kRowCluster, 1, 1) __launch_bounds__(kFilterThr
         if (tid == 0) sh.mine[turn].arg = mine;
         cluster_sync();
         if (tid < 32) {
-            const ArgMax all = cluster_best(&sh.mine[turn].arg);
+            const ArgMax all = cluster_best(&sh.mine[turn].arg, blocks);
             if (tid == 0) sh.best = all;
         }
         __syncthreads();
@@ -462,7 +467,7 @@ __global__ void __cluster_dims__(kRowCluster, 1, 1) __launch_bounds__(kFilterThr
 
     // Scaled logits y = x / T: the maximum.
     ArgMax top{-INFINITY, 0x7fffffff};
-    for (int c = (int)rank * kFilterThreads + tid; c < chunks; c += kRowCluster * kFilterThreads) {
+    for (int c = (int)rank * kFilterThreads + tid; c < chunks; c += stride) {
         float xs[4];
         load_chunk(c, xs);
 #pragma unroll
@@ -534,7 +539,7 @@ __global__ void __cluster_dims__(kRowCluster, 1, 1) __launch_bounds__(kFilterThr
         // every block copies the lists of all: what follows runs in each block alone, alike
         cluster_sync();
         unsigned start = 0;
-        for (unsigned r = 0; r < (unsigned)kRowCluster; ++r) {
+        for (unsigned r = 0; r < blocks; ++r) {
             const unsigned n = peer_u32(&sh.list_size, r);
             for (unsigned i = tid; i < n && start + i < (unsigned)kListCapacity; i += kFilterThreads)
                 sh.all[start + i] = peer_u32(&sh.list[i], r);
@@ -688,7 +693,7 @@ __global__ void __cluster_dims__(kRowCluster, 1, 1) __launch_bounds__(kFilterThr
     // ---- the draw ------------------------------------------------------------
     const unsigned long long seed = seeds[row], draw = draw_index[row];
     ArgMax best{-INFINITY, 0x7fffffff};
-    for (int c = (int)rank * kFilterThreads + tid; c < chunks; c += kRowCluster * kFilterThreads) {
+    for (int c = (int)rank * kFilterThreads + tid; c < chunks; c += stride) {
         float xs[4];
         load_chunk(c, xs);
         bool any = false;
@@ -764,12 +769,47 @@ B200_EXPORT int b200_sample(const float* logits, int rows, int vocab, const floa
         if (status) return status;
     }
     if (kinds & 2) {
-        if (vocab >= kFilterMaxVocab) return fail("sample", "filters (top-k, top-p, min-p) take a vocabulary below 524288");
         static const cudaError_t attribute = cudaFuncSetAttribute(sample_filtered_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                                                   (int)sizeof(FilterShared));
         if (attribute != cudaSuccess) return fail("sample", cudaGetErrorString(attribute));
-        sample_filtered_kernel<<<rows * kRowCluster, kFilterThreads, sizeof(FilterShared), stream>>>(logits, vocab, temperature, top_k, top_p, min_p,
-                                                                                  seeds, draw_index, tokens, greedy_eps);
+        cudaLaunchConfig_t config = {};
+        config.blockDim = dim3(kFilterThreads);
+        config.dynamicSmemBytes = sizeof(FilterShared);
+        config.stream = stream;
+        cudaLaunchAttribute cluster[1];
+        cluster[0].id = cudaLaunchAttributeClusterDimension;
+        cluster[0].val.clusterDim.y = 1;
+        cluster[0].val.clusterDim.z = 1;
+        config.attrs = cluster;
+        config.numAttrs = 1;
+        // Blocks to a row: eight while the GPU then holds all rows at once (a cluster needs its SMs
+        // side by side, so fewer clusters of eight fit than an eighth of the SMs), fewer for more rows;
+        // never so few that a column of a block could overflow (a thread takes every (blocks * 1024)-th
+        // chunk of four tokens, and the 32 warps of a block share a lane's column).
+        static int clusters_that_fit[kRowCluster + 1] = {};
+        auto fit = [&](int n) {
+            if (clusters_that_fit[n] == 0) {
+                config.gridDim = dim3(n * 64);
+                cluster[0].val.clusterDim.x = n;
+                int count = 0;
+                if (cudaOccupancyMaxActiveClusters(&count, sample_filtered_kernel, &config) != cudaSuccess || count < 1) {
+                    cudaGetLastError();
+                    count = sm_count() / (2 * n) > 0 ? sm_count() / (2 * n) : 1;
+                }
+                clusters_that_fit[n] = count;
+            }
+            return clusters_that_fit[n];
+        };
+        auto column_tokens = [&](int n) { return 128ll * ((vocab + 4096ll * n - 1) / (4096ll * n)); };
+        int blocks = kRowCluster;
+        while (blocks > 2 && rows > fit(blocks)) blocks >>= 1;
+        while (blocks < kRowCluster && column_tokens(blocks) > kColumnMaxTokens) blocks <<= 1;
+        if (column_tokens(blocks) > kColumnMaxTokens)
+            return fail("sample", "filters (top-k, top-p, min-p) take a vocabulary of 1015808 tokens at most");
+        config.gridDim = dim3(rows * blocks);
+        cluster[0].val.clusterDim.x = blocks;
+        cudaLaunchKernelEx(&config, sample_filtered_kernel, logits, vocab, temperature, top_k, top_p, min_p, seeds, draw_index, tokens,
+                           greedy_eps);
     }
     return check_launch("sample");
 }
