@@ -218,7 +218,7 @@ B200_EXPORT int b200_prefill_attention_tc_bf16(
     const int blocks = (num_tokens - token_offset) / kAtBlockRows + num_requests;
     if (blocks > 65535) return fail("prefill_attention_tc", "too many tokens for one launch");
     dim3 grid(nq, blocks, key_splits);
-    prefill_attention_tc_kernel<<<grid, kAtThreads, kAtSmem, stream>>>(
+    launch_overlapped(prefill_attention_tc_kernel, grid, dim3(kAtThreads), kAtSmem, stream,
         map_q, map_k, map_v, (__nv_bfloat16*)out, query_start, seq_lens, block_table, num_requests, max_pages,
         nq, nkv, page_size, scale * kLog2e, window, token_offset, key_splits, partial_o, partial_ml, error_flag);
     if (int rc = check_launch("prefill_attention_tc")) return rc;

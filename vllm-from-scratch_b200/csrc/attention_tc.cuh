@@ -283,6 +283,10 @@ __global__ void __launch_bounds__(kAtThreads, 1) prefill_attention_tc_kernel(
                 tma_load_2d(dst + kAtStageHalf, map, 64, row, bar);
             }
         };
+        // Queries, keys and values come from the kernel ahead on the stream; everything up to here
+        // (barriers, tensor memory, the zeroed stages) may have run beside its last blocks.  Nothing
+        // else of this block reads or writes global memory before data that these copies bring.
+        overlap_wait();
         if (lane == 0) {
             const int groups_here = rows_here > kAtRows ? 2 : 1;
             mbar_expect_tx(q_bar, (unsigned)groups_here * 2 * kAtHalf);

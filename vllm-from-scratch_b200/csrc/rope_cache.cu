@@ -130,6 +130,7 @@ __global__ void __launch_bounds__(128) head_norm_rope_cache_token_kernel(
     constexpr int HALF = D / 2, PER = HALF / 16;
     struct alignas(2 * PER) Vec { __nv_bfloat16 v[PER]; };
     __shared__ float sin_s[HALF], cos_s[HALF];
+    overlap_trigger();              // the attention kernel behind this one may set itself up meanwhile
     const int token = blockIdx.x;
     const float pos = (float)positions[token];
     for (int j = threadIdx.x; j < HALF; j += blockDim.x) sincosf(pos * inv_freq[j], &sin_s[j], &cos_s[j]);
