@@ -125,7 +125,10 @@ class LLMEngine:
             priority, seed=seed))
 
     def abort_request(self, request_ids) -> None:
+        request_ids = [request_ids] if isinstance(request_ids, str) else list(request_ids)
         self.scheduler.finish_requests(request_ids, RequestStatus.FINISHED_ABORTED)
+        for request_id in request_ids:
+            self.sampler.forget(request_id)
 
     def has_unfinished_requests(self) -> bool:
         return self.scheduler.has_unfinished_requests()
@@ -166,6 +169,9 @@ class LLMEngine:
                 self.runner.clear_device_errors()
                 raise RuntimeError(f"the step is void: {problem}")
         outputs = self.scheduler.update(current.plan, sampled)
+        for output in outputs:
+            if output.finished:
+                self.sampler.forget(output.request_id)
         idle = not self.scheduler.has_unfinished_requests()
         if self._pending is not None and idle:
             self._pending = None            # everyone stopped: what was queued ahead is of no use
@@ -221,7 +227,8 @@ class LLMEngine:
         tokens = self.sampler.sample_device(
             logits, [r.sampling_params for r in sampling], [r.seed for r in sampling],
             [r.prompt_token_ids for r in sampling], [r.output_token_ids for r in sampling],
-            ahead=0 if previous is None else 1, extra=kernels.STATUS_WORDS if on_gpu else 0)
+            ahead=0 if previous is None else 1, extra=kernels.STATUS_WORDS if on_gpu else 0,
+            keys=[r.request_id for r in sampling])
         if on_gpu:
             self.runner.write_status(tokens[len(sampling):])
         return _InFlight(plan, sampling, tokens, self._pinned(tokens.shape[0]), has_status=on_gpu)

@@ -22,23 +22,62 @@ from .. import kernels
 from .params import GREEDY_EPS, SamplingParams
 
 
+class _Seen:
+    """The distinct tokens that a request has seen, sorted, and how often each was generated:
+    what the penalties need, kept up from step to step instead of being counted again."""
+
+    __slots__ = ("tokens", "counts", "outputs")
+
+    def __init__(self, prompt: Sequence[int]) -> None:
+        self.tokens = np.unique(np.asarray(prompt, dtype=np.int32))
+        self.counts = np.zeros(self.tokens.shape[0], dtype=np.int32)
+        self.outputs = 0                        # output tokens counted so far
+
+    def extend(self, output: Sequence[int]) -> None:
+        fresh = output[self.outputs:]
+        self.outputs = len(output)
+        if len(fresh) > 32:                     # a whole history at once
+            values, counts = np.unique(np.asarray(fresh, dtype=np.int32), return_counts=True)
+            tokens = np.union1d(self.tokens, values)
+            merged = np.zeros(tokens.shape[0], dtype=np.int32)
+            merged[np.searchsorted(tokens, self.tokens)] = self.counts
+            merged[np.searchsorted(tokens, values)] += counts.astype(np.int32)
+            self.tokens, self.counts = tokens, merged
+            return
+        for token in fresh:
+            at = int(np.searchsorted(self.tokens, token))
+            if at < self.tokens.shape[0] and self.tokens[at] == token:
+                self.counts[at] += 1
+            else:
+                self.tokens = np.insert(self.tokens, at, token)
+                self.counts = np.insert(self.counts, at, 1)
+
+
 class Sampler:
     def __init__(self, vocab_size: int, device: torch.device | str) -> None:
         self.vocab_size = vocab_size
         self.device = torch.device(device)
+        self._seen: dict[str, _Seen] = {}       # by the key a caller names a request with
+
+    def forget(self, key: str) -> None:
+        """The request of this key is over (its key may name another request later)."""
+        self._seen.pop(key, None)
 
     def _to_device(self, array: np.ndarray) -> torch.Tensor:
         return torch.from_numpy(array).to(self.device, non_blocking=True)
 
     def sample(self, logits: torch.Tensor, params: Sequence[SamplingParams], seeds: Sequence[int],
-               prompts: Sequence[Sequence[int]], outputs: Sequence[Sequence[int]]) -> list[int]:
+               prompts: Sequence[Sequence[int]], outputs: Sequence[Sequence[int]],
+               keys: Sequence[str] | None = None) -> list[int]:
         """``logits`` is ``[rows, vocab]`` float32 on the device (changed in place by
-        penalties and masks); the other arguments have one entry per row."""
-        tokens = self.sample_device(logits, params, seeds, prompts, outputs)
+        penalties and masks); the other arguments have one entry per row.  ``keys``: a name
+        per request, the same from step to step; what a request has seen is then kept up under
+        its name instead of being counted anew every step (``forget`` it when the request ends)."""
+        tokens = self.sample_device(logits, params, seeds, prompts, outputs, keys=keys)
         return tokens.tolist()
 
     def sample_device(self, logits, params, seeds, prompts, outputs, ahead: int = 0,
-                      extra: int = 0) -> torch.Tensor:
+                      extra: int = 0, keys: Sequence[str] | None = None) -> torch.Tensor:
         """The sampled ids as an int32 tensor on the device, without waiting for them.
         ``ahead``: how many output tokens of every row are still on their way to the
         host and so missing from ``outputs`` (they count for the draw index and for
@@ -50,7 +89,7 @@ class Sampler:
             raise ValueError(f"{rows} rows of logits for {len(params)} requests")
         if ahead and any(p.has_penalties for p in params):
             raise ValueError("penalties need every earlier token: such rows cannot be sampled ahead")
-        self._penalties(logits, params, prompts, outputs)
+        self._penalties(logits, params, prompts, outputs, keys)
         self._min_tokens(logits, params, outputs, ahead)
         temperature = np.array([p.temperature for p in params], dtype=np.float32)
         top_k = np.array([p.top_k if p.top_k > 0 else 0 for p in params], dtype=np.int32)
@@ -66,22 +105,27 @@ class Sampler:
                        self._to_device(draw), tokens[:rows], GREEDY_EPS, kinds)
         return tokens
 
-    def _penalties(self, logits, params, prompts, outputs) -> None:
+    def _penalties(self, logits, params, prompts, outputs, keys=None) -> None:
         if not any(p.has_penalties for p in params):
             return
         offsets, seen, counts = [0], [], []
-        for p, prompt, output in zip(params, prompts, outputs):
+        for row, (p, prompt, output) in enumerate(zip(params, prompts, outputs)):
             if p.has_penalties:
-                in_output = Counter(output)
-                for token in sorted(set(prompt) | set(in_output)):
-                    seen.append(token)
-                    counts.append(in_output.get(token, 0))
-            offsets.append(len(seen))
-        if not seen:
+                history = self._seen.get(keys[row]) if keys is not None else None
+                if history is None or history.outputs > len(output):
+                    history = _Seen(prompt)
+                    if keys is not None:
+                        self._seen[keys[row]] = history
+                history.extend(output)
+                seen.append(history.tokens)
+                counts.append(history.counts)
+            offsets.append(offsets[-1] + (seen[-1].shape[0] if p.has_penalties else 0))
+        if offsets[-1] == 0:
             return
+        seen, counts = np.concatenate(seen), np.concatenate(counts)
         kernels.apply_penalties(
             logits, self._to_device(np.array(offsets, dtype=np.int32)),
-            self._to_device(np.array(seen, dtype=np.int32)), self._to_device(np.array(counts, dtype=np.int32)),
+            self._to_device(seen.astype(np.int32, copy=False)), self._to_device(counts.astype(np.int32, copy=False)),
             self._to_device(np.array([p.repetition_penalty for p in params], dtype=np.float32)),
             self._to_device(np.array([p.frequency_penalty for p in params], dtype=np.float32)),
             self._to_device(np.array([p.presence_penalty for p in params], dtype=np.float32)))
