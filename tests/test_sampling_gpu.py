@@ -123,6 +123,30 @@ def test_rows_with_and_without_filters_draw_alike(vocab, n):
         run(none, 0)
 
 
+def test_a_rows_token_does_not_depend_on_the_batch():
+    """Few rows get eight blocks each, many rows four or two: thresholds and draws are exact
+    functions of the row, so a row's token is the same whichever company it keeps."""
+    import vllm_from_scratch_b200.kernels as k
+    vocab = 32003
+    g = torch.Generator().manual_seed(8)
+    many = (torch.randn(70, vocab, generator=g) * 2.5).cuda()
+    settings = [(0.8, 40, 0.9, 0.0), (1.0, 0, 0.7, 0.0), (1.2, 7, 1.0, 0.0), (0.9, 0, 1.0, 0.03), (0.7, 0, 1.0, 0.0), (0.0, 0, 1.0, 0.0)]
+
+    def run(rows):
+        n = rows.shape[0]
+        column = lambda j, kind: torch.tensor([settings[i % len(settings)][j] for i in range(n)], dtype=kind, device="cuda")
+        out = torch.empty(n, dtype=torch.int32, device="cuda")
+        k.sample(rows, column(0, torch.float32), column(1, torch.int32), column(2, torch.float32), column(3, torch.float32),
+                 torch.arange(n, dtype=torch.int64, device="cuda") + 50, torch.arange(n, dtype=torch.int64, device="cuda") % 3,
+                 out, 1e-5)
+        return out.cpu().tolist()
+
+    whole = run(many)
+    assert run(many[:6].contiguous()) == whole[:6]
+    assert run(many[:24].contiguous()) == whole[:24]
+    assert len(set(whole)) > 20
+
+
 def test_filters_refuse_a_vocabulary_beyond_their_counters():
     import vllm_from_scratch_b200.kernels as k
     row = torch.zeros(1 << 20)
