@@ -91,18 +91,25 @@ class Sampler:
             raise ValueError("penalties need every earlier token: such rows cannot be sampled ahead")
         self._penalties(logits, params, prompts, outputs, keys)
         self._min_tokens(logits, params, outputs, ahead)
-        temperature = np.array([p.temperature for p in params], dtype=np.float32)
-        top_k = np.array([p.top_k if p.top_k > 0 else 0 for p in params], dtype=np.int32)
-        top_p = np.array([p.top_p for p in params], dtype=np.float32)
-        min_p = np.array([p.min_p for p in params], dtype=np.float32)
-        seed = np.array([s & 0x7FFFFFFFFFFFFFFF for s in seeds], dtype=np.int64)
-        draw = np.array([len(o) + ahead for o in outputs], dtype=np.int64)
+        # The six per-row arrays travel as one buffer: 64-bit words first, so that every view is aligned.
+        words = np.empty(rows * 8, dtype=np.int32)
+        wide = words[:rows * 4].view(np.int64)
+        wide[:rows] = [s & 0x7FFFFFFFFFFFFFFF for s in seeds]
+        wide[rows:] = [len(o) + ahead for o in outputs]
+        temperature, top_p, min_p = (words[rows * (4 + i):rows * (5 + i)].view(np.float32) for i in (0, 2, 3))
+        top_k = words[rows * 5:rows * 6]
+        temperature[:] = [p.temperature for p in params]
+        top_k[:] = [p.top_k if p.top_k > 0 else 0 for p in params]
+        top_p[:] = [p.top_p for p in params]
+        min_p[:] = [p.min_p for p in params]
         tokens = torch.empty(rows + extra, dtype=torch.int32, device=logits.device)
         filtered = (temperature >= GREEDY_EPS) & ((top_k > 0) | ~(top_p >= 1.0) | ~(min_p <= 0.0))
         kinds = (1 if not filtered.all() else 0) | (2 if filtered.any() else 0)
-        kernels.sample(logits, self._to_device(temperature), self._to_device(top_k),
-                       self._to_device(top_p), self._to_device(min_p), self._to_device(seed),
-                       self._to_device(draw), tokens[:rows], GREEDY_EPS, kinds)
+        on_device = self._to_device(words)
+        wide_d = on_device[:rows * 4].view(torch.int64)
+        part = lambda i: on_device[rows * (4 + i):rows * (5 + i)]
+        kernels.sample(logits, part(0).view(torch.float32), part(1), part(2).view(torch.float32), part(3).view(torch.float32),
+                       wide_d[:rows], wide_d[rows:], tokens[:rows], GREEDY_EPS, kinds)
         return tokens
 
     def _penalties(self, logits, params, prompts, outputs, keys=None) -> None:
