@@ -252,8 +252,8 @@ def test_steps_queued_ahead_give_the_same_tokens(folders, dtype):
     has reported its tokens.  Every request must end with the same tokens, finish for the
     same reason and at the same length as without it: greedy and seeded rows, a stop id
     that ends a request while its next step is already queued, ``max_tokens``,
-    ``min_tokens``, a request with penalties (which must fall back), and requests that
-    join while others decode."""
+    ``min_tokens``, requests with penalties (whose token in flight the sampler counts on the
+    device), and requests that join while others decode."""
     import vllm_from_scratch_b200 as engine
     raw = tiny_configs.TINY_B
     prompts = [helpers.random_tokens(raw["vocab_size"], n, seed=300 + i) for i, n in enumerate([9, 33, 17, 5, 21])]
@@ -272,7 +272,7 @@ def test_steps_queued_ahead_give_the_same_tokens(folders, dtype):
             engine.SamplingParams(temperature=0.9, top_k=12, top_p=0.9, seed=5, max_tokens=33, min_tokens=4,
                                   stop_token_ids=[stop_id]),
             engine.SamplingParams(temperature=0.0, max_tokens=25, repetition_penalty=1.3, presence_penalty=0.2),
-            engine.SamplingParams(temperature=0.7, seed=11, max_tokens=50),
+            engine.SamplingParams(temperature=0.7, seed=11, max_tokens=50, frequency_penalty=0.4, repetition_penalty=0.9),
         ]
         results[mode] = _generate_with_arrivals(llm, prompts, params, arrivals)
         llm.engine.runner.manager.check_invariants()

@@ -234,6 +234,42 @@ def test_penalties_and_masks_follow_the_formula():
     assert torch.isfinite(device[1]).all()
 
 
+def test_penalties_count_a_token_that_is_still_on_the_device():
+    """A step sampled ahead of the one before it lacks that step's token in its lists; the kernel
+    takes it from the device.  Bit for bit what the lists with the token in them give: a token
+    that was listed before (prompt only, or generated), one that is new, a row without penalties,
+    a row without such a token."""
+    import vllm_from_scratch_b200.kernels as k
+    vocab = 311
+    g = torch.Generator().manual_seed(9)
+    logits = torch.randn(5, vocab, generator=g) * 3
+    prompts = [[1, 2, 2, 300], [5, 6], [7, 8], [3], [10, 11]]
+    outputs = [[2, 9, 9], [6], [8, 8, 310], [], [12]]
+    last = [9, 5, 44, 77, None]                     # generated again; from the prompt; new; a row without penalties; none
+    rep, freq, pres = [1.3, 0.8, 1.0, 1.0, 1.1], [0.3, 0.7, 0.11, 0.0, 0.2], [0.1, 0.0, 0.4, 0.0, 0.3]
+    i32 = lambda v: torch.tensor(v, dtype=torch.int32, device="cuda")
+    f32 = lambda v: torch.tensor(v, dtype=torch.float32, device="cuda")
+
+    def lists(generated):
+        offsets, seen_tokens, counts = [0], [], []
+        for r in range(5):
+            for t in sorted(set(prompts[r]) | set(generated[r])):
+                seen_tokens.append(t)
+                counts.append(generated[r].count(t))
+            offsets.append(len(seen_tokens))
+        return i32(offsets), i32(seen_tokens), i32(counts)
+
+    whole = logits.cuda()
+    k.apply_penalties(whole, *lists([o + ([t] if t is not None else []) for o, t in zip(outputs, last)]),
+                      f32(rep), f32(freq), f32(pres))
+    ahead = logits.cuda()
+    on_device = i32([0, 77, 44, 5, 9, 123])          # in another order than the rows, with a word behind them
+    k.apply_penalties(ahead, *lists(outputs), f32(rep), f32(freq), f32(pres), on_device, i32([4, 3, 2, 1, -1]))
+    assert torch.equal(ahead, whole)
+    assert not torch.equal(ahead.cpu()[:3], logits[:3])
+    assert torch.equal(ahead.cpu()[3], logits[3])
+
+
 def test_min_tokens_masks_stop_ids_even_for_greedy_rows():
     import vllm_from_scratch_b200 as engine
     sampler = engine.Sampler(64, "cuda")

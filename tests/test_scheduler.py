@@ -209,7 +209,7 @@ def test_schedule_ahead_leaves_out_what_ends_by_length_and_declines_when_unsure(
     stopper.cache.check_invariants()
     assert stopper.cache.stats()["requests"] == 0
 
-    # declines: someone waits; a prompt portion was in the step; penalties; no page left
+    # declines: someone waits; a prompt portion was in the step; no page left
     waiting, _ = make(seqs=1, budget=16)
     plan = _decoding(waiting, [("a", 3), ("b", 3)], max_tokens=9)
     assert waiting.schedule_ahead(plan) is None
@@ -218,8 +218,9 @@ def test_schedule_ahead_leaves_out_what_ends_by_length_and_declines_when_unsure(
     portion.add_request(request("b", 9, max_tokens=9))
     run_step(portion)
     assert portion.schedule_ahead(portion.schedule()) is None
+    # penalties do not keep a step from being planned ahead: the sampler counts the token in flight on the device
     penal, _ = make(budget=16)
-    assert penal.schedule_ahead(_decoding(penal, [("a", 3)], max_tokens=9, repetition_penalty=1.2)) is None
+    assert penal.schedule_ahead(_decoding(penal, [("a", 3)], max_tokens=9, repetition_penalty=1.2)) is not None
     full, cache = make(pages=2, page_size=4, budget=16)
     plan = _decoding(full, [("a", 7)], max_tokens=9)         # 8 tokens fill both pages
     assert full.schedule_ahead(plan) is None

@@ -722,23 +722,40 @@ __global__ void __launch_bounds__(kFilterThreads, 1) sample_filtered_kernel(
 // output (0 = prompt only).  minivllm/sample/ops/penalties.py:51-72: a seen token's
 // logit is divided by the repetition penalty when positive, multiplied when not;
 // then frequency * count and presence * [count > 0] are subtracted.
+// A row may have one more generated token that the lists do not hold yet, because it is still
+// on the device (a step sampled ahead of the one before): last_tokens[last_rows[r]], no such
+// token where last_rows[r] is negative.  It counts as if it stood in the lists: one more for a
+// listed token, a count of one for a new one, with the arithmetic of a listed token either way.
 __global__ void penalties_kernel(float* __restrict__ logits, int vocab, const int* __restrict__ offsets,
                                  const int* __restrict__ seen_tokens, const int* __restrict__ output_counts,
                                  const float* __restrict__ repetition, const float* __restrict__ frequency,
-                                 const float* __restrict__ presence) {
+                                 const float* __restrict__ presence, const int* __restrict__ last_tokens,
+                                 const int* __restrict__ last_rows) {
     const int row = blockIdx.x;
     float* x = logits + (size_t)row * vocab;
+    const float rep = repetition[row], freq = frequency[row], pres = presence[row];
+    int last = -1;
+    if (last_tokens != nullptr && last_rows[row] >= 0) last = last_tokens[last_rows[row]];
+    if (last >= vocab) last = -1;
+    auto penalised = [&](float v, int count) {
+        v = v > 0.0f ? v * (1.0f / rep) : v * rep;
+        v -= freq * (float)count;
+        if (count > 0) v -= pres;
+        return v;
+    };
+    bool listed = false;
     for (int i = offsets[row] + threadIdx.x; i < offsets[row + 1]; i += blockDim.x) {
         const int token = seen_tokens[i];
         if (token < 0 || token >= vocab) continue;
-        float v = x[token];
-        const float rep = repetition[row];
-        v = v > 0.0f ? v * (1.0f / rep) : v * rep;
-        const int count = output_counts[i];
-        v -= frequency[row] * (float)count;
-        if (count > 0) v -= presence[row];
-        x[token] = v;
+        int count = output_counts[i];
+        if (token == last) {
+            ++count;
+            listed = true;
+        }
+        x[token] = penalised(x[token], count);
     }
+    listed = __syncthreads_or(listed);
+    if (threadIdx.x == 0 && last >= 0 && !listed) x[last] = penalised(x[last], 1);
 }
 
 // logits[rows[i], tokens[i]] = -inf: stop tokens of requests that have not yet
@@ -832,11 +849,14 @@ B200_EXPORT int b200_collect_status(const int* a, const int* b, const int* c, in
 
 B200_EXPORT int b200_penalties(float* logits, int rows, int vocab, const int* offsets,
                                const int* seen_tokens, const int* output_counts, const float* repetition,
-                               const float* frequency, const float* presence, cudaStream_t stream) {
+                               const float* frequency, const float* presence, const int* last_tokens,
+                               const int* last_rows, cudaStream_t stream) {
+    // last_tokens / last_rows: null, or per row the place in last_tokens of one more generated token (negative: none)
     using namespace b200;
     if (rows == 0) return 0;
+    if ((last_tokens == nullptr) != (last_rows == nullptr)) return fail("penalties", "last tokens and their rows go together");
     penalties_kernel<<<rows, 256, 0, stream>>>(logits, vocab, offsets, seen_tokens, output_counts,
-                                               repetition, frequency, presence);
+                                               repetition, frequency, presence, last_tokens, last_rows);
     return check_launch("penalties");
 }
 

@@ -209,10 +209,12 @@ class LLMEngine:
                                      [item.num_tokens - 1] if item.samples else []))
             if item.samples:
                 sampling.append(request)
+        last = None
         if previous is not None:
             row_of = {request.request_id: row for row, request in enumerate(previous.sampling)}
             rows = [row_of[item.request.request_id] for item in plan.scheduled]
             logits = self.decode_graphs.run(entries, device_tokens=(previous.tokens, rows))
+            last = (previous.tokens, [row_of[request.request_id] for request in sampling])
         elif self.decode_graphs is not None and self.decode_graphs.accepts(entries):
             logits = self.decode_graphs.run(entries)
         elif self.mixed_graphs is not None:
@@ -228,7 +230,7 @@ class LLMEngine:
             logits, [r.sampling_params for r in sampling], [r.seed for r in sampling],
             [r.prompt_token_ids for r in sampling], [r.output_token_ids for r in sampling],
             ahead=0 if previous is None else 1, extra=kernels.STATUS_WORDS if on_gpu else 0,
-            keys=[r.request_id for r in sampling])
+            keys=[r.request_id for r in sampling], last=last)
         if on_gpu:
             self.runner.write_status(tokens[len(sampling):])
         return _InFlight(plan, sampling, tokens, self._pinned(tokens.shape[0]), has_status=on_gpu)

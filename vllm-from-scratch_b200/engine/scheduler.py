@@ -208,8 +208,7 @@ class Scheduler:
         request of it that cannot end by length goes on with the one token that
         ``previous`` samples, which the host does not know yet.  Declines (``None``)
         whenever that is not plainly the next step: something waits, ``previous`` was not
-        a pure decode step or preempted, a page is missing (no preemption on a guess), or
-        a request samples with penalties (they need the unknown token)."""
+        a pure decode step or preempted, or a page is missing (no preemption on a guess)."""
         if self.waiting or previous.preempted_ids or not previous.scheduled:
             return None
         if len(previous.scheduled) != len(self.running):
@@ -218,8 +217,7 @@ class Scheduler:
         for item in previous.scheduled:
             request = item.request
             if (not item.samples or item.num_tokens != 1 or request.status is not RequestStatus.RUNNING
-                    or request.num_computed_tokens != request.num_tokens
-                    or request.sampling_params.has_penalties):
+                    or request.num_computed_tokens != request.num_tokens):
                 return None
             produced = len(request.output_token_ids) + 1            # with the token in flight
             if produced >= request.sampling_params.max_tokens or request.num_tokens + 1 >= self.max_model_len:

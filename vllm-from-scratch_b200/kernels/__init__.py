@@ -401,10 +401,17 @@ def sample(logits: torch.Tensor, temperature: torch.Tensor, top_k: torch.Tensor,
 
 def apply_penalties(logits: torch.Tensor, offsets: torch.Tensor, seen_tokens: torch.Tensor,
                     output_counts: torch.Tensor, repetition: torch.Tensor, frequency: torch.Tensor,
-                    presence: torch.Tensor) -> None:
+                    presence: torch.Tensor, last_tokens: torch.Tensor | None = None,
+                    last_rows: torch.Tensor | None = None) -> None:
     """In place: for row r and each distinct seen token ``seen_tokens[offsets[r]:
-    offsets[r + 1]]`` apply the repetition, frequency and presence penalties."""
+    offsets[r + 1]]`` apply the repetition, frequency and presence penalties.  With
+    ``last_tokens`` and ``last_rows`` row r has one more generated token,
+    ``last_tokens[last_rows[r]]`` (none where ``last_rows[r]`` is negative), which the lists do
+    not hold because it has not reached the host yet."""
     rows, vocab = logits.shape
+    last = (0, 0)
+    if last_tokens is not None:
+        last = (_check("last tokens", last_tokens, torch.int32), _check("rows of the last tokens", last_rows, torch.int32, (rows,)))
     _run("sampling", "b200_penalties",
          _P(_check("logits", logits, torch.float32)), _I(rows), _I(vocab),
          _P(_check("offsets", offsets, torch.int32, (rows + 1,))),
@@ -412,7 +419,7 @@ def apply_penalties(logits: torch.Tensor, offsets: torch.Tensor, seen_tokens: to
          _P(_check("output counts", output_counts, torch.int32, tuple(seen_tokens.shape))),
          _P(_check("repetition", repetition, torch.float32, (rows,))),
          _P(_check("frequency", frequency, torch.float32, (rows,))),
-         _P(_check("presence", presence, torch.float32, (rows,))), _stream())
+         _P(_check("presence", presence, torch.float32, (rows,))), _P(last[0]), _P(last[1]), _stream())
 
 
 def mask_tokens(logits: torch.Tensor, rows: torch.Tensor, tokens: torch.Tensor) -> None:

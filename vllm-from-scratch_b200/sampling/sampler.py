@@ -77,19 +77,23 @@ class Sampler:
         return tokens.tolist()
 
     def sample_device(self, logits, params, seeds, prompts, outputs, ahead: int = 0,
-                      extra: int = 0, keys: Sequence[str] | None = None) -> torch.Tensor:
+                      extra: int = 0, keys: Sequence[str] | None = None,
+                      last: tuple[torch.Tensor, Sequence[int]] | None = None) -> torch.Tensor:
         """The sampled ids as an int32 tensor on the device, without waiting for them.
-        ``ahead``: how many output tokens of every row are still on their way to the
-        host and so missing from ``outputs`` (they count for the draw index and for
-        ``min_tokens``; rows with penalties cannot be sampled ahead).  ``extra``: that
+        ``ahead``: how many output tokens of every row (none or one) are still on their way to
+        the host and so missing from ``outputs``; they count for the draw index and for
+        ``min_tokens``, and rows with penalties need them: ``last`` is then the device tensor that
+        holds them and, per row, the place of the row's token in it.  ``extra``: that
         many more int32 words are allocated behind the ids for the caller to fill (the
         step's status words, so that one copy brings both to the host)."""
         rows = logits.shape[0]
         if rows != len(params):
             raise ValueError(f"{rows} rows of logits for {len(params)} requests")
-        if ahead and any(p.has_penalties for p in params):
-            raise ValueError("penalties need every earlier token: such rows cannot be sampled ahead")
-        self._penalties(logits, params, prompts, outputs, keys)
+        if ahead not in (0, 1):
+            raise ValueError("at most one token of a row may be on its way")
+        if ahead and last is None and any(p.has_penalties for p in params):
+            raise ValueError("penalties need every earlier token: name the tensor that holds the one on its way")
+        self._penalties(logits, params, prompts, outputs, keys, last if ahead else None)
         self._min_tokens(logits, params, outputs, ahead)
         # The six per-row arrays travel as one buffer: 64-bit words first, so that every view is aligned.
         words = np.empty(rows * 8, dtype=np.int32)
@@ -112,7 +116,7 @@ class Sampler:
                        wide_d[:rows], wide_d[rows:], tokens[:rows], GREEDY_EPS, kinds)
         return tokens
 
-    def _penalties(self, logits, params, prompts, outputs, keys=None) -> None:
+    def _penalties(self, logits, params, prompts, outputs, keys=None, last=None) -> None:
         if not any(p.has_penalties for p in params):
             return
         offsets, seen, counts = [0], [], []
@@ -127,15 +131,21 @@ class Sampler:
                 seen.append(history.tokens)
                 counts.append(history.counts)
             offsets.append(offsets[-1] + (seen[-1].shape[0] if p.has_penalties else 0))
-        if offsets[-1] == 0:
+        if offsets[-1] == 0 and last is None:
             return
-        seen, counts = np.concatenate(seen), np.concatenate(counts)
+        seen = np.concatenate(seen) if seen else np.zeros(0, dtype=np.int32)
+        counts = np.concatenate(counts) if counts else np.zeros(0, dtype=np.int32)
+        last_tokens = last_rows = None
+        if last is not None:
+            last_tokens = last[0]
+            last_rows = self._to_device(np.asarray(last[1], dtype=np.int32))
         kernels.apply_penalties(
             logits, self._to_device(np.array(offsets, dtype=np.int32)),
             self._to_device(seen.astype(np.int32, copy=False)), self._to_device(counts.astype(np.int32, copy=False)),
             self._to_device(np.array([p.repetition_penalty for p in params], dtype=np.float32)),
             self._to_device(np.array([p.frequency_penalty for p in params], dtype=np.float32)),
-            self._to_device(np.array([p.presence_penalty for p in params], dtype=np.float32)))
+            self._to_device(np.array([p.presence_penalty for p in params], dtype=np.float32)),
+            last_tokens, last_rows)
 
     def _min_tokens(self, logits, params, outputs, ahead: int = 0) -> None:
         rows, tokens = [], []
