@@ -114,9 +114,10 @@ def test_demo_command_line_prints_the_tokens_of_the_entry_point(tmp_path, capsys
         code = demo.main([*questions, "--random-weights", str(config_file), "--random-seed", "4", "--dtype", dtype,
                           "--max-model-len", "128", "--max-new-tokens", "9", "--block-size", "8",
                           "--num-kv-blocks", "48", "--max-num-seqs", "2", "--max-num-batched-tokens", "32",
-                          "--trace", "--scheduler-trace"])
+                          "--trace", "--scheduler-trace", "--logprobs", "2"])
         assert code == 0
         printed = capsys.readouterr().out
+        assert printed.count("cumulative logprob") == 3 and "(rank 1)" in printed
         answers = {int(m.group(1)): json.loads(m.group(2)) for m in re.finditer(r"answer\[q(\d+)\]: (\[.*\])", printed)}
         assert sorted(answers) == [0, 1, 2] and all(len(a) == 9 for a in answers.values())
         assert "finish reason LENGTH" in printed and "first step (num_scheduled_tokens=" in printed
@@ -285,6 +286,53 @@ def test_steps_queued_ahead_give_the_same_tokens(folders, dtype):
         assert ahead.token_ids == sync.token_ids, f"request {index}"
         assert ahead.finish_reason == sync.finish_reason and ahead.stop_reason == sync.stop_reason
     assert results[True][1].finish_reason.name == "STOP" and len(results[True][1].token_ids) <= 11
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_logprobs_of_generated_tokens_match_plain(folders, dtype):
+    """``SamplingParams.logprobs``: every generated token comes with its log-probability under the
+    model's own logits (before temperature and penalties, minivllm/sample/sampler.py:86-95), its
+    place, and the most likely tokens; the plain model gives the same numbers, with and without
+    steps queued ahead, and a request without the option gets none."""
+    import vllm_from_scratch_b200 as engine
+    name = "B" if dtype == "float32" else "E"
+    raw = getattr(tiny_configs, f"TINY_{name}")
+    prompts = [helpers.random_tokens(raw["vocab_size"], n, seed=700 + i) for i, n in enumerate([12, 40, 7])]
+    params = [engine.SamplingParams(temperature=0.0, max_tokens=10, logprobs=3),
+              engine.SamplingParams(temperature=0.8, top_k=20, seed=3, max_tokens=14, logprobs=0, repetition_penalty=1.2, min_tokens=2),
+              engine.SamplingParams(temperature=0.0, max_tokens=9)]
+    results = {}
+    for mode in (False, True):
+        llm = engine.LLM(folders[name], dtype=dtype, max_model_len=128, block_size=16, max_num_seqs=4,
+                         max_num_batched_tokens=64, async_scheduling=mode)
+        results[mode] = llm.generate(prompts, params)
+    bound = 1e-4 if dtype == "float32" else 2 * tiny_configs.BF16_REL[name]
+    for index, (prompt, out) in enumerate(zip(prompts, results[True])):
+        other = results[False][index]
+        assert out.token_ids == other.token_ids
+        if params[index].logprobs is None:
+            assert out.logprobs is None and out.cumulative_logprob is None
+            continue
+        assert len(out.logprobs) == len(out.token_ids)
+        assert [{t: (round(v.logprob, 5), v.rank) for t, v in entry.items()} for entry in out.logprobs] == \
+               [{t: (round(v.logprob, 5), v.rank) for t, v in entry.items()} for entry in other.logprobs]
+        weights = torch.bfloat16 if dtype == "bfloat16" else None
+        logits = helpers.plain_logits(folders[name], list(prompt) + out.token_ids[:-1], round_weights_to=weights)
+        total = 0.0
+        for place, (token, entry) in enumerate(zip(out.token_ids, out.logprobs)):
+            row = logits[len(prompt) - 1 + place]
+            expected = torch.log_softmax(row.double(), dim=-1)
+            scale = 1.0 if dtype == "float32" else float(row.abs().max())
+            assert abs(entry[token].logprob - float(expected[token])) < bound * scale, (index, place)
+            total += entry[token].logprob
+            wanted = params[index].logprobs
+            assert len(entry) in (wanted, wanted + 1)
+            if dtype == "float32":
+                assert entry[token].rank == int((row >= row[token]).sum())
+                best = torch.topk(row, wanted).indices.tolist() if wanted else []
+                listed = [t for t, v in sorted(entry.items(), key=lambda kv: kv[1].rank) if v.rank <= wanted]
+                assert listed == best, (index, place)
+        assert abs(out.cumulative_logprob - total) < 1e-6
 
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])

@@ -270,6 +270,46 @@ def test_penalties_count_a_token_that_is_still_on_the_device():
     assert torch.equal(ahead.cpu()[3], logits[3])
 
 
+@pytest.mark.parametrize("vocab", [503, 4096, 151936])
+def test_logprobs_follow_log_softmax_top_k_and_rank(vocab):
+    """minivllm/sample/sampler.py:313-349: log_softmax of the row at the sampled token, how many
+    logits are at least as large, and the largest tokens in order; rows that ask for lists of
+    different lengths or for none; ties; a token masked to -inf."""
+    import vllm_from_scratch_b200.kernels as k
+    g = torch.Generator().manual_seed(vocab)
+    rows = 6
+    logits = torch.randn(rows, vocab, generator=g) * 4
+    logits[1, 7] = logits[1, 300] = logits[1].max() + 1.0          # a tie at the top
+    logits[2, 5] = float("-inf")
+    tokens = torch.tensor([3, 300, 5, 11, vocab - 1, 0], dtype=torch.int32)
+    wanted = torch.tensor([5, 2, 0, -1, 32, 1], dtype=torch.int32)
+    width = 33
+    ids = torch.full((rows, width), -7, dtype=torch.int32, device="cuda")
+    values = torch.full((rows, width), 7.0, device="cuda")
+    place = torch.full((rows,), -7, dtype=torch.int32, device="cuda")
+    k.logprobs(logits.cuda(), tokens.cuda(), wanted.cuda(), ids, values, place)
+    ids, values, place = ids.cpu(), values.cpu(), place.cpu()
+    expected = torch.log_softmax(logits.double(), dim=-1)
+    for r in range(rows):
+        n = int(wanted[r])
+        if n < 0:
+            assert (ids[r] == -7).all() and place[r] == -7
+            continue
+        t = int(tokens[r])
+        assert ids[r, 0] == t and place[r] == int((logits[r] >= logits[r, t]).sum())
+        if logits[r, t] == float("-inf"):
+            assert values[r, 0] == float("-inf")
+        else:
+            assert abs(float(values[r, 0]) - float(expected[r, t])) < 1e-4
+        order = sorted(range(vocab), key=lambda i: (-float(logits[r, i]), i))[:n]
+        assert ids[r, 1:1 + n].tolist() == order
+        assert torch.allclose(values[r, 1:1 + n].double(), expected[r, order], atol=1e-4)
+        assert (ids[r, 1 + n:] == -7).all()
+    with pytest.raises(k.KernelError):
+        k.logprobs(logits.cuda(), tokens.cuda(), wanted.cuda(), torch.zeros((rows, 40), dtype=torch.int32, device="cuda"),
+                   torch.zeros((rows, 40), device="cuda"), place.cuda())
+
+
 def test_min_tokens_masks_stop_ids_even_for_greedy_rows():
     import vllm_from_scratch_b200 as engine
     sampler = engine.Sampler(64, "cuda")

@@ -241,3 +241,29 @@ def test_an_id_is_free_again_only_after_its_finished_notice_went_out():
     scheduler.add_request(request("r", 3))
     with pytest.raises(ValueError, match="already in use"):
         scheduler.add_request(request("r", 3))
+
+
+def test_logprobs_travel_with_the_tokens():
+    """``SamplingParams.logprobs`` within what is built; a step's columns of log-probabilities become
+    one dict per generated token (minivllm/logprobs.py:50-76): the generated token with its place,
+    then the list with places 1, 2, ..., a token that is both keeping the list's entry."""
+    from vllm_from_scratch_b200.engine.request import Logprob
+    for bad in (-1, 33):
+        with pytest.raises(NotImplementedError):
+            SamplingParams(logprobs=bad)
+    scheduler, _ = make(budget=16)
+    scheduler.add_request(request("a", 3, max_tokens=3, logprobs=2))
+    scheduler.add_request(request("b", 3, max_tokens=3))
+    plan = scheduler.schedule()
+    outputs = scheduler.update(plan, {"a": 7, "b": 8}, {"a": ([7, 9, 7], [-1.5, -0.25, -1.5], 2)})
+    by_id = {o.request_id: o for o in outputs}
+    assert by_id["b"].logprobs is None and by_id["b"].cumulative_logprob is None
+    assert by_id["a"].logprobs == [{7: Logprob(-1.5, 2), 9: Logprob(-0.25, 1)}]
+    assert by_id["a"].cumulative_logprob == -1.5
+    plan = scheduler.schedule()
+    outputs = scheduler.update(plan, {"a": 4, "b": 8}, {"a": ([4, 9, 1], [-3.0, -0.5, -1.0], 5)})
+    a = {o.request_id: o for o in outputs}["a"]
+    assert a.logprobs[1] == {4: Logprob(-3.0, 5), 9: Logprob(-0.5, 1), 1: Logprob(-1.0, 2)}
+    assert a.cumulative_logprob == -4.5 and len(a.logprobs) == len(a.token_ids) == 2
+    with pytest.raises(RuntimeError, match="log-probabilities"):
+        scheduler.update(scheduler.schedule(), {"a": 1, "b": 2})

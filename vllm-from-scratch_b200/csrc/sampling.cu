@@ -238,6 +238,141 @@ __global__ void __cluster_dims__(kPlainCluster, 1, 1) __launch_bounds__(kPlainTh
     }
 }
 
+// ---- log-probabilities of what was sampled ---------------------------------------------------
+// For a row that wants them: log_softmax of its logits (as they were before penalties, masks and
+// temperature: minivllm/sample/sampler.py:86-95, 313-315) at the sampled token, that token's place
+// among all tokens (how many logits are at least as large: minivllm/sample/sampler.py:318-349),
+// and the `wanted[row]` largest tokens in order (ties by token id).  A cluster of eight blocks to
+// a row: one pass for the maximum, the sum of exponentials (pairs of a maximum and a sum, joined
+// in a fixed order: the same row gives the same bits in any batch) and the place, then one pass
+// for every token of the list, each the largest that comes after the one before it.
+//   ids, values: [rows][width], column 0 the sampled token, columns 1 .. wanted[row] the list;
+//   place: [rows].  Rows with wanted[row] < 0 are left alone.
+constexpr int kLogprobThreads = 512;
+constexpr int kMaxLogprobs = 32;
+
+struct SoftmaxPart {
+    float top, sum;             // sum of exp(x - top) over a part of the row
+};
+
+__device__ __forceinline__ SoftmaxPart join(SoftmaxPart a, SoftmaxPart b) {
+    if (b.top == -INFINITY) return a;
+    if (a.top == -INFINITY) return b;
+    const float top = fmaxf(a.top, b.top);
+    return SoftmaxPart{top, a.sum * expf(a.top - top) + b.sum * expf(b.top - top)};
+}
+
+__global__ void __cluster_dims__(kRowCluster, 1, 1) __launch_bounds__(kLogprobThreads) logprobs_kernel(
+    const float* __restrict__ logits, int vocab, const int* __restrict__ tokens, const int* __restrict__ wanted, int width,
+    int* __restrict__ ids, float* __restrict__ values, int* __restrict__ place) {
+    __shared__ ArgMax scratch[33];
+    __shared__ SoftmaxPart parts[kLogprobThreads / 32];
+    __shared__ unsigned counts[kLogprobThreads / 32];
+    struct Shown {              // what this block shows to the others, used in turn
+        SoftmaxPart part;
+        unsigned count;
+        ArgMax best;
+    };
+    __shared__ Shown shown[2];
+    __shared__ ArgMax agreed;
+    const int row = blockIdx.x / kRowCluster, tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    const unsigned rank = cluster_rank();
+    const int n = wanted[row];
+    if (n < 0) return;                                  // the whole cluster leaves
+    const float* x = logits + (size_t)row * vocab;
+    const int token = tokens[row];
+    const float x_token = token >= 0 && token < vocab ? x[token] : -INFINITY;
+    const int chunks = (vocab + 3) >> 2;
+    const bool vec = (vocab & 3) == 0 && ((uintptr_t)x & 15) == 0;
+    auto each = [&](auto&& f) {                         // f(logit, token id) over this thread's share of the row
+        for (int c = (int)rank * kLogprobThreads + tid; c < chunks; c += kRowCluster * kLogprobThreads) {
+            if (vec) {
+                const float4 v = reinterpret_cast<const float4*>(x)[c];
+                f(v.x, 4 * c); f(v.y, 4 * c + 1); f(v.z, 4 * c + 2); f(v.w, 4 * c + 3);
+            } else {
+#pragma unroll
+                for (int j = 0; j < 4; ++j)
+                    if (4 * c + j < vocab) f(x[4 * c + j], 4 * c + j);
+            }
+        }
+    };
+    int turn = 0;
+
+    // maximum, sum of exponentials, place of the sampled token
+    SoftmaxPart mine{-INFINITY, 0.0f};
+    unsigned at_least = 0;
+    each([&](float v, int) {
+        if (v > mine.top) {
+            mine.sum = mine.sum * expf(mine.top - v) + 1.0f;    // exp(-inf) = 0 for the first
+            mine.top = v;
+        } else if (v > -INFINITY) {
+            mine.sum += expf(v - mine.top);
+        }
+        at_least += v >= x_token ? 1u : 0u;
+    });
+#pragma unroll
+    for (int offset = 16; offset > 0; offset >>= 1) {
+        mine = join(mine, SoftmaxPart{__shfl_xor_sync(0xffffffffu, mine.top, offset), __shfl_xor_sync(0xffffffffu, mine.sum, offset)});
+        at_least += __shfl_xor_sync(0xffffffffu, at_least, offset);
+    }
+    if (lane == 0) {
+        parts[warp] = mine;
+        counts[warp] = at_least;
+    }
+    __syncthreads();
+    if (tid == 0) {
+        SoftmaxPart all = parts[0];
+        unsigned count = counts[0];
+        for (int w = 1; w < kLogprobThreads / 32; ++w) {
+            all = join(all, parts[w]);
+            count += counts[w];
+        }
+        shown[turn].part = all;
+        shown[turn].count = count;
+    }
+    cluster_sync();
+    SoftmaxPart whole{-INFINITY, 0.0f};
+    unsigned count = 0;
+    for (unsigned r = 0; r < (unsigned)kRowCluster; ++r) {          // every thread, the same order
+        whole = join(whole, SoftmaxPart{__uint_as_float(peer_u32(&shown[turn].part.top, r)),
+                                        __uint_as_float(peer_u32(&shown[turn].part.sum, r))});
+        count += peer_u32(&shown[turn].count, r);
+    }
+    turn ^= 1;
+    const float log_sum = whole.top + logf(whole.sum);
+    if (rank == 0 && tid == 0) {
+        ids[(size_t)row * width] = token;
+        values[(size_t)row * width] = x_token - log_sum;
+        place[row] = (int)count;
+    }
+
+    // the list: each time the largest token that comes after the last one (value falling, id rising)
+    ArgMax last{INFINITY, -1};
+    for (int j = 0; j < n && j + 1 < width; ++j) {
+        ArgMax best{-INFINITY, 0x7fffffff};
+        each([&](float v, int i) {
+            const bool after = v < last.value || (v == last.value && i > last.index);
+            if (after) best = better(best, ArgMax{v, i});
+        });
+        best = block_argmax(best, scratch);
+        if (tid == 0) shown[turn].best = best;
+        cluster_sync();
+        if (tid < 32) {
+            const ArgMax all = cluster_best(&shown[turn].best, (unsigned)kRowCluster);
+            if (tid == 0) agreed = all;
+        }
+        __syncthreads();
+        last = agreed;
+        turn ^= 1;
+        if (rank == 0 && tid == 0) {
+            ids[(size_t)row * width + 1 + j] = last.index == 0x7fffffff ? -1 : last.index;
+            values[(size_t)row * width + 1 + j] = last.value - log_sum;
+        }
+        __syncthreads();                                // `agreed` is written again in the next round
+    }
+    cluster_sync();                                     // no block leaves while another may read what it shows
+}
+
 // ---- rows with a filter ------------------------------------------------------------------------
 constexpr int kFilterThreads = 1024;         // four threads to each of 256 bins when columns are summed
 constexpr int kCoarseBins = 256;
@@ -829,6 +964,18 @@ B200_EXPORT int b200_sample(const float* logits, int rows, int vocab, const floa
                            greedy_eps);
     }
     return check_launch("sample");
+}
+
+// Log-probabilities of the sampled tokens and of the largest tokens of rows that want them (see
+// logprobs_kernel); width: columns of ids and values, 1 + the longest list.
+B200_EXPORT int b200_logprobs(const float* logits, int rows, int vocab, const int* tokens, const int* wanted, int width,
+                              int* ids, float* values, int* place, cudaStream_t stream) {
+    using namespace b200;
+    if (rows == 0) return 0;
+    if (vocab <= 0) return fail("logprobs", "vocabulary must be positive");
+    if (width < 1 || width > kMaxLogprobs + 1) return fail("logprobs", "lists of 0 to 32 tokens");
+    logprobs_kernel<<<rows * kRowCluster, kLogprobThreads, 0, stream>>>(logits, vocab, tokens, wanted, width, ids, values, place);
+    return check_launch("logprobs");
 }
 
 namespace b200 {

@@ -56,6 +56,8 @@ def build_parser() -> argparse.ArgumentParser:
     parser.add_argument("--presence-penalty", type=float, default=0.0)
     parser.add_argument("--frequency-penalty", type=float, default=0.0)
     parser.add_argument("--min-tokens", type=int, default=0)
+    parser.add_argument("--logprobs", type=int, default=None,
+                        help="report every generated token's log-probability and this many most likely tokens")
     parser.add_argument("--seed", type=int, default=None)
     parser.add_argument("--ignore-eos", action="store_true")
     parser.add_argument("--trace", action="store_true", help="print what the first step fed to the model")
@@ -125,6 +127,7 @@ def main(argv=None) -> int:
             top_p=args.top_p, min_p=args.min_p, seed=args.seed, min_tokens=args.min_tokens,
             ignore_eos=args.ignore_eos, repetition_penalty=args.repetition_penalty,
             presence_penalty=args.presence_penalty, frequency_penalty=args.frequency_penalty,
+            logprobs=args.logprobs,
             eos_token_id=raw_config.get("eos_token_id") if not isinstance(raw_config.get("eos_token_id"), list)
             else raw_config["eos_token_id"][0]))
         print(f"\nprompt q{index}: {len(prompt)} tokens")
@@ -157,6 +160,12 @@ def main(argv=None) -> int:
         shown = tokenizer.decode(output.token_ids, skip_special_tokens=True) if tokenizer else output.token_ids
         print(f"\nanswer[q{index}]: {shown}")
         print(f"   finish reason {output.finish_reason.name if output.finish_reason else None}")
+        if output.logprobs is not None:
+            print(f"   cumulative logprob {output.cumulative_logprob:.4f}")
+            for token, entry in zip(output.token_ids, output.logprobs):
+                others = ", ".join(f"{t}: {v.logprob:.3f}" for t, v in sorted(entry.items(), key=lambda kv: kv[1].rank)
+                                   if t != token)
+                print(f"   {token}: {entry[token].logprob:.3f} (rank {entry[token].rank})" + (f"   [{others}]" if others else ""))
     stats = runner.manager.stats()
     print(f"\n{steps} steps, {generated} tokens, {seconds:.2f} s ({generated / max(seconds, 1e-9):.1f} tok/s)")
     print(f"cache at the end: {stats}; preemptions {llm.scheduler.num_preemptions}")

@@ -17,6 +17,7 @@ import time
 from pathlib import Path
 from typing import Sequence
 
+import numpy as np
 import torch
 
 from .. import kernels
@@ -39,10 +40,12 @@ class _InFlight:
     ``has_status``), and the pinned copy on its way to the host."""
 
     def __init__(self, plan: SchedulerOutput, sampling: list[Request], tokens: torch.Tensor | None,
-                 host: torch.Tensor | None, has_status: bool = False) -> None:
+                 host: torch.Tensor | None, has_status: bool = False, logprob_width: int = 0) -> None:
         self.plan, self.sampling, self.tokens, self.host = plan, sampling, tokens, host
         self.has_status = has_status
+        self.logprob_width = logprob_width          # columns of log-probabilities per row behind ids and status (0: none)
         self.status: list[int] | None = None        # filled by wait()
+        self.logprobs: dict[str, tuple[list[int], list[float], int]] | None = None
         self.arrived: torch.cuda.Event | None = None
         if tokens is not None and host is not None:
             host[:tokens.shape[0]].copy_(tokens, non_blocking=True)
@@ -54,11 +57,19 @@ class _InFlight:
             return {}
         if self.arrived is not None:
             self.arrived.synchronize()
-            values = self.host[:self.tokens.shape[0]].tolist()
+            words = self.host[:self.tokens.shape[0]].numpy()
         else:
-            values = self.tokens.tolist()
+            words = self.tokens.cpu().numpy()
+        rows = len(self.sampling)
+        extra = kernels.STATUS_WORDS if self.has_status else 0
+        values = words[:rows + extra].tolist()
         if self.has_status:
-            self.status = values[len(self.sampling):]
+            self.status = values[rows:]
+        if self.logprob_width:
+            ids, bits, places = Sampler.logprob_views(words[rows + extra:], rows, self.logprob_width)
+            ids, numbers, places = ids.tolist(), bits.view(np.float32).tolist(), places.tolist()
+            self.logprobs = {request.request_id: (ids[row], numbers[row], places[row])
+                             for row, request in enumerate(self.sampling) if request.sampling_params.logprobs is not None}
         return {request.request_id: token for request, token in zip(self.sampling, values)}
 
 
@@ -168,7 +179,7 @@ class LLMEngine:
             if problem:
                 self.runner.clear_device_errors()
                 raise RuntimeError(f"the step is void: {problem}")
-        outputs = self.scheduler.update(current.plan, sampled)
+        outputs = self.scheduler.update(current.plan, sampled, current.logprobs)
         for output in outputs:
             if output.finished:
                 self.sampler.forget(output.request_id)
@@ -188,7 +199,8 @@ class LLMEngine:
         if self.runner.device.type != "cuda":
             return None
         if not self._host_tokens:
-            size = max(rows, self.config.scheduler_config.max_num_seqs + kernels.STATUS_WORDS)
+            most = self.config.scheduler_config.max_num_seqs
+            size = max(rows, most + kernels.STATUS_WORDS + Sampler.logprob_words(most, kernels.MAX_LOGPROBS + 1))
             self._host_tokens = [torch.empty(size, dtype=torch.int32, pin_memory=True) for _ in range(2)]
         self._host_tokens.reverse()
         buffer = self._host_tokens[0]
@@ -232,8 +244,9 @@ class LLMEngine:
             ahead=0 if previous is None else 1, extra=kernels.STATUS_WORDS if on_gpu else 0,
             keys=[r.request_id for r in sampling], last=last)
         if on_gpu:
-            self.runner.write_status(tokens[len(sampling):])
-        return _InFlight(plan, sampling, tokens, self._pinned(tokens.shape[0]), has_status=on_gpu)
+            self.runner.write_status(tokens[len(sampling):len(sampling) + kernels.STATUS_WORDS])
+        return _InFlight(plan, sampling, tokens, self._pinned(tokens.shape[0]), has_status=on_gpu,
+                         logprob_width=Sampler.logprob_width([r.sampling_params for r in sampling]))
 
     # -------------------------------------------------------------------- trace
     def _describe_inputs(self, plan: SchedulerOutput) -> dict | None:

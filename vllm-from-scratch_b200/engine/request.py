@@ -32,6 +32,16 @@ class FinishReason(enum.Enum):
     ABORT = "abort"
 
 
+@dataclass
+class Logprob:
+    """What is reported of one token at one generated position (minivllm/logprobs.py:30-37):
+    its log-probability and its place among all tokens (1: the most likely)."""
+
+    logprob: float
+    rank: int | None = None
+    decoded_token: str | None = None
+
+
 _REASON = {
     RequestStatus.FINISHED_STOPPED: FinishReason.STOP,
     RequestStatus.FINISHED_LENGTH_CAPPED: FinishReason.LENGTH,
@@ -52,6 +62,33 @@ class Request:
     num_computed_tokens: int = 0
     num_preemptions: int = 0
     stop_reason: int | None = None
+    # With SamplingParams.logprobs: per generated token a dict from token id to Logprob, the
+    # generated token and the most likely ones (minivllm/logprobs.py:50-76), and the sum of the
+    # generated tokens' log-probabilities.
+    logprobs: list[dict[int, Logprob]] | None = None
+    cumulative_logprob: float | None = None
+
+    def append_output(self, token: int, reported: tuple[list[int], list[float], int] | None = None) -> None:
+        """The one place where a generated token is added.  ``reported``: the columns of the
+        sampler's log-probabilities for it (ids and values, the generated token first, and its
+        place)."""
+        self.output_token_ids.append(int(token))
+        wanted = self.sampling_params.logprobs
+        if wanted is None:
+            return
+        if reported is None:
+            raise RuntimeError(f"request {self.request_id!r} asked for log-probabilities and the step brought none")
+        ids, values, place = reported
+        if self.logprobs is None:
+            self.logprobs, self.cumulative_logprob = [], 0.0
+        # the generated token first, then the list with places 1, 2, ...: a token that is both keeps
+        # the later entry, as in the reference's dict
+        entry = {int(ids[0]): Logprob(float(values[0]), int(place))}
+        for position in range(1, wanted + 1):
+            if ids[position] >= 0:
+                entry[int(ids[position])] = Logprob(float(values[position]), position)
+        self.logprobs.append(entry)
+        self.cumulative_logprob += float(values[0])
 
     @property
     def all_token_ids(self) -> list[int]:
@@ -81,6 +118,8 @@ class RequestOutput:
     finish_reason: FinishReason | None = None
     stop_reason: int | None = None
     num_preemptions: int = 0
+    logprobs: list[dict[int, Logprob]] | None = None        # aligned with token_ids
+    cumulative_logprob: float | None = None
 
 
 def check_stop(request: Request, max_model_len: int) -> bool:

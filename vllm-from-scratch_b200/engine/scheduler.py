@@ -260,10 +260,11 @@ class Scheduler:
                 f"{len(self.running)} running and {len(self.waiting)} waiting requests{detail}")
 
     # ------------------------------------------------------------------- update
-    def update(self, output: SchedulerOutput, sampled: dict[str, int]) -> list[RequestOutput]:
-        """Commit the step's results: append sampled tokens, decide who is over,
-        give their pages back, publish full pages (minivllm/core/sched/
-        scheduler.py:596-733)."""
+    def update(self, output: SchedulerOutput, sampled: dict[str, int],
+               logprobs: dict[str, tuple[list[int], list[float], int]] | None = None) -> list[RequestOutput]:
+        """Commit the step's results: append sampled tokens (with their log-probabilities where
+        a request asked for them), decide who is over, give their pages back, publish full pages
+        (minivllm/core/sched/scheduler.py:596-733)."""
         results: list[RequestOutput] = []
         for item in output.scheduled:
             request = item.request
@@ -273,7 +274,7 @@ class Scheduler:
             if item.samples:
                 if request.request_id not in sampled:
                     raise RuntimeError(f"no token was sampled for request {request.request_id!r}")
-                request.output_token_ids.append(int(sampled[request.request_id]))
+                request.append_output(sampled[request.request_id], (logprobs or {}).get(request.request_id))
                 finished = check_stop(request, self.max_model_len)
             # Publish full pages first: they stay hittable after the request is gone.
             self.cache.commit(request.request_id, request.num_computed_tokens, request.all_token_ids)
@@ -283,7 +284,8 @@ class Scheduler:
             if item.samples:
                 results.append(RequestOutput(
                     request.request_id, request.prompt_token_ids, list(request.output_token_ids), finished,
-                    request.finish_reason, request.stop_reason, request.num_preemptions))
+                    request.finish_reason, request.stop_reason, request.num_preemptions,
+                    None if request.logprobs is None else list(request.logprobs), request.cumulative_logprob))
         return results
 
     # -------------------------------------------------------------------- trace

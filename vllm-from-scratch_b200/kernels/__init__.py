@@ -399,6 +399,25 @@ def sample(logits: torch.Tensor, temperature: torch.Tensor, top_k: torch.Tensor,
          _P(_check("sampled tokens", tokens, torch.int32, (rows,))), _F(greedy_eps), _I(kinds), _stream())
 
 
+MAX_LOGPROBS = 32       # the longest list of largest tokens that `logprobs` returns beside the sampled one
+
+
+def logprobs(logits: torch.Tensor, tokens: torch.Tensor, wanted: torch.Tensor, ids: torch.Tensor,
+             values: torch.Tensor, place: torch.Tensor) -> None:
+    """For every row r with ``wanted[r] >= 0``: ``values[r, 0]`` = log_softmax(logits[r]) at
+    ``tokens[r]`` (``ids[r, 0]``), ``place[r]`` = how many logits of the row are at least as large,
+    and columns ``1 .. wanted[r]`` the largest tokens in order with their log-probabilities."""
+    rows, vocab = logits.shape
+    width = ids.shape[1]
+    _run("sampling", "b200_logprobs",
+         _P(_check("logits", logits, torch.float32)), _I(rows), _I(vocab),
+         _P(_check("sampled tokens", tokens, torch.int32, (rows,))),
+         _P(_check("lengths of the lists", wanted, torch.int32, (rows,))), _I(width),
+         _P(_check("token ids", ids, torch.int32, (rows, width))),
+         _P(_check("log-probabilities", values, torch.float32, (rows, width))),
+         _P(_check("places", place, torch.int32, (rows,))), _stream())
+
+
 def apply_penalties(logits: torch.Tensor, offsets: torch.Tensor, seen_tokens: torch.Tensor,
                     output_counts: torch.Tensor, repetition: torch.Tensor, frequency: torch.Tensor,
                     presence: torch.Tensor, last_tokens: torch.Tensor | None = None,

@@ -12,7 +12,6 @@ sample/gumbel.py:94-131).
 
 from __future__ import annotations
 
-from collections import Counter
 from typing import Sequence
 
 import numpy as np
@@ -89,6 +88,11 @@ class Sampler:
         rows = logits.shape[0]
         if rows != len(params):
             raise ValueError(f"{rows} rows of logits for {len(params)} requests")
+        width = self.logprob_width(params)
+        raw = logits
+        if width and (any(p.has_penalties for p in params)
+                      or any(len(o) + ahead < p.min_tokens for p, o in zip(params, outputs))):
+            raw = logits.clone()                # log-probabilities are those of the logits as the model gave them
         if ahead not in (0, 1):
             raise ValueError("at most one token of a row may be on its way")
         if ahead and last is None and any(p.has_penalties for p in params):
@@ -106,7 +110,7 @@ class Sampler:
         top_k[:] = [p.top_k if p.top_k > 0 else 0 for p in params]
         top_p[:] = [p.top_p for p in params]
         min_p[:] = [p.min_p for p in params]
-        tokens = torch.empty(rows + extra, dtype=torch.int32, device=logits.device)
+        tokens = torch.empty(rows + extra + self.logprob_words(rows, width), dtype=torch.int32, device=logits.device)
         filtered = (temperature >= GREEDY_EPS) & ((top_k > 0) | ~(top_p >= 1.0) | ~(min_p <= 0.0))
         kinds = (1 if not filtered.all() else 0) | (2 if filtered.any() else 0)
         on_device = self._to_device(words)
@@ -114,7 +118,32 @@ class Sampler:
         part = lambda i: on_device[rows * (4 + i):rows * (5 + i)]
         kernels.sample(logits, part(0).view(torch.float32), part(1), part(2).view(torch.float32), part(3).view(torch.float32),
                        wide_d[:rows], wide_d[rows:], tokens[:rows], GREEDY_EPS, kinds)
+        if width:
+            wanted = self._to_device(np.array([-1 if p.logprobs is None else p.logprobs for p in params], dtype=np.int32))
+            ids, values, place = self.logprob_views(tokens[rows + extra:], rows, width)
+            kernels.logprobs(raw, tokens[:rows], wanted, ids, values.view(torch.float32), place)
         return tokens
+
+    # Log-probabilities ride behind the ids (and the caller's extra words) in the same tensor, so that
+    # one copy brings everything to the host: [rows x width] token ids, [rows x width] float32
+    # values as their bits, [rows] places.
+    @staticmethod
+    def logprob_width(params: Sequence[SamplingParams]) -> int:
+        """Columns per row: the sampled token and the longest list; 0 if no row wants any."""
+        wanted = [p.logprobs for p in params if p.logprobs is not None]
+        return 1 + max(wanted) if wanted else 0
+
+    @staticmethod
+    def logprob_words(rows: int, width: int) -> int:
+        return rows * (2 * width + 1) if width else 0
+
+    @staticmethod
+    def logprob_views(words, rows: int, width: int):
+        """(ids, values as int32 bits, places) of ``words``, the tail of a sampled tensor or of
+        its host copy (a tensor or a numpy array)."""
+        ids = words[:rows * width].reshape(rows, width)
+        values = words[rows * width:2 * rows * width].reshape(rows, width)
+        return ids, values, words[2 * rows * width:2 * rows * width + rows]
 
     def _penalties(self, logits, params, prompts, outputs, keys=None, last=None) -> None:
         if not any(p.has_penalties for p in params):
