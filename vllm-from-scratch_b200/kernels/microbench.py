@@ -145,6 +145,8 @@ def main(argv=None) -> int:
     parser.add_argument("--top-p", type=float, default=1.0, help="sample")
     parser.add_argument("--min-p", type=float, default=0.0, help="sample")
     parser.add_argument("--spread", type=float, default=1.0, help="sample: standard deviation of the random logits")
+    parser.add_argument("--logprobs", type=int, default=None,
+                        help="sample: time the kernel for log-probabilities instead, with lists of this many tokens")
     parser.add_argument("--no-split-norm", action="store_true",
                         help="layer_products: the two norms as kernels of their own")
     parser.add_argument("--layers", type=int, default=4, help="step: layers of the model")
@@ -298,6 +300,18 @@ def main(argv=None) -> int:
         def launches():
             for _ in range(args.repeat):
                 kernels.sample(logits, temperature, top_k, top_p, min_p, seeds, draws, picked, 1e-5, 2 if filtered else 1)
+        if args.logprobs is not None:
+            launches()
+            width = args.logprobs + 1
+            ids = torch.empty(rows, width, dtype=torch.int32, device="cuda")
+            values = torch.empty(rows, width, device="cuda")
+            places = torch.empty(rows, dtype=torch.int32, device="cuda")
+            wanted = full(args.logprobs, torch.int32)
+
+            def launches():
+                for _ in range(args.repeat):
+                    kernels.logprobs(logits, picked, wanted, ids, values, places)
+            record.update(logprobs=args.logprobs)
         ms = _time(launches, args.warmup, args.iters, not args.keep_l2) / args.repeat
         record.update(rows=rows, vocab=args.vocab, temperature=args.temperature, top_k=args.top_k, top_p=args.top_p,
                       min_p=args.min_p, repeat=args.repeat, gb_s=round(rows * args.vocab * 4 / ms / 1e6, 1))
