@@ -289,6 +289,52 @@ def test_steps_queued_ahead_give_the_same_tokens(folders, dtype):
 
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_many_requests_with_random_options_the_same_with_and_without_steps_queued_ahead(folders, dtype):
+    """Twenty requests with options drawn at random (greedy or seeded, filters, penalties, stop
+    ids, ``min_tokens``, log-probabilities) that join at random steps: queueing steps ahead changes
+    nothing of what any of them gets."""
+    import random
+    import vllm_from_scratch_b200 as engine
+    raw = tiny_configs.TINY_B
+    rng = random.Random(11)
+    prompts, params, arrivals = [], [], []
+    for index in range(20):
+        prompts.append(helpers.random_tokens(raw["vocab_size"], rng.randint(1, 60), seed=900 + index))
+        options = {"max_tokens": rng.randint(1, 40), "temperature": rng.choice([0.0, 0.0, 0.7, 1.0, 1.3])}
+        if options["temperature"] > 0:
+            options["seed"] = rng.randrange(1000)
+            options.update(rng.choice([{}, {"top_k": rng.randint(1, 50)}, {"top_p": rng.uniform(0.3, 0.99)},
+                                       {"min_p": rng.uniform(0.01, 0.2)}, {"top_k": 30, "top_p": 0.8, "min_p": 0.02}]))
+        options.update(rng.choice([{}, {}, {"repetition_penalty": rng.uniform(0.8, 1.5)},
+                                   {"frequency_penalty": rng.uniform(0.1, 1.0), "presence_penalty": rng.uniform(0.0, 0.5)}]))
+        options.update(rng.choice([{}, {}, {"logprobs": rng.randint(0, 4)}]))
+        options.update(rng.choice([{}, {}, {"stop_token_ids": [rng.randrange(raw["vocab_size"]) for _ in range(40)]}]))
+        if rng.random() < 0.3:
+            options["min_tokens"] = rng.randint(0, options["max_tokens"])
+        params.append(engine.SamplingParams(**options))
+        arrivals.append(rng.randint(0, 45))
+    arrivals.sort()
+    results = {}
+    for mode in (False, True):
+        llm = engine.LLM(folders["B"], dtype=dtype, max_model_len=128, block_size=8, max_num_seqs=6,
+                         max_num_batched_tokens=40, async_scheduling=mode)
+        results[mode] = _generate_with_arrivals(llm, prompts, params, arrivals)
+        llm.engine.runner.manager.check_invariants()
+        assert llm.engine.runner.manager.stats()["requests"] == 0 and not llm.engine.sampler._seen
+    assert llm.engine.num_steps_ahead > 20
+    for index, (sync, ahead) in enumerate(zip(results[False], results[True])):
+        assert ahead.token_ids == sync.token_ids, f"request {index}: {params[index]}"
+        assert ahead.finish_reason == sync.finish_reason and ahead.stop_reason == sync.stop_reason
+        if dtype == "float32":
+            assert ahead.logprobs == sync.logprobs and ahead.cumulative_logprob == sync.cumulative_logprob
+        elif sync.logprobs is not None:
+            # a request that stops while its next step is queued keeps its row for that step: the
+            # others' logits are then those of a batch of another size, equal up to bfloat16 rounding
+            for token, one, other in zip(ahead.token_ids, ahead.logprobs, sync.logprobs):
+                assert abs(one[token].logprob - other[token].logprob) < 0.05
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
 def test_logprobs_of_generated_tokens_match_plain(folders, dtype):
     """``SamplingParams.logprobs``: every generated token comes with its log-probability under the
     model's own logits (before temperature and penalties, minivllm/sample/sampler.py:86-95), its
