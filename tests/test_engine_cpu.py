@@ -102,6 +102,17 @@ def test_stop_token_and_min_tokens(folders):
     held = llm.generate([prompt], engine.SamplingParams(temperature=0.0, max_tokens=6, min_tokens=6,
                                                         stop_token_ids=[stopper]))[0]
     assert stopper not in held.token_ids[:5] and len(held.token_ids) == 6
+    # the counts the entry point reports, and an abort between steps
+    core = llm.engine
+    core.add_request("x", prompt, engine.SamplingParams(temperature=0.0, max_tokens=5))
+    core.add_request("y", prompt, engine.SamplingParams(temperature=0.0, max_tokens=5))
+    assert core.get_num_unfinished_requests() == 2 and core.has_unfinished_requests()
+    core.step()
+    core.abort_request(["x"])
+    assert core.get_num_unfinished_requests() == 1
+    while core.has_unfinished_requests():
+        core.step()
+    assert core.get_num_unfinished_requests() == 0 and core.runner.manager.stats()["requests"] == 0
 
 
 def test_a_kernel_error_flag_stops_the_engine(folders, monkeypatch):

@@ -144,6 +144,10 @@ class LLMEngine:
     def has_unfinished_requests(self) -> bool:
         return self.scheduler.has_unfinished_requests()
 
+    def get_num_unfinished_requests(self) -> int:
+        """Running and waiting requests (minivllm/engine/llm_engine.py:83-86)."""
+        return len(self.scheduler.running) + len(self.scheduler.waiting)
+
     # --------------------------------------------------------------------- step
     def step(self) -> list[RequestOutput]:
         if self._failure is not None:
