@@ -102,6 +102,14 @@ def test_stop_token_and_min_tokens(folders):
     held = llm.generate([prompt], engine.SamplingParams(temperature=0.0, max_tokens=6, min_tokens=6,
                                                         stop_token_ids=[stopper]))[0]
     assert stopper not in held.token_ids[:5] and len(held.token_ids) == 6
+    # outputs carry text where the engine has a tokenizer
+    class Spelled:
+        def decode(self, ids, skip_special_tokens=True):
+            return " ".join(f"<{i}>" for i in ids)
+    worded = engine.LLM(folders["A"], dtype="float32", device="cpu", enforce_eager=True, max_model_len=64,
+                        tokenizer=Spelled())
+    out = worded.generate([prompt], engine.SamplingParams(temperature=0.0, max_tokens=3))[0]
+    assert out.token_ids == free[:3] and out.text == " ".join(f"<{i}>" for i in free[:3]) and held.text is None
     # the counts the entry point reports, and an abort between steps
     core = llm.engine
     core.add_request("x", prompt, engine.SamplingParams(temperature=0.0, max_tokens=5))

@@ -74,8 +74,11 @@ class _InFlight:
 
 
 class LLMEngine:
-    def __init__(self, config: EngineConfig, runner: ModelRunner | None = None) -> None:
+    def __init__(self, config: EngineConfig, runner: ModelRunner | None = None, tokenizer=None) -> None:
+        """``tokenizer``: anything with ``decode(ids, skip_special_tokens=True)``; outputs then carry
+        ``text`` (minivllm/engine/llm_engine.py:25, minivllm/outputs.py:198)."""
         self.config = config
+        self.tokenizer = tokenizer
         model, cache, sched = config.model_config, config.cache_config, config.scheduler_config
         self.runner = runner or ModelRunner.from_folder(
             model.model, model.dtype, cache.block_size, cache.num_gpu_blocks, sched.max_num_seqs,
@@ -187,6 +190,8 @@ class LLMEngine:
         for output in outputs:
             if output.finished:
                 self.sampler.forget(output.request_id)
+            if self.tokenizer is not None:
+                output.text = self.tokenizer.decode(output.token_ids, skip_special_tokens=True)
         idle = not self.scheduler.has_unfinished_requests()
         if self._pending is not None and idle:
             self._pending = None            # everyone stopped: what was queued ahead is of no use
@@ -283,13 +288,14 @@ class LLM:
                  block_size: int = 16, num_gpu_blocks: int | None = None, max_num_seqs: int = 8,
                  max_num_batched_tokens: int = 2048, enable_prefix_caching: bool = False,
                  enforce_eager: bool = False, seed: int = 0, device: str = "cuda",
-                 async_scheduling: bool = True) -> None:
+                 async_scheduling: bool = True, tokenizer=None) -> None:
         if num_gpu_blocks is None:
             num_gpu_blocks = max_num_seqs * -(-max_model_len // block_size)
         self.engine = LLMEngine(EngineConfig(
             ModelConfig(str(model), dtype, max_model_len, enforce_eager, seed),
             CacheConfig(block_size, num_gpu_blocks, enable_prefix_caching),
-            SchedulerConfig(max_num_seqs, max_num_batched_tokens, async_scheduling=async_scheduling), device))
+            SchedulerConfig(max_num_seqs, max_num_batched_tokens, async_scheduling=async_scheduling), device),
+            tokenizer=tokenizer)
         self._counter = 0
 
     def generate(self, prompt_token_ids: Sequence[Sequence[int]],

@@ -120,6 +120,7 @@ class RequestOutput:
     num_preemptions: int = 0
     logprobs: list[dict[int, Logprob]] | None = None        # aligned with token_ids
     cumulative_logprob: float | None = None
+    text: str | None = None                                 # of token_ids, where the engine has a tokenizer
 
 
 def check_stop(request: Request, max_model_len: int) -> bool:
