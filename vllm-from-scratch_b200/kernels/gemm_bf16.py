@@ -31,13 +31,36 @@ SKINNY_MAX_WEIGHT_ROWS = 8192
 # The engine's own few-rows kernels win on the short products of a small model's layer, where
 # the wait for the first bytes is most of the time and their copies start before the kernel ahead
 # has finished.  A matrix of tens of megabytes streams long enough for that not to matter, and
-# there the library's kernels are ahead (8 token rows, cold weights, microseconds own / library):
-# 6144 x 4096 14.7 / 11.1, 4096 x 12288 37.6 / 30.3, 10240 x 5120 29.5 / 20.6, 5120 x 8192
-# 32.4 / 17.4, 5120 x 25600 113 / 47, gated 24576 x 4096 60.7 / 36.9 (plus the activation
-# kernel); the output product over 151936 x 2048 takes the library 105.6 us, 0.90 of the copy
-# bandwidth.  Matrices above these sizes go to the library.
-OWN_MAX_WEIGHT_BYTES = 40 << 20
+# there the library's kernels are ahead; their time hardly grows with the token rows, the own
+# kernels' does, and the library is at its worst on few weight rows of a long K (launches back to
+# back over cold weights, microseconds own / library at 1, 8 and 16 token rows):
+#   2048 x 6144 (25 MB)    6.5 / 16.9    7.8 / 14.7    9.6 / 10.2
+#   2560 x 4096 (21 MB)    7.5 / 12.7    6.9 / 12.0    8.7 /  8.1
+#   6144 x 2560 (31 MB)    8.7 /  8.4   10.1 /  7.8   13.7 /  8.4
+#   4096 x 4096 (34 MB)    9.1 / 13.3   12.0 / 11.7   16.9 /  9.7
+#   2560 x 9728 (50 MB)   17.8 / 23.3   22.5 / 23.5   29.1 / 15.0
+#   6144 x 4096 (50 MB)   12.7 / 11.9   14.9 / 11.4   18.3 / 12.5
+#   4096 x 12288 (101 MB) 31.2 / 31.4   37.9 / 30.3   50.1 / 21.6
+#   gated 19456 x 2560 (100 MB) 23.0 / 20.4, 24.6 / 19.9, 34.1 / 20.1 (the library's with the activation kernel)
+# and the output product over 151936 x 2048 takes the library 105.6 us, 0.90 of the copy bandwidth.
+# The limits below follow these; whole decode steps with them against one limit of 40 MB for every
+# number of rows (models of 10 to 12 layers): Qwen3-4B widths 1.000 against 1.052 ms at batch 1, 1.236
+# against 1.254 at 16; Qwen3-8B widths 1.427 against 1.477 at 16; Qwen3-1.7B widths the same choices.
 OWN_MAX_GATED_WEIGHT_BYTES = 64 << 20
+
+
+def own_limit_bytes(m: int, weight_rows: int, gated: bool) -> int:
+    """The largest weight matrix that the engine's own kernels take for ``m`` token rows."""
+    if gated:
+        return OWN_MAX_GATED_WEIGHT_BYTES
+    few_rows = weight_rows <= 4096
+    if m <= 4:
+        return (56 if few_rows else 40) << 20
+    if m <= 8:
+        return (36 if few_rows else 28) << 20
+    return 26 << 20
+
+
 _P, _I = ctypes.c_void_p, ctypes.c_int
 
 
@@ -46,9 +69,11 @@ def _skinny_ok(m: int, n: int, k: int, *tensors: torch.Tensor) -> bool:
             and all(t.data_ptr() % 16 == 0 for t in tensors))
 
 
-def _small_enough(w: torch.Tensor, gated: bool) -> bool:
-    limit = OWN_MAX_GATED_WEIGHT_BYTES if gated else OWN_MAX_WEIGHT_BYTES
-    return w.numel() * w.element_size() <= limit
+def _small_enough(m: int, w: torch.Tensor, gated: bool) -> bool:
+    """Whether a product of ``m`` token rows with ``w`` is one for the engine's own kernels."""
+    return w.numel() * w.element_size() <= own_limit_bytes(m, w.shape[0] // 2 if gated else w.shape[0], gated)
+
+
 
 
 def _resident_ok(m: int, k: int, gated: bool, *tensors: torch.Tensor) -> bool:
@@ -72,7 +97,7 @@ def _skinny(x, w, out, gated_inter: int) -> None:
 
 
 def gemm_bf16(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor) -> None:
-    if _small_enough(w, False) and (
+    if _small_enough(x.shape[0], w, False) and (
             _skinny_ok(x.shape[0], w.shape[0], x.shape[1], x, w, out)
             or (w.shape[0] <= SKINNY_MAX_WEIGHT_ROWS and _resident_ok(x.shape[0], x.shape[1], False, x, w, out))):
         _skinny(x, w, out, 0)
@@ -89,7 +114,7 @@ def gated_silu_gemm_bf16(x: torch.Tensor, w_gate_up: torch.Tensor, out: torch.Te
     if tc_gated_ok(x.shape[0], out.shape[1], x.shape[1], x, w_gate_up, out):
         tc_gated_gemm(x, w_gate_up, out)
         return True
-    if not _small_enough(w_gate_up, True) or not (
+    if not _small_enough(x.shape[0], w_gate_up, True) or not (
             _skinny_ok(x.shape[0], w_gate_up.shape[0], x.shape[1], x, w_gate_up, out)
             or _resident_ok(x.shape[0], x.shape[1], True, x, w_gate_up, out)):
         return False
@@ -105,7 +130,7 @@ def split_norm_ok(tokens: int, w: torch.Tensor, fold: bool, gated: bool = False)
     """Whether ``split_norm_gemm`` takes the product: a shape for the resident-rows kernel, where the
     engine would use that kernel anyway, and whole blocks of eight result columns."""
     rows = w.shape[0] // 2 if gated else w.shape[0]
-    return (USE_SPLIT_NORM and rows % 8 == 0 and _small_enough(w, gated)
+    return (USE_SPLIT_NORM and rows % 8 == 0 and _small_enough(tokens, w, gated)
             and (gated or w.shape[0] <= SKINNY_MAX_WEIGHT_ROWS) and _resident_ok(tokens, w.shape[1], gated, w))
 
 
