@@ -279,11 +279,24 @@ def main(argv=None) -> int:
                     kernels.gemm(act, w_down, down)
                     kernels.add_rmsnorm(down, res, gain, 1e-6, normed)
                     kernels.gemm(normed, w_qkv, qkv)
-                else:
+                    continue
+                # a norm is split only where the engine would split it: both products around it its own kernels'
+                first = kernels.split_norm_ok(m, w_out, True) and kernels.split_norm_ok(m, w_gate_up, False, True)
+                second = kernels.split_norm_ok(m, w_down, True) and kernels.split_norm_ok(m, w_qkv, False)
+                if first:
                     kernels.gemm(x, w_out, out, fold=(res, gain, squares[0]))
                     kernels.gated_silu_gemm(out, w_gate_up, act, scale=(squares[0], 1e-6))
+                else:
+                    kernels.gemm(x, w_out, out)
+                    kernels.add_rmsnorm(out, res, gain, 1e-6, normed)
+                    kernels.gated_silu_gemm(normed, w_gate_up, act)
+                if second:
                     kernels.gemm(act, w_down, down, fold=(res, gain, squares[1]))
                     kernels.gemm(down, w_qkv, qkv, scale=(squares[1], 1e-6))
+                else:
+                    kernels.gemm(act, w_down, down)
+                    kernels.add_rmsnorm(down, res, gain, 1e-6, normed)
+                    kernels.gemm(normed, w_qkv, qkv)
         ms = _time(sweep, args.warmup, args.iters, False) / copies
         record.update(m=m, hidden=hidden, inter=inter, attended=attended, qkv=qkv_width,
                       split_norm=not args.no_split_norm, gb_s=round(layer_bytes / ms / 1e6, 1))
